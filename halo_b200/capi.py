@@ -1,0 +1,105 @@
+"""ctypes binding of libhalo_cuda.so (the C ABI declared in include/halo_cuda.h).
+
+The library is the product; this module only loads it and mirrors its structs.  There is no CPU
+fallback: if the library is missing, or no sm_100 device is present, the calls fail loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libhalo_cuda.so"
+
+OK = 0
+E_MODEL, E_MEMORY, E_BACKEND, E_KERNEL, E_CONFIG, E_API, E_DEVICE, E_UNSUPPORTED = -1, -2, -3, -4, -5, -6, -7, -8
+ERROR_NAMES = {E_MODEL: "Model", E_MEMORY: "Memory", E_BACKEND: "Backend", E_KERNEL: "Kernel", E_CONFIG: "Config", E_API: "Api",
+               E_DEVICE: "Device", E_UNSUPPORTED: "Unsupported"}
+
+OP_GET_ROWS, OP_GEMV, OP_LM_HEAD = 0, 3, 14
+GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16 = 0, 1, 2, 3, 4, 5
+FLAG_ALLOW_GEMM = 1
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("pci_id", C.c_char * 16), ("arch", C.c_char * 16), ("cc_major", C.c_int32),
+                ("cc_minor", C.c_int32), ("sm_count", C.c_int32), ("l2_bytes", C.c_int32), ("driver_version", C.c_int32),
+                ("runtime_version", C.c_int32), ("total_bytes", C.c_uint64), ("clock_khz", C.c_int32), ("mem_clock_khz", C.c_int32)]
+
+
+class Variant(C.Structure):
+    _fields_ = [("id", C.c_uint32), ("op", C.c_uint32), ("family", C.c_uint32), ("name", C.c_char_p)]
+
+
+class Gemv(C.Structure):
+    _fields_ = [("wtype", C.c_uint32), ("variant_id", C.c_uint32), ("w", C.c_void_p), ("w_stride", C.c_uint64), ("x", C.c_void_p),
+                ("x_stride", C.c_uint64), ("y", C.c_void_p), ("y_stride", C.c_uint64), ("rows", C.c_uint32), ("cols", C.c_uint32),
+                ("n_vec", C.c_uint32), ("flags", C.c_uint32)]
+
+
+class LmHead(C.Structure):
+    _fields_ = [("gemv", Gemv), ("result", C.c_void_p), ("ids", C.c_void_p), ("valid_rows", C.c_uint32), ("row_offset", C.c_uint32)]
+
+
+class GetRows(C.Structure):
+    _fields_ = [("type", C.c_uint32), ("variant_id", C.c_uint32), ("table", C.c_void_p), ("table_stride", C.c_uint64),
+                ("ids", C.c_void_p), ("out", C.c_void_p), ("out_stride", C.c_uint64), ("n_rows", C.c_uint32), ("cols", C.c_uint32),
+                ("n_ids", C.c_uint32), ("status", C.c_void_p)]
+
+
+# Every symbol include/halo_cuda.h declares: name -> (restype, argtypes)
+_P = C.c_void_p
+SYMBOLS = {
+    "halo_cuda_device_count": (C.c_int, [C.POINTER(C.c_int)]),
+    "halo_cuda_ctx_create": (C.c_int, [C.c_int, C.POINTER(_P)]),
+    "halo_cuda_ctx_destroy": (C.c_int, [_P]),
+    "halo_cuda_device_info": (C.c_int, [_P, C.POINTER(DeviceInfo)]),
+    "halo_cuda_malloc": (C.c_int, [_P, C.c_uint64, C.c_int, C.POINTER(_P)]),
+    "halo_cuda_free": (C.c_int, [_P, _P]),
+    "halo_cuda_stream_create": (C.c_int, [_P, C.POINTER(_P)]),
+    "halo_cuda_stream_destroy": (C.c_int, [_P, _P]),
+    "halo_cuda_stream_sync": (C.c_int, [_P, _P, C.c_uint64]),
+    "halo_cuda_ctx_lost": (C.c_int, [_P]),
+    "halo_cuda_memcpy_h2d_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),
+    "halo_cuda_memcpy_d2h_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),
+    "halo_cuda_memcpy_d2d_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),
+    "halo_cuda_memset_async": (C.c_int, [_P, _P, C.c_int, C.c_uint64, _P]),
+    "halo_cuda_host_alloc": (C.c_int, [_P, C.c_uint64, C.POINTER(_P)]),
+    "halo_cuda_host_free": (C.c_int, [_P, _P]),
+    "halo_cuda_event_create": (C.c_int, [_P, C.POINTER(_P)]),
+    "halo_cuda_event_destroy": (C.c_int, [_P, _P]),
+    "halo_cuda_event_record": (C.c_int, [_P, _P, _P]),
+    "halo_cuda_event_elapsed_ns": (C.c_int, [_P, _P, _P, C.POINTER(C.c_uint64)]),
+    "halo_cuda_row_bytes": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "halo_cuda_variants": (C.c_int, [C.c_uint32, C.POINTER(Variant), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "halo_cuda_gemv_resolve": (C.c_int, [_P, C.POINTER(Gemv), C.POINTER(C.c_uint32)]),
+    "halo_cuda_plan_set": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "halo_cuda_plan_clear": (C.c_int, [_P]),
+    "halo_cuda_last_error": (C.c_size_t, [C.c_char_p, C.c_size_t]),
+    "halo_cuda_gemv": (C.c_int, [_P, C.POINTER(Gemv), _P]),
+    "halo_cuda_lm_head": (C.c_int, [_P, C.POINTER(LmHead), _P]),
+    "halo_cuda_get_rows": (C.c_int, [_P, C.POINTER(GetRows), _P]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the in-tree library and sets every prototype; raises if it was not built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise FileNotFoundError(f"{LIB_PATH} is missing: run `python -m halo_b200.build` (there is no CPU fallback)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(1024)
+    load().halo_cuda_last_error(buf, len(buf))
+    return buf.value.decode(errors="replace")

@@ -1,0 +1,545 @@
+// Context, memory, streams, registry, operand validation and dispatch of libhalo_cuda.so.
+#include <chrono>
+#include <cstring>
+#include <new>
+#include <string>
+#include <thread>
+
+#include "internal.h"
+
+namespace halo_cuda {
+
+namespace {
+thread_local std::string g_error;
+
+constexpr HaloCudaVariant kGemvVariants[] = {
+    {HALO_CUDA_GEMV_EXACT8, HALO_CUDA_OP_GEMV, 0, "gemv_exact8"},
+    {HALO_CUDA_GEMV_WARP_F32, HALO_CUDA_OP_GEMV, 1, "gemv_warp_f32"},
+    {HALO_CUDA_GEMV_MMA_F16X2, HALO_CUDA_OP_GEMV, 2, "gemv_mma_f16x2"},
+    {HALO_CUDA_GEMM_TCGEN05_F16, HALO_CUDA_OP_GEMV, 2, "gemm_tcgen05_f16"},
+    {HALO_CUDA_GEMM_TCGEN05_BF16, HALO_CUDA_OP_GEMV, 2, "gemm_tcgen05_bf16"},
+};
+constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
+constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
+
+bool ranges_overlap(const void* a, uint64_t a_bytes, const void* b, uint64_t b_bytes) {
+    if (a_bytes == 0 || b_bytes == 0) return false;
+    const auto lo1 = reinterpret_cast<uintptr_t>(a), lo2 = reinterpret_cast<uintptr_t>(b);
+    return lo1 < lo2 + b_bytes && lo2 < lo1 + a_bytes;
+}
+
+bool mul_overflows(uint64_t a, uint64_t b) { return b != 0 && a > UINT64_MAX / b; }
+}  // namespace
+
+int fail(int status, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return status;
+}
+
+bool type_info(uint32_t wtype, TypeInfo* out) {
+    switch (wtype) {
+        case HALO_CUDA_T_F32: *out = {1, 4}; return true;
+        case HALO_CUDA_T_Q4_0: *out = {32, 18}; return true;
+        case HALO_CUDA_T_Q8_0: *out = {32, 34}; return true;
+        case HALO_CUDA_T_Q4_K: *out = {256, 144}; return true;
+        case HALO_CUDA_T_Q6_K: *out = {256, 210}; return true;
+        default: return false;
+    }
+}
+
+int enter(HaloCudaCtx* ctx) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    if (ctx->lost) return fail(HALO_CUDA_E_DEVICE, "device %d is lost (an earlier wait timed out or faulted)", ctx->device);
+    HC_CUDA(cudaSetDevice(ctx->device));
+    return 0;
+}
+
+int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out) {
+    if (bytes > ctx->workspace_bytes[slot]) {
+        // Work already enqueued may still read the old block: drain before releasing it.
+        HC_CUDA(cudaStreamSynchronize(stream));
+        if (ctx->workspace[slot] != nullptr) HC_CUDA(cudaFree(ctx->workspace[slot]));
+        ctx->workspace[slot] = nullptr;
+        ctx->workspace_bytes[slot] = 0;
+        const uint64_t want = (bytes + (1u << 20) - 1) & ~uint64_t{(1u << 20) - 1};
+        HC_CUDA(cudaMalloc(&ctx->workspace[slot], want));
+        ctx->workspace_bytes[slot] = want;
+    }
+    *out = ctx->workspace[slot];
+    return 0;
+}
+
+// The checks of the CPU backend's Resolver (src/backend/cpu_backend.cpp:98-162) for raw device pointers:
+// presence, stride >= row, overflow-checked extents, fp32 alignment, output disjoint from every input.
+int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* c) {
+    if (a == nullptr) return fail(HALO_CUDA_E_API, "%s: null argument struct", op);
+    TypeInfo ti{};
+    if (!type_info(a->wtype, &ti)) return fail(HALO_CUDA_E_UNSUPPORTED, "%s: no dequantization for weight type id %u", op, a->wtype);
+    if (a->cols % ti.block_elems != 0)
+        return fail(HALO_CUDA_E_MODEL, "%s: %u elements is not a multiple of the block size %u", op, a->cols, ti.block_elems);
+    c->wtype = a->wtype;
+    c->rows = a->rows;
+    c->cols = a->cols;
+    c->n_vec = a->n_vec;
+    c->flags = a->flags;
+    c->row_bytes = uint64_t{a->cols} / ti.block_elems * ti.block_bytes;
+    c->w = static_cast<const uint8_t*>(a->w);
+    c->x = a->x;
+    c->y = a->y;
+    c->w_stride = a->w_stride != 0 ? a->w_stride : c->row_bytes;
+    c->x_stride = a->x_stride != 0 ? a->x_stride : uint64_t{a->cols} * 4;
+    c->y_stride = a->y_stride != 0 ? a->y_stride : uint64_t{a->rows} * 4;
+    struct Op {
+        const char* name;
+        const void* p;
+        uint64_t n, row, stride, align;
+        bool optional;
+    } ops[3] = {{"w", c->w, a->rows, c->row_bytes, c->w_stride, a->wtype == HALO_CUDA_T_F32 ? 4u : 1u, false},
+                {"x", c->x, a->n_vec, uint64_t{a->cols} * 4, c->x_stride, 4, false},
+                {"y", c->y, a->n_vec, uint64_t{a->rows} * 4, c->y_stride, 4, y_optional}};
+    uint64_t extent[3] = {0, 0, 0};
+    for (int i = 0; i < 3; ++i) {
+        const Op& o = ops[i];
+        if (o.n == 0 || o.row == 0) {
+            if (o.p == nullptr) continue;
+        }
+        if (o.p == nullptr) {
+            if (o.optional) continue;
+            return fail(HALO_CUDA_E_KERNEL, "%s: operand %s is empty", op, o.name);
+        }
+        if (o.n > 1 && o.stride < o.row)
+            return fail(HALO_CUDA_E_KERNEL, "%s: operand %s row stride %llu < row bytes %llu", op, o.name,
+                        (unsigned long long)o.stride, (unsigned long long)o.row);
+        if (o.n != 0) {
+            if (mul_overflows(o.n - 1, o.stride) || (o.n - 1) * o.stride > UINT64_MAX - o.row)
+                return fail(HALO_CUDA_E_KERNEL, "%s: operand %s size overflows", op, o.name);
+            extent[i] = (o.n - 1) * o.stride + o.row;
+        }
+        if (reinterpret_cast<uintptr_t>(o.p) % o.align != 0 || o.stride % o.align != 0)
+            return fail(HALO_CUDA_E_KERNEL, "%s: operand %s is not %llu-byte aligned", op, o.name, (unsigned long long)o.align);
+    }
+    if (c->y != nullptr) {
+        if (ranges_overlap(c->y, extent[2], c->x, extent[1])) return fail(HALO_CUDA_E_KERNEL, "%s: output y overlaps operand x", op);
+        if (ranges_overlap(c->y, extent[2], c->w, extent[0])) return fail(HALO_CUDA_E_KERNEL, "%s: output y overlaps operand w", op);
+    }
+    return 0;
+}
+
+uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested) {
+    if (requested != HALO_CUDA_GEMV_DEFAULT) return requested;
+    if (c.cols == 0) return HALO_CUDA_GEMV_EXACT8;
+    const bool gemm_ok = (c.flags & HALO_CUDA_GEMV_FLAG_ALLOW_GEMM) != 0;
+    if (ctx != nullptr) {
+        for (const PlanEntry& p : ctx->plan) {
+            if (p.wtype != c.wtype || p.rows != c.rows || p.cols != c.cols || c.n_vec < p.n_vec_lo || c.n_vec > p.n_vec_hi) continue;
+            const bool is_gemm = p.variant_id == HALO_CUDA_GEMM_TCGEN05_F16 || p.variant_id == HALO_CUDA_GEMM_TCGEN05_BF16;
+            if (is_gemm && (!gemm_ok || !gemm_tcgen05_supports(c))) continue;
+            if (p.variant_id == HALO_CUDA_GEMV_MMA_F16X2 && !gemv_mma_supports(c)) continue;
+            if (p.variant_id == HALO_CUDA_GEMV_WARP_F32 && !gemv_warp_f32_supports(c)) continue;
+            return p.variant_id;
+        }
+    }
+    // Without a plan: the tensor-core GEMM only where the caller accepts its numerics and the batch is
+    // prefill-sized; otherwise one numerics family for every batch size, so that a row's bits do not depend
+    // on how many rows share the call (include/halo/backend/backend.h:300-304).
+    if (gemm_ok && c.n_vec >= 64 && gemm_tcgen05_supports(c)) return HALO_CUDA_GEMM_TCGEN05_F16;
+    if (gemv_mma_supports(c)) return HALO_CUDA_GEMV_MMA_F16X2;
+    if (gemv_warp_f32_supports(c)) return HALO_CUDA_GEMV_WARP_F32;
+    return HALO_CUDA_GEMV_EXACT8;
+}
+
+namespace {
+int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream_t s) {
+    const uint32_t v = resolve_variant(ctx, c, requested);
+    switch (v) {
+        case HALO_CUDA_GEMV_EXACT8: return launch_gemv_exact8(c, s);
+        case HALO_CUDA_GEMV_WARP_F32:
+            if (!gemv_warp_f32_supports(c)) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_warp_f32 does not take this weight type");
+            return launch_gemv_warp_f32(c, s);
+        case HALO_CUDA_GEMV_MMA_F16X2:
+            if (!gemv_mma_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_f16x2 needs Q4_K weights in dense 16-byte-aligned rows");
+            return launch_gemv_mma(ctx, c, s);
+        case HALO_CUDA_GEMM_TCGEN05_F16:
+        case HALO_CUDA_GEMM_TCGEN05_BF16:
+            if (!gemm_tcgen05_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemm_tcgen05 needs Q4_K weights in 16-byte-aligned rows and cols %% 256 == 0");
+            return launch_gemm_tcgen05(ctx, c, v == HALO_CUDA_GEMM_TCGEN05_BF16, s);
+        default: return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", v);
+    }
+}
+}  // namespace
+}  // namespace halo_cuda
+
+using namespace halo_cuda;
+
+extern "C" {
+
+int halo_cuda_device_count(int* count) {
+    if (count == nullptr) return fail(HALO_CUDA_E_API, "null count");
+    *count = 0;
+    const cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) {
+        *count = 0;
+        return fail(HALO_CUDA_E_DEVICE, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int halo_cuda_ctx_create(int device, HaloCudaCtx** out) {
+    if (out == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) return fail(HALO_CUDA_E_DEVICE, "no CUDA device is usable");
+    if (device < 0 || device >= n) return fail(HALO_CUDA_E_DEVICE, "device %d outside [0, %d)", device, n);
+    HaloCudaCtx* ctx = new (std::nothrow) HaloCudaCtx();
+    if (ctx == nullptr) return fail(HALO_CUDA_E_MEMORY, "out of host memory");
+    ctx->device = device;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&ctx->prop, device);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail(HALO_CUDA_E_DEVICE, "device %d: %s", device, cudaGetErrorString(e));
+    }
+    if (ctx->prop.major != 10) {
+        // The kernels are built for sm_100a only; there is no other code path.
+        const int major = ctx->prop.major, minor = ctx->prop.minor;
+        delete ctx;
+        return fail(HALO_CUDA_E_DEVICE, "device %d is sm_%d%d; this library holds sm_100a code only", device, major, minor);
+    }
+    *out = ctx;
+    return 0;
+}
+
+int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
+    if (ctx == nullptr) return 0;
+    if (cudaSetDevice(ctx->device) == cudaSuccess) {
+        for (void* p : ctx->workspace)
+            if (p != nullptr) cudaFree(p);
+    }
+    delete ctx;
+    return 0;
+}
+
+int halo_cuda_device_info(HaloCudaCtx* ctx, HaloCudaDeviceInfo* info) {
+    if (ctx == nullptr || info == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    std::memset(info, 0, sizeof *info);
+    std::snprintf(info->name, sizeof info->name, "%.127s", ctx->prop.name);
+    // cudaDeviceProp carries bus addresses, not the PCI device id: the vendor id is NVIDIA's, and the device id
+    // is filled in by NVML-aware callers (0000 marks "not read").
+    std::snprintf(info->pci_id, sizeof info->pci_id, "10de:0000");
+    std::snprintf(info->arch, sizeof info->arch, "sm_%d%da", ctx->prop.major, ctx->prop.minor);
+    info->cc_major = ctx->prop.major;
+    info->cc_minor = ctx->prop.minor;
+    info->sm_count = ctx->prop.multiProcessorCount;
+    info->l2_bytes = ctx->prop.l2CacheSize;
+    info->total_bytes = ctx->prop.totalGlobalMem;
+    cudaDriverGetVersion(&info->driver_version);
+    cudaRuntimeGetVersion(&info->runtime_version);
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, ctx->device) == cudaSuccess) info->clock_khz = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, ctx->device) == cudaSuccess) info->mem_clock_khz = v;
+    return 0;
+}
+
+int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int zero, void** ptr) {
+    if (ptr == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    *ptr = nullptr;
+    if (int rc = enter(ctx)) return rc;
+    const cudaError_t e = cudaMalloc(ptr, bytes == 0 ? 1 : bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(HALO_CUDA_E_MEMORY, "cannot allocate %llu bytes on device %d: %s", (unsigned long long)bytes, ctx->device,
+                    cudaGetErrorString(e));
+    }
+    if (zero != 0 && bytes != 0) HC_CUDA(cudaMemset(*ptr, 0, bytes));
+    return 0;
+}
+
+int halo_cuda_free(HaloCudaCtx* ctx, void* ptr) {
+    if (ptr == nullptr) return 0;
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    HC_CUDA(cudaSetDevice(ctx->device));
+    HC_CUDA(cudaFree(ptr));
+    return 0;
+}
+
+int halo_cuda_host_alloc(HaloCudaCtx* ctx, uint64_t bytes, void** ptr) {
+    if (ptr == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    *ptr = nullptr;
+    if (int rc = enter(ctx)) return rc;
+    const cudaError_t e = cudaHostAlloc(ptr, bytes == 0 ? 1 : bytes, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(HALO_CUDA_E_MEMORY, "cannot pin %llu host bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int halo_cuda_host_free(HaloCudaCtx* ctx, void* ptr) {
+    if (ptr == nullptr) return 0;
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    HC_CUDA(cudaFreeHost(ptr));
+    return 0;
+}
+
+int halo_cuda_stream_create(HaloCudaCtx* ctx, HaloCudaStream* stream) {
+    if (stream == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    if (int rc = enter(ctx)) return rc;
+    cudaStream_t s = nullptr;
+    HC_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return 0;
+}
+
+int halo_cuda_stream_destroy(HaloCudaCtx* ctx, HaloCudaStream stream) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    if (stream == nullptr) return 0;
+    HC_CUDA(cudaSetDevice(ctx->device));
+    HC_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_stream_sync(HaloCudaCtx* ctx, HaloCudaStream stream, uint64_t timeout_ns) {
+    if (int rc = enter(ctx)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (timeout_ns == 0) {
+        e = cudaStreamSynchronize(s);
+    } else {
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::nanoseconds(timeout_ns);
+        unsigned spins = 0;
+        while ((e = cudaStreamQuery(s)) == cudaErrorNotReady) {
+            if (std::chrono::steady_clock::now() >= deadline) {
+                ctx->lost = true;
+                return fail(HALO_CUDA_E_BACKEND, "stream wait exceeded %llu ns; device %d marked lost", (unsigned long long)timeout_ns,
+                            ctx->device);
+            }
+            if (++spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+        }
+    }
+    if (e != cudaSuccess) {
+        ctx->lost = true;
+        return fail(HALO_CUDA_E_BACKEND, "stream wait failed on device %d: %s", ctx->device, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int halo_cuda_ctx_lost(HaloCudaCtx* ctx) { return ctx != nullptr && ctx->lost ? 1 : 0; }
+
+int halo_cuda_memcpy_h2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (dst == nullptr || src == nullptr) return fail(HALO_CUDA_E_KERNEL, "upload: null pointer");
+    HC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_memcpy_d2h_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (dst == nullptr || src == nullptr) return fail(HALO_CUDA_E_KERNEL, "download: null pointer");
+    HC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_memcpy_d2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (dst == nullptr || src == nullptr) return fail(HALO_CUDA_E_KERNEL, "COPY: null pointer");
+    const auto d = reinterpret_cast<uintptr_t>(dst), s = reinterpret_cast<uintptr_t>(src);
+    if (d < s + bytes && s < d + bytes) return fail(HALO_CUDA_E_KERNEL, "COPY: output dst overlaps operand src");
+    HC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_memset_async(HaloCudaCtx* ctx, void* dst, int value, uint64_t bytes, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (bytes == 0) return 0;
+    if (dst == nullptr) return fail(HALO_CUDA_E_KERNEL, "memset: null pointer");
+    HC_CUDA(cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_event_create(HaloCudaCtx* ctx, HaloCudaEvent* event) {
+    if (event == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    if (int rc = enter(ctx)) return rc;
+    cudaEvent_t e = nullptr;
+    HC_CUDA(cudaEventCreate(&e));
+    *event = e;
+    return 0;
+}
+
+int halo_cuda_event_destroy(HaloCudaCtx* ctx, HaloCudaEvent event) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    if (event == nullptr) return 0;
+    HC_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+    return 0;
+}
+
+int halo_cuda_event_record(HaloCudaCtx* ctx, HaloCudaEvent event, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    HC_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int halo_cuda_event_elapsed_ns(HaloCudaCtx* ctx, HaloCudaEvent start, HaloCudaEvent stop, uint64_t* ns) {
+    if (ns == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    if (int rc = enter(ctx)) return rc;
+    HC_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+    float ms = 0.0f;
+    HC_CUDA(cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+    *ns = static_cast<uint64_t>(static_cast<double>(ms) * 1.0e6);
+    return 0;
+}
+
+int halo_cuda_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes) {
+    if (bytes == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    TypeInfo ti{};
+    if (!type_info(wtype, &ti)) return fail(HALO_CUDA_E_UNSUPPORTED, "unknown or unsupported tensor type id %u", wtype);
+    if (cols % ti.block_elems != 0)
+        return fail(HALO_CUDA_E_MODEL, "%llu elements is not a multiple of the block size %u", (unsigned long long)cols, ti.block_elems);
+    const uint64_t nb = cols / ti.block_elems;
+    if (nb > uint64_t{INT64_MAX} / ti.block_bytes) return fail(HALO_CUDA_E_MODEL, "byte size overflows");
+    *bytes = nb * ti.block_bytes;
+    return 0;
+}
+
+int halo_cuda_variants(uint32_t op, HaloCudaVariant* out, uint32_t cap, uint32_t* count) {
+    if (count == nullptr) return fail(HALO_CUDA_E_API, "null count");
+    const HaloCudaVariant* table = nullptr;
+    uint32_t n = 0;
+    switch (op) {
+        case HALO_CUDA_OP_GEMV: table = kGemvVariants; n = sizeof kGemvVariants / sizeof kGemvVariants[0]; break;
+        case HALO_CUDA_OP_LM_HEAD: table = kLmHeadVariants; n = 1; break;
+        case HALO_CUDA_OP_GET_ROWS: table = kGetRowsVariants; n = 1; break;
+        default: *count = 0; return fail(HALO_CUDA_E_UNSUPPORTED, "op id %u is not implemented by the cuda backend", op);
+    }
+    *count = n;
+    for (uint32_t i = 0; i < n && i < cap && out != nullptr; ++i) out[i] = table[i];
+    return 0;
+}
+
+int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec_lo, uint32_t n_vec_hi,
+                       uint32_t variant_id) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    if (variant_id == 0 || variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+        return fail(HALO_CUDA_E_CONFIG, "plan: unknown kernel variant id %u", variant_id);
+    if (n_vec_lo > n_vec_hi) return fail(HALO_CUDA_E_API, "plan: empty n_vec range");
+    for (PlanEntry& p : ctx->plan) {
+        if (p.wtype == wtype && p.rows == rows && p.cols == cols && p.n_vec_lo == n_vec_lo && p.n_vec_hi == n_vec_hi) {
+            p.variant_id = variant_id;
+            return 0;
+        }
+    }
+    ctx->plan.push_back({wtype, rows, cols, n_vec_lo, n_vec_hi, variant_id});
+    return 0;
+}
+
+int halo_cuda_plan_clear(HaloCudaCtx* ctx) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    ctx->plan.clear();
+    return 0;
+}
+
+size_t halo_cuda_last_error(char* buf, size_t len) {
+    if (buf != nullptr && len != 0) std::snprintf(buf, len, "%s", g_error.c_str());
+    return g_error.size();
+}
+
+int halo_cuda_gemv_resolve(HaloCudaCtx* ctx, const HaloCudaGemv* args, uint32_t* variant_id) {
+    if (variant_id == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    GemvCall c{};
+    if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
+    *variant_id = resolve_variant(ctx, c, args->variant_id);
+    return 0;
+}
+
+int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    GemvCall c{};
+    if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
+    if (args->variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+        return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
+    if (c.rows == 0 || c.n_vec == 0) return 0;
+    return run_gemv(ctx, c, args->variant_id, static_cast<cudaStream_t>(stream));
+}
+
+int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* a, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (a == nullptr) return fail(HALO_CUDA_E_API, "LM_HEAD: null argument struct");
+    GemvCall c{};
+    if (int rc = validate_gemv(&a->gemv, "LM_HEAD", true, &c)) return rc;
+    if (a->gemv.variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+        return fail(HALO_CUDA_E_CONFIG, "LM_HEAD: unknown kernel variant id %u on the cuda backend", a->gemv.variant_id);
+    if (c.n_vec == 0) return 0;
+    if (a->result == nullptr) return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: operand result is empty");
+    if (reinterpret_cast<uintptr_t>(a->result) % 4 != 0 || reinterpret_cast<uintptr_t>(a->ids) % 4 != 0)
+        return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: result / ids are not 4-byte aligned");
+    const uint64_t res_bytes = uint64_t{c.n_vec} * 12, ids_bytes = a->ids != nullptr ? uint64_t{c.n_vec} * 4 : 0;
+    const uint64_t x_ext = (uint64_t{c.n_vec} - 1) * c.x_stride + uint64_t{c.cols} * 4;
+    const uint64_t w_ext = c.rows == 0 ? 0 : (uint64_t{c.rows} - 1) * c.w_stride + c.row_bytes;
+    const uint64_t y_ext = c.y == nullptr ? 0 : (uint64_t{c.n_vec} - 1) * c.y_stride + uint64_t{c.rows} * 4;
+    struct R { const void* p; uint64_t n; const char* name; };
+    const R outs[2] = {{a->result, res_bytes, "result"}, {a->ids, ids_bytes, "ids"}};
+    const R ins[3] = {{c.x, x_ext, "x"}, {c.w, w_ext, "w"}, {c.y, y_ext, "logits"}};
+    for (const R& o : outs)
+        for (const R& i : ins)
+            if (o.p != nullptr && i.p != nullptr && ranges_overlap(o.p, o.n, i.p, i.n))
+                return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: output %s overlaps operand %s", o.name, i.name);
+    if (a->ids != nullptr && ranges_overlap(a->ids, ids_bytes, a->result, res_bytes))
+        return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: output ids overlaps operand result");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Logits go to the caller's buffer when one is given, else to context scratch; the argmax then runs over
+    // exactly the values the gemv stored (cpu_backend.cpp:734-750).
+    const uint64_t logits_bytes = c.y == nullptr ? uint64_t{c.n_vec} * c.rows * 4 : 0;
+    const uint64_t part_bytes = argmax_scratch_bytes(c.rows, c.n_vec);
+    const uint64_t logits_pad = (logits_bytes + 255) & ~uint64_t{255};
+    void* ws = nullptr;
+    if (int rc = workspace(ctx, 1, logits_pad + part_bytes + 256, s, &ws)) return rc;
+    GemvCall g = c;
+    if (c.y == nullptr) {
+        g.y = static_cast<float*>(ws);
+        g.y_stride = uint64_t{c.rows} * 4;
+    }
+    if (c.rows != 0) {
+        if (int rc = run_gemv(ctx, g, a->gemv.variant_id, s)) return rc;
+    }
+    return launch_argmax(g.y, g.y_stride / 4, c.rows, c.n_vec, a->valid_rows, a->row_offset, a->result, a->ids,
+                         static_cast<uint8_t*>(ws) + logits_pad, s);
+}
+
+int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* a, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    if (a == nullptr) return fail(HALO_CUDA_E_API, "GET_ROWS: null argument struct");
+    if (a->variant_id > 1) return fail(HALO_CUDA_E_CONFIG, "GET_ROWS: unknown kernel variant id %u on the cuda backend", a->variant_id);
+    TypeInfo ti{};
+    if (!type_info(a->type, &ti)) return fail(HALO_CUDA_E_UNSUPPORTED, "GET_ROWS: no dequantization for type id %u", a->type);
+    if (a->cols % ti.block_elems != 0)
+        return fail(HALO_CUDA_E_MODEL, "GET_ROWS: %u elements is not a multiple of the block size %u", a->cols, ti.block_elems);
+    const uint64_t rb = uint64_t{a->cols} / ti.block_elems * ti.block_bytes;
+    const uint64_t ts = a->table_stride != 0 ? a->table_stride : rb;
+    const uint64_t os = a->out_stride != 0 ? a->out_stride : uint64_t{a->cols} * 4;
+    if (a->n_ids == 0 || a->cols == 0) return 0;
+    if (a->table == nullptr || a->out == nullptr) return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: operand table / out is empty");
+    if (a->n_rows > 1 && ts < rb) return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: table row stride %llu < row bytes %llu", (unsigned long long)ts, (unsigned long long)rb);
+    if (a->n_ids > 1 && os < uint64_t{a->cols} * 4) return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: out row stride < row bytes");
+    if (reinterpret_cast<uintptr_t>(a->out) % 4 != 0 || os % 4 != 0 || reinterpret_cast<uintptr_t>(a->ids) % 4 != 0)
+        return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: out / ids are not 4-byte aligned");
+    if (a->type == HALO_CUDA_T_F32 && (reinterpret_cast<uintptr_t>(a->table) % 4 != 0 || ts % 4 != 0))
+        return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: operand table is not 4-byte aligned");
+    if (a->ids == nullptr && a->n_ids > a->n_rows) return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: %u rows requested from a table of %u", a->n_ids, a->n_rows);
+    const uint64_t t_ext = a->n_rows == 0 ? 0 : (uint64_t{a->n_rows} - 1) * ts + rb;
+    const uint64_t o_ext = (uint64_t{a->n_ids} - 1) * os + uint64_t{a->cols} * 4;
+    if (ranges_overlap(a->out, o_ext, a->table, t_ext)) return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: output out overlaps operand table");
+    if (a->ids != nullptr && ranges_overlap(a->out, o_ext, a->ids, uint64_t{a->n_ids} * 4))
+        return fail(HALO_CUDA_E_KERNEL, "GET_ROWS: output out overlaps operand ids");
+    return launch_get_rows(*a, rb, ts, os, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,82 @@
+// Internal declarations shared by the translation units of libhalo_cuda.so.  Not part of the ABI.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <vector>
+
+#include "halo_cuda.h"
+
+namespace halo_cuda {
+
+/// Records the calling thread's failure message and returns `status` (for `return fail(...)`).
+int fail(int status, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define HC_CUDA(expr)                                                                                     \
+    do {                                                                                                  \
+        cudaError_t e_ = (expr);                                                                          \
+        if (e_ != cudaSuccess)                                                                            \
+            return ::halo_cuda::fail(e_ == cudaErrorMemoryAllocation ? HALO_CUDA_E_MEMORY : HALO_CUDA_E_BACKEND, \
+                                     "%s: %s", #expr, cudaGetErrorString(e_));                            \
+    } while (0)
+
+struct TypeInfo {
+    uint32_t block_elems, block_bytes;
+};
+/// Block geometry of a supported weight type (src/tensor/dtype.cpp:19-51); false for any other id.
+bool type_info(uint32_t wtype, TypeInfo* out);
+
+struct PlanEntry {
+    uint32_t wtype, rows, cols, n_vec_lo, n_vec_hi, variant_id;
+};
+
+}  // namespace halo_cuda
+
+struct HaloCudaCtx {
+    int device = 0;
+    cudaDeviceProp prop{};
+    bool lost = false;
+    // Scratch for kernels that need global memory beyond their operands (activation staging, split-K
+    // partials).  Grown on demand, reused in stream order; one thread drives a context.
+    // Slot 0 serves the matmul kernels, slot 1 the LM head (its logits and argmax partials live across a matmul).
+    void* workspace[2] = {nullptr, nullptr};
+    uint64_t workspace_bytes[2] = {0, 0};
+    std::vector<halo_cuda::PlanEntry> plan;
+};
+
+namespace halo_cuda {
+
+/// Makes ctx's device current; E_API for a null ctx, E_DEVICE once the context is lost.
+int enter(HaloCudaCtx* ctx);
+/// Returns ctx scratch of at least `bytes` (grows with cudaMalloc; earlier contents are dropped).
+int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out);
+
+/// A validated gemv: strides resolved to bytes, geometry checked.
+struct GemvCall {
+    uint32_t wtype, rows, cols, n_vec, flags;
+    const uint8_t* w;
+    const float* x;
+    float* y;
+    uint64_t w_stride, x_stride, y_stride;  // bytes
+    uint64_t row_bytes;
+};
+int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* out);
+uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested);
+
+// kernel launchers (one per translation unit); each returns a status
+int launch_gemv_exact8(const GemvCall& c, cudaStream_t s);
+int launch_gemv_warp_f32(const GemvCall& c, cudaStream_t s);
+bool gemv_warp_f32_supports(const GemvCall& c);
+int launch_gemv_mma(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+bool gemv_mma_supports(const GemvCall& c);
+int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s);
+bool gemm_tcgen05_supports(const GemvCall& c);
+int launch_get_rows(const HaloCudaGetRows& a, uint64_t row_bytes, uint64_t table_stride, uint64_t out_stride, cudaStream_t s);
+int launch_argmax(const float* logits, uint64_t stride_elems, uint32_t n, uint32_t n_vec, uint32_t valid, uint32_t row_offset,
+                  uint32_t* result, int32_t* ids, void* scratch, cudaStream_t s);
+uint64_t argmax_scratch_bytes(uint32_t n, uint32_t n_vec);
+
+}  // namespace halo_cuda

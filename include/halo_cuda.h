@@ -1,0 +1,185 @@
+/*
+ * halo_cuda.h -- C ABI of the B200 (sm_100a) backend for HALO's quantized weight matmul.
+ *
+ * This is the boundary a `backends/cuda` adapter binds: plain pointers and sizes, no C++ types,
+ * no exceptions.  Every entry point returns 0 on success or a negative status; the statuses map
+ * one to one onto halo::ErrorCode (include/halo/core/error.h:15-26 of the reference) as
+ * status = -(1 + code), so the adapter can rethrow the error class the CPU backend would throw.
+ * halo_cuda_last_error() gives the message of the calling thread's last failure.
+ *
+ * All validation happens on the host before anything is enqueued (the contract of
+ * include/halo/backend/backend.h:7-9): a call that returns non-zero has launched nothing and
+ * written nothing.  Work is enqueued on the given stream and runs in stream order; results are
+ * readable after halo_cuda_stream_sync().  A context and its streams are driven by one thread.
+ *
+ * There is no CPU fallback anywhere behind this header: with no usable device every call fails.
+ */
+#ifndef HALO_CUDA_H
+#define HALO_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: -(1 + halo::ErrorCode) ------------------------------------------------ */
+#define HALO_CUDA_OK 0
+#define HALO_CUDA_E_MODEL (-1)       /* element count not a whole number of blocks */
+#define HALO_CUDA_E_MEMORY (-2)      /* allocation failure */
+#define HALO_CUDA_E_BACKEND (-3)     /* CUDA runtime failure, stream wait timeout */
+#define HALO_CUDA_E_KERNEL (-4)      /* shape / alias / range / alignment problem */
+#define HALO_CUDA_E_CONFIG (-5)      /* unknown kernel variant id */
+#define HALO_CUDA_E_API (-6)         /* malformed call (null struct, bad op id) */
+#define HALO_CUDA_E_DEVICE (-7)      /* no usable device */
+#define HALO_CUDA_E_UNSUPPORTED (-8) /* valid request this backend does not implement */
+
+/* ---- weight types: ggml ids, equal to halo::DType (include/halo/tensor/dtype.h:18-32) ------- */
+#define HALO_CUDA_T_F32 0
+#define HALO_CUDA_T_Q4_0 2
+#define HALO_CUDA_T_Q8_0 8
+#define HALO_CUDA_T_Q4_K 12
+#define HALO_CUDA_T_Q6_K 14
+
+/* ---- operator ids of the variant registry: halo::backend::OpId (backend.h:186-206) ---------- */
+#define HALO_CUDA_OP_GET_ROWS 0
+#define HALO_CUDA_OP_GEMV 3
+#define HALO_CUDA_OP_LM_HEAD 14
+
+/* ---- kernel variants of MATMUL (KernelChoice::variant_id, backend.h:173-176).  Ids are explicit
+ * and append-only; 0 selects by shape.  "family" groups variants whose rows are bitwise independent
+ * of the batch size among themselves (the batch-invariance contract of backend.h:300-304). -------- */
+#define HALO_CUDA_GEMV_DEFAULT 0
+#define HALO_CUDA_GEMV_EXACT8 1       /* bit-identical to the CPU backend (8-lane dot order) */
+#define HALO_CUDA_GEMV_WARP_F32 2     /* fp32 CUDA-core streaming kernel, warp-shuffle reduce */
+#define HALO_CUDA_GEMV_MMA_F16X2 3    /* tensor-core skinny kernel, x split into fp16 hi + lo */
+#define HALO_CUDA_GEMM_TCGEN05_F16 4  /* prefill: dequant to fp16 in shared memory + tcgen05 MMA */
+#define HALO_CUDA_GEMM_TCGEN05_BF16 5 /* same with bf16 operands */
+
+#define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
+
+typedef struct HaloCudaCtx HaloCudaCtx; /* one per device, opaque */
+typedef void* HaloCudaStream;           /* a cudaStream_t */
+typedef void* HaloCudaEvent;            /* a cudaEvent_t */
+
+typedef struct HaloCudaDeviceInfo {
+    char name[128];
+    char pci_id[16]; /* "vvvv:dddd" vendor:device, the ProfileKey gpu_device field */
+    char arch[16];   /* "sm_100a" */
+    int32_t cc_major, cc_minor, sm_count, l2_bytes;
+    int32_t driver_version, runtime_version; /* as cudaDriverGetVersion / cudaRuntimeGetVersion */
+    uint64_t total_bytes;
+    int32_t clock_khz, mem_clock_khz;
+} HaloCudaDeviceInfo;
+
+/* One registered kernel variant: halo::backend::VariantInfo (backend.h:210-216). */
+typedef struct HaloCudaVariant {
+    uint32_t id;
+    uint32_t op;
+    uint32_t family; /* 0 = fp32 exact order, 1 = fp32 reordered, 2 = fp16 tensor-core operands */
+    const char* name;
+} HaloCudaVariant;
+
+/* MATMUL / QUANT_GEMV: y[t][n] = sum_i x[t][i] * dequant(W)[n][i].
+ * Replaces Backend::gemv(Stream&, const GemvArgs&) (backend.h:283-314, 562) as implemented by
+ * CpuBackend::gemv (src/backend/cpu_backend.cpp:338-351).  All pointers are device pointers.
+ *   w: `rows` rows of row_bytes(wtype, cols) bytes, w_stride bytes apart (0 = dense), any alignment;
+ *   x: n_vec rows of cols fp32, x_stride bytes apart (0 = dense), 4-byte aligned;
+ *   y: n_vec rows of rows fp32, y_stride bytes apart (0 = dense), 4-byte aligned; must not overlap x or w.
+ * rows == 0 or n_vec == 0 is a no-op. */
+typedef struct HaloCudaGemv {
+    uint32_t wtype;
+    uint32_t variant_id;
+    const void* w;
+    uint64_t w_stride;
+    const float* x;
+    uint64_t x_stride;
+    float* y;
+    uint64_t y_stride;
+    uint32_t rows, cols, n_vec;
+    uint32_t flags;
+} HaloCudaGemv;
+
+/* LM head: gemv over the vocabulary + fused argmax.  Replaces Backend::lm_head(Stream&, const
+ * LmHeadArgs&) (backend.h:437-460) as implemented by CpuBackend::lm_head (cpu_backend.cpp:669-770).
+ *   gemv.y may be null (logits not wanted); result: n_vec triples {index u32, value bits, nan 0/1}
+ *   (12 bytes each, backend.h:430); ids (optional): n_vec int32 winners, 0 for a poisoned vector;
+ *   valid_rows: rows at or after it are left out of the argmax (0 = no clamp);
+ *   row_offset: added to every winning index (the vocabulary offset of a column-split shard). */
+typedef struct HaloCudaLmHead {
+    HaloCudaGemv gemv;
+    uint32_t* result;
+    int32_t* ids;
+    uint32_t valid_rows;
+    uint32_t row_offset;
+} HaloCudaLmHead;
+
+/* GET_ROWS-shaped exact dequantization: out[i] = dequant(table row ids[i]), or row i when ids is null.
+ * Replaces Backend::get_rows (backend.h:251-262; cpu_backend.cpp:291-311) for the four block formats;
+ * the unpacked values are bit-identical to tensor::dequantize_row (src/tensor/quant.cpp:430-435).
+ * An id outside [0, n_rows) sets bit 8 (kStatusBadIndex, backend.h:165) of *status (device word,
+ * optional) and writes nothing for that row. */
+typedef struct HaloCudaGetRows {
+    uint32_t type;
+    uint32_t variant_id;
+    const void* table;
+    uint64_t table_stride;
+    const int32_t* ids;
+    float* out;
+    uint64_t out_stride;
+    uint32_t n_rows, cols, n_ids;
+    uint32_t* status;
+} HaloCudaGetRows;
+
+/* ---- device, context, memory, streams ------------------------------------------------------- */
+int halo_cuda_device_count(int* count);
+int halo_cuda_ctx_create(int device, HaloCudaCtx** ctx);
+int halo_cuda_ctx_destroy(HaloCudaCtx* ctx);
+int halo_cuda_device_info(HaloCudaCtx* ctx, HaloCudaDeviceInfo* info);
+/* Device memory; zero != 0 clears it (Backend::allocate is zero-filled, backend.h:523). */
+int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int zero, void** ptr);
+int halo_cuda_free(HaloCudaCtx* ctx, void* ptr);
+int halo_cuda_stream_create(HaloCudaCtx* ctx, HaloCudaStream* stream);
+int halo_cuda_stream_destroy(HaloCudaCtx* ctx, HaloCudaStream stream);
+/* Stream::wait() (backend.h:497): blocks until the stream drains or timeout_ns passes (0 = no limit).
+ * A timeout returns HALO_CUDA_E_BACKEND and marks the context lost (Backend::lost(), backend.h:517-520). */
+int halo_cuda_stream_sync(HaloCudaCtx* ctx, HaloCudaStream stream, uint64_t timeout_ns);
+int halo_cuda_ctx_lost(HaloCudaCtx* ctx); /* 1 once a wait timed out or the device faulted, else 0 */
+/* Backend::upload / download / copy (backend.h:549-552, 476-481); src of an upload must stay valid until the sync. */
+int halo_cuda_memcpy_h2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream);
+int halo_cuda_memcpy_d2h_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream);
+int halo_cuda_memcpy_d2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream);
+int halo_cuda_memset_async(HaloCudaCtx* ctx, void* dst, int value, uint64_t bytes, HaloCudaStream stream);
+/* Pinned host staging memory for uploads and downloads. */
+int halo_cuda_host_alloc(HaloCudaCtx* ctx, uint64_t bytes, void** ptr);
+int halo_cuda_host_free(HaloCudaCtx* ctx, void* ptr);
+/* Device timing for the autotuner's Measurement.device_ns (src/autotune/tuner.cpp:133-138). */
+int halo_cuda_event_create(HaloCudaCtx* ctx, HaloCudaEvent* event);
+int halo_cuda_event_destroy(HaloCudaCtx* ctx, HaloCudaEvent event);
+int halo_cuda_event_record(HaloCudaCtx* ctx, HaloCudaEvent event, HaloCudaStream stream);
+int halo_cuda_event_elapsed_ns(HaloCudaCtx* ctx, HaloCudaEvent start, HaloCudaEvent stop, uint64_t* ns);
+
+/* ---- geometry, registry, errors ---------------------------------------------------------------- */
+/* tensor::row_bytes (src/tensor/quant.cpp:422-428): E_MODEL if cols is not whole blocks, E_UNSUPPORTED for other types. */
+int halo_cuda_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes);
+/* Backend::variants(op) (backend.h:556): writes up to cap entries, *count = number registered. */
+int halo_cuda_variants(uint32_t op, HaloCudaVariant* out, uint32_t cap, uint32_t* count);
+/* The variant id 0 resolves to for this call (what the shape heuristic, or an installed plan, picks). */
+int halo_cuda_gemv_resolve(HaloCudaCtx* ctx, const HaloCudaGemv* args, uint32_t* variant_id);
+/* Installs the autotuner's choice for one shape bucket: calls with variant_id 0, this wtype, rows, cols and
+ * n_vec in [n_vec_lo, n_vec_hi] run `variant_id` (the "KernelPlan" join of ADR-001 5.6). */
+int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec_lo, uint32_t n_vec_hi,
+                       uint32_t variant_id);
+int halo_cuda_plan_clear(HaloCudaCtx* ctx);
+size_t halo_cuda_last_error(char* buf, size_t len);
+
+/* ---- the operators ------------------------------------------------------------------------------ */
+int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);
+int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);
+int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaStream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HALO_CUDA_H */
