@@ -181,7 +181,7 @@ def run_ours(args) -> None:
     wbufs = [be.import_host_readonly(w.reshape(-1)) for _ in range(COPIES)]
     xb = be.import_host_readonly(x)
     ybufs = [be.allocate(N_ROWS * 4) for _ in range(COPIES)]
-    calls = [hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef.of(xb), hb.TensorRef.of(ybufs[i]), N_ROWS, K_COLS, 1, 0)
+    calls = [hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef.of(xb), hb.TensorRef.of(ybufs[i]), N_ROWS, K_COLS, 1, args.variant)
              for i in range(COPIES)]
     structs = [be._gemv_struct(a, "MATMUL", False) for a in calls]
     variant = be.resolve_variant(calls[0])
@@ -220,7 +220,8 @@ def run_ours(args) -> None:
             ms = float(t.item())
         return ms
 
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(n_warm):
         one_pass()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -242,13 +243,13 @@ def run_ours(args) -> None:
             lib.halo_cuda_memcpy_d2h_async(ctx, hy.value + i * N_ROWS * 4, g.y, N_ROWS * 4, st.handle)
         st.wait()
 
-    for _ in range(3):
+    for _ in range(0 if args.profile else 3):
         e2e_pass()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(1 if args.profile else args.steps):
         e2e_pass()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = (time.perf_counter() - t0) * (args.steps if args.profile else 1)
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -278,10 +279,10 @@ def run_ours(args) -> None:
         if world > 1:
             dist.destroy_process_group()
         return
-    cpu, _ = cpu_baseline(4, 3) if world == 1 or True else (None, 0)
+    cpu = None if args.profile else cpu_baseline(4, 3)[0]
     line = {
         "metric": "q4_k_mul_mat_weight_gbs_m1", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": n_warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1 per GPU, {COPIES} distinct weight copies per step",
                    "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
@@ -306,7 +307,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--copies", type=int, default=COPIES, help="distinct weight copies cycled per step")
+    ap.add_argument("--variant", type=int, default=0, help="kernel variant id (0 = what the backend selects)")
+    ap.add_argument("--profile", action="store_true", help="small run for ncu: no CPU baseline, no e2e leg, warm-up as given")
     args = ap.parse_args()
+    global COPIES
+    COPIES = args.copies
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -257,7 +257,12 @@ int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int zero, void** ptr) {
         return fail(HALO_CUDA_E_MEMORY, "cannot allocate %llu bytes on device %d: %s", (unsigned long long)bytes, ctx->device,
                     cudaGetErrorString(e));
     }
-    if (zero != 0 && bytes != 0) HC_CUDA(cudaMemset(*ptr, 0, bytes));
+    if (zero != 0 && bytes != 0) {
+        // The clear runs on the legacy default stream, which the non-blocking streams of this library do not wait
+        // for: finish it here so that no later upload can be overtaken by it.
+        HC_CUDA(cudaMemset(*ptr, 0, bytes));
+        HC_CUDA(cudaStreamSynchronize(nullptr));
+    }
     return 0;
 }
 

@@ -107,14 +107,23 @@ def test_exact_variant_f32_weights_with_tail(hz, checker):
 
 # ---- the fast fp32 variant: bounded, batch-invariant, and not vacuous ------------------------------------------
 
-FAST = [capi.GEMV_WARP_F32]
+FAST = [capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2]
+MMA_TYPES = (synth.Q4_K,)
+
+
+def _skip_unless_supported(variant, t):
+    if variant == capi.GEMV_MMA_F16X2 and t not in MMA_TYPES:
+        pytest.skip("gemv_mma_f16x2 takes Q4_K weights")
 
 
 @pytest.mark.parametrize("variant", FAST)
 @pytest.mark.parametrize("t,n,k,m", [(synth.Q4_K, 17408, 5120, 1), (synth.Q6_K, 5120, 17408, 4), (synth.Q8_0, 5120, 17408, 8),
-                                     (synth.Q4_0, 2048, 5120, 16), (synth.Q4_K, 37, 512, 3), (synth.Q6_K, 13, 5120, 17)])
+                                     (synth.Q4_0, 2048, 5120, 16), (synth.Q4_K, 37, 512, 3), (synth.Q6_K, 13, 5120, 17),
+                                     (synth.Q4_K, 5120, 17408, 4), (synth.Q4_K, 1000, 5120, 16), (synth.Q4_K, 130, 256, 21),
+                                     (synth.Q4_K, 5120, 17408, 13)])
 def test_fast_variant_within_summation_bound(hz, checker, variant, t, n, k, m):
     from gpu_util import summation_bound
+    _skip_unless_supported(variant, t)
     w = synth.quant_weights(t, n, k, 0, 1)
     x = synth.activations(m, k, 0, 2)
     y = hz.gemv(t, w, x, n, k, variant=variant, y_guard=8)
@@ -134,6 +143,7 @@ def test_fast_variant_within_summation_bound(hz, checker, variant, t, n, k, m):
 @pytest.mark.parametrize("t", TYPES)
 def test_fast_variant_rows_do_not_depend_on_batch_size(hz, variant, t):
     # every row of a batch is bitwise its own n_vec == 1 gemv (include/halo/backend/backend.h:300-304)
+    _skip_unless_supported(variant, t)
     n, k = 96, 2560
     w = synth.quant_weights(t, n, k, 3, 1)
     x = synth.activations(16, k, 3, 2)
@@ -141,6 +151,34 @@ def test_fast_variant_rows_do_not_depend_on_batch_size(hz, variant, t):
     for m in (1, 2, 3, 4, 5, 8, 11):
         ym = hz.gemv(t, w, x[:m], n, k, variant=variant)
         assert np.array_equal(bits(ym), bits(y16[:m])), f"batch of {m}"
+
+
+def test_mma_variant_batch_invariance_across_k_chunking(hz):
+    # K = 17408 makes the shared-memory staging of x chunk differently for 1, 4 and 16 rows; the bits must not move
+    n, k = 48, 17408
+    w = synth.quant_weights(synth.Q4_K, n, k, 6, 1)
+    x = synth.activations(20, k, 6, 2)
+    y20 = hz.gemv(synth.Q4_K, w, x, n, k, variant=capi.GEMV_MMA_F16X2)
+    for m in (1, 4, 7, 16):
+        ym = hz.gemv(synth.Q4_K, w, x[:m], n, k, variant=capi.GEMV_MMA_F16X2)
+        assert np.array_equal(bits(ym), bits(y20[:m])), f"batch of {m}"
+
+
+def test_mma_variant_handles_extreme_activation_ranges(hz, checker):
+    # per-row power-of-two scaling keeps tiny and huge activations inside fp16; a NaN poisons only its own row
+    n, k = 64, 1024
+    w = synth.quant_weights(synth.Q4_K, n, k, 7, 1)
+    x = synth.activations(4, k, 7, 2)
+    x[0] *= 1e-6
+    x[1] *= 3e4
+    x[2, 5] = np.nan
+    x[3] = 0.0
+    y = hz.gemv(synth.Q4_K, w, x, n, k, variant=capi.GEMV_MMA_F16X2)
+    ref = checker.gemv(synth.Q4_K, w, x, n, k)
+    for r in (0, 1):
+        assert np.max(np.abs(y[r] - ref[r])) <= 1e-4 * np.max(np.abs(ref[r]))
+    assert np.all(np.isnan(y[2])) and not np.any(np.isnan(y[[0, 1, 3]]))
+    assert not y[3].any()
 
 
 def test_default_variant_is_registered_and_runs(hz, checker):
