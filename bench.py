@@ -307,12 +307,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--copies", type=int, default=COPIES, help="distinct weight copies cycled per step")
+    ap.add_argument("--copies", type=int, default=16, help="distinct weight copies cycled per step")
     ap.add_argument("--variant", type=int, default=0, help="kernel variant id (0 = what the backend selects)")
     ap.add_argument("--profile", action="store_true", help="small run for ncu: no CPU baseline, no e2e leg, warm-up as given")
     args = ap.parse_args()
-    global COPIES
-    COPIES = args.copies
+    globals()["COPIES"] = args.copies
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -212,6 +212,14 @@ int halo_cuda_ctx_create(int device, HaloCudaCtx** out) {
         delete ctx;
         return fail(HALO_CUDA_E_DEVICE, "device %d is sm_%d%d; this library holds sm_100a code only", device, major, minor);
     }
+    void* host_word = nullptr;
+    if (cudaHostAlloc(&host_word, sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess) {
+        ctx->error_word_host = static_cast<uint32_t*>(host_word);
+        *ctx->error_word_host = 0;
+        void* dev_word = nullptr;
+        if (cudaHostGetDevicePointer(&dev_word, host_word, 0) == cudaSuccess) ctx->error_word_dev = static_cast<uint32_t*>(dev_word);
+    }
+    cudaGetLastError();
     *out = ctx;
     return 0;
 }
@@ -221,6 +229,7 @@ int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
     if (cudaSetDevice(ctx->device) == cudaSuccess) {
         for (void* p : ctx->workspace)
             if (p != nullptr) cudaFree(p);
+        if (ctx->error_word_host != nullptr) cudaFreeHost(ctx->error_word_host);
     }
     delete ctx;
     return 0;
@@ -331,6 +340,11 @@ int halo_cuda_stream_sync(HaloCudaCtx* ctx, HaloCudaStream stream, uint64_t time
     if (e != cudaSuccess) {
         ctx->lost = true;
         return fail(HALO_CUDA_E_BACKEND, "stream wait failed on device %d: %s", ctx->device, cudaGetErrorString(e));
+    }
+    if (ctx->error_word_host != nullptr && *static_cast<volatile uint32_t*>(ctx->error_word_host) != 0) {
+        ctx->lost = true;
+        return fail(HALO_CUDA_E_BACKEND, "a kernel on device %d gave up a bounded wait (status word 0x%x); device marked lost", ctx->device,
+                    *ctx->error_word_host);
     }
     return 0;
 }

@@ -45,6 +45,10 @@ struct HaloCudaCtx {
     void* workspace[2] = {nullptr, nullptr};
     uint64_t workspace_bytes[2] = {0, 0};
     std::vector<halo_cuda::PlanEntry> plan;
+    // One word of mapped pinned host memory that kernels OR error bits into (bit 0: a bounded device-side wait
+    // expired).  The host reads it after every stream wait; a set bit marks the context lost.
+    uint32_t* error_word_host = nullptr;
+    uint32_t* error_word_dev = nullptr;
 };
 
 namespace halo_cuda {
