@@ -312,6 +312,16 @@ class CudaBackend:
         h.valid_rows, h.row_offset = a.valid_rows, a.row_offset
         _check(self.lib.halo_cuda_lm_head(self.ctx, C.byref(h), s.handle))
 
+    def lm_head_noalloc(self, s: Stream, a: LmHeadArgs) -> None:
+        """lm_head for hosts that may not allocate device memory mid-run: same operands, logits buffer required,
+        argmax partials in the library's fixed 64 KiB scratch (halo_cuda_lm_head_noalloc)."""
+        h = capi.LmHead()
+        h.gemv = self._gemv_struct(a.gemv, "LM_HEAD", False)
+        h.result = self._resolve(a.result, a.gemv.n_vec * ARGMAX_RESULT_BYTES, "result", "LM_HEAD", write=True) or None
+        h.ids = self._resolve(a.ids, a.gemv.n_vec * 4, "ids", "LM_HEAD", write=True) or None
+        h.valid_rows, h.row_offset = a.valid_rows, a.row_offset
+        _check(self.lib.halo_cuda_lm_head_noalloc(self.ctx, C.byref(h), s.handle))
+
     def get_rows(self, s: Stream, a: GetRowsArgs, status: Buffer | None = None) -> None:
         rb = C.c_uint64()
         _check(self.lib.halo_cuda_row_bytes(a.type, a.cols, C.byref(rb)))

@@ -79,6 +79,7 @@ SYMBOLS = {
     "halo_cuda_gemv": (C.c_int, [_P, C.POINTER(Gemv), _P]),
     "halo_cuda_lm_head": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_get_rows": (C.c_int, [_P, C.POINTER(GetRows), _P]),
+    "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),
 }
 
 _lib = None

@@ -179,6 +179,16 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
 int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);
 int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaStream stream);
 
+/* The LM head for callers that cannot allocate device memory while they run (a serving loop whose buffers were all
+ * sized at start-up, an embedder with a fixed memory budget).  No counterpart in the reference: its backends
+ * allocate their scratch freely.  Same arguments and results as halo_cuda_lm_head, with three differences: the
+ * logits buffer gemv.y is required; the argmax partials live in a fixed 64 KiB array inside the library's device
+ * image, so ceil(rows / 8192) * n_vec must not exceed 4096 (E_UNSUPPORTED beyond that); and the matmul runs only
+ * variants 0-3, which need no scratch of their own.  The array is shared by all calls on a GPU: calls that overlap
+ * on the device race on it, so keep them on one stream.  The first call on each device resolves the array's
+ * address and should be made before any stream capture begins.  It calls no cudaMalloc / cudaFree. */
+int halo_cuda_lm_head_noalloc(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);
+
 #ifdef __cplusplus
 }
 #endif
