@@ -16,8 +16,9 @@ constexpr HaloCudaVariant kGemvVariants[] = {
     {HALO_CUDA_GEMV_EXACT8, HALO_CUDA_OP_GEMV, 0, "gemv_exact8"},
     {HALO_CUDA_GEMV_WARP_F32, HALO_CUDA_OP_GEMV, 1, "gemv_warp_f32"},
     {HALO_CUDA_GEMV_MMA_F16X2, HALO_CUDA_OP_GEMV, 2, "gemv_mma_f16x2"},
-    {HALO_CUDA_GEMM_TCGEN05_F16, HALO_CUDA_OP_GEMV, 2, "gemm_tcgen05_f16"},
-    {HALO_CUDA_GEMM_TCGEN05_BF16, HALO_CUDA_OP_GEMV, 2, "gemm_tcgen05_bf16"},
+    {HALO_CUDA_GEMM_TCGEN05_F16, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_f16"},
+    {HALO_CUDA_GEMM_TCGEN05_BF16, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_bf16"},
+    {HALO_CUDA_GEMV_MMA_M1, HALO_CUDA_OP_GEMV, 3, "gemv_mma_m1"},
 };
 constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
 constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
@@ -139,7 +140,7 @@ uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t req
             if (p.wtype != c.wtype || p.rows != c.rows || p.cols != c.cols || c.n_vec < p.n_vec_lo || c.n_vec > p.n_vec_hi) continue;
             const bool is_gemm = p.variant_id == HALO_CUDA_GEMM_TCGEN05_F16 || p.variant_id == HALO_CUDA_GEMM_TCGEN05_BF16;
             if (is_gemm && (!gemm_ok || !gemm_tcgen05_supports(c))) continue;
-            if (p.variant_id == HALO_CUDA_GEMV_MMA_F16X2 && !gemv_mma_supports(c)) continue;
+            if ((p.variant_id == HALO_CUDA_GEMV_MMA_F16X2 || p.variant_id == HALO_CUDA_GEMV_MMA_M1) && !gemv_mma_supports(c)) continue;
             if (p.variant_id == HALO_CUDA_GEMV_WARP_F32 && !gemv_warp_f32_supports(c)) continue;
             return p.variant_id;
         }
@@ -165,6 +166,10 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
             if (!gemv_mma_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_f16x2 needs Q4_K weights in dense 16-byte-aligned rows");
             return launch_gemv_mma(ctx, c, s);
+        case HALO_CUDA_GEMV_MMA_M1:
+            if (!gemv_mma_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_m1 needs Q4_K weights in dense 16-byte-aligned rows");
+            return launch_gemv_mma_m1(ctx, c, s);
         case HALO_CUDA_GEMM_TCGEN05_F16:
         case HALO_CUDA_GEMM_TCGEN05_BF16:
             if (!gemm_tcgen05_supports(c))
@@ -447,7 +452,7 @@ int halo_cuda_variants(uint32_t op, HaloCudaVariant* out, uint32_t cap, uint32_t
 int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec_lo, uint32_t n_vec_hi,
                        uint32_t variant_id) {
     if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
-    if (variant_id == 0 || variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+    if (variant_id == 0 || variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
         return fail(HALO_CUDA_E_CONFIG, "plan: unknown kernel variant id %u", variant_id);
     if (n_vec_lo > n_vec_hi) return fail(HALO_CUDA_E_API, "plan: empty n_vec range");
     for (PlanEntry& p : ctx->plan) {
@@ -483,7 +488,7 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
     if (int rc = enter(ctx)) return rc;
     GemvCall c{};
     if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
-    if (args->variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+    if (args->variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
         return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
     if (c.rows == 0 || c.n_vec == 0) return 0;
     return run_gemv(ctx, c, args->variant_id, static_cast<cudaStream_t>(stream));
@@ -494,7 +499,7 @@ int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* a, HaloCudaStream 
     if (a == nullptr) return fail(HALO_CUDA_E_API, "LM_HEAD: null argument struct");
     GemvCall c{};
     if (int rc = validate_gemv(&a->gemv, "LM_HEAD", true, &c)) return rc;
-    if (a->gemv.variant_id > HALO_CUDA_GEMM_TCGEN05_BF16)
+    if (a->gemv.variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
         return fail(HALO_CUDA_E_CONFIG, "LM_HEAD: unknown kernel variant id %u on the cuda backend", a->gemv.variant_id);
     if (c.n_vec == 0) return 0;
     if (a->result == nullptr) return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: operand result is empty");

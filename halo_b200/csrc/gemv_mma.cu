@@ -25,7 +25,10 @@
 // per sub-block.  Every mbarrier wait is bounded: on expiry the warp raises the context's error word and leaves.
 //
 // Roofline: HBM.  Algorithmic bytes = rows * row_bytes + 4 * n_vec * cols + 4 * n_vec * rows.
+#include <cuda.h>
 #include <cuda_fp16.h>
+
+#include <cstring>
 
 #include "internal.h"
 
@@ -35,6 +38,10 @@ namespace {
 
 constexpr int kRowBlocks = 8;         // 16-row blocks per CTA: a CTA covers 128 W rows
 constexpr uint32_t kSmemBudget = 220 * 1024;
+#ifndef HALO_MMA_CHAINS
+#define HALO_MMA_CHAINS 2
+#endif
+constexpr int kChains = HALO_MMA_CHAINS;  // part of a row's arithmetic: the same for every token count
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -82,12 +89,14 @@ __device__ __forceinline__ void split4(float4 v, uint2& hi, uint2& lo) {
 }
 
 // ---- shared-memory weight ring -------------------------------------------------------------------------------------
-// Each warp streams its own rows: per pipeline stage, 16 bulk copies (cp.async.bulk, one 144-byte super-block per W
-// row) land in a 16 x 160-byte slot and complete on that stage's mbarrier.  The 16-byte row padding makes the
-// fragment reads below conflict-free.  Nothing but the owning warp touches a slot, so the only synchronisation is
-// the mbarrier (data arrived) and program order (slot consumed before it is refilled).
-constexpr uint32_t kSlotRow = 160, kSlotBytes = 16 * kSlotRow, kStageTx = 16 * 144;
-constexpr uint32_t kWaitSpins = 1u << 20;  // try_wait polls (each blocks for a short hardware-defined time) before a stage is declared lost
+// Each warp streams its own rows: per pipeline stage one TMA tile copy (cp.async.bulk.tensor.2d over a tensor map of
+// the weight matrix as rows of bytes) brings the 144-byte super-block of its 16 W rows into a 16 x 160-byte slot and
+// completes on that stage's mbarrier.  The box is 160 bytes wide: the 16 extra bytes (the next block's header, or
+// zero fill past the row end) only pad the slot so that the fragment reads below are bank-conflict-free.  Rows past
+// the end of the matrix are zero-filled by the copy engine.  Nothing but the owning warp touches a slot, so the
+// only synchronisation is the mbarrier (data arrived) and program order (slot consumed before it is refilled).
+constexpr uint32_t kSlotRow = 160, kSlotBytes = 16 * kSlotRow, kStageTx = kSlotBytes;
+constexpr uint32_t kWaitSpins = 1u << 14;  // try_wait polls (each blocks for a short hardware-defined time) before a stage is declared lost
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -112,23 +121,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
+/// One tile of the tensor map: bytes [x, x + 160) of rows [y, y + 16).  x must be a multiple of 16.
+__device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
                  : "memory");
 }
 
 // Shared-memory layout (byte offsets from the dynamic base), for `ncols` = 2 * tokens columns:
 //   [0, 16) unused | scales | partial maxima | mbarriers | weight ring |
 //   xs:  [sub-block][column][64 B] fp16 x in slot order    sx: [super-block][column][16 B] sub-block sums / 32
-constexpr uint32_t kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 256, kOffRing = 1024;
+constexpr uint32_t kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
+constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eight bytes per warp and stage (<= 6 stages)
 
 // NTOK: x rows of this launch (1..16), i.e. 2 * NTOK B columns in G = ceil(NTOK / 4) MMA column groups.
 // KS: warps sharing one 16-row block; warp ks takes the super-blocks sb = ks (mod KS), a split that depends on
 // nothing but KS, and the KS partial sums are added in ks order.  NS: ring stages per warp.
 template <int NTOK, int KS, int NS>
 __global__ void __launch_bounds__(kRowBlocks * KS * 32, 1)
-gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const float* __restrict__ x, uint64_t x_stride,
+gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, uint64_t x_stride,
                     float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t chunk_sb,
                     uint32_t* __restrict__ error_word) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -136,6 +147,7 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
     constexpr int G = (NTOK + 3) / 4;
     constexpr uint32_t kThreads = kRowBlocks * KS * 32;
     constexpr uint32_t kWarps = kRowBlocks * KS;
+    static_assert(kWarps <= kMaxWarps && NS <= 6, "shared-memory header layout");
     constexpr uint32_t kOffData = kOffRing + kWarps * NS * kSlotBytes;
     constexpr uint32_t kCols = 2 * NTOK;             // B columns that carry a token
     constexpr uint32_t kSubStride = kCols * 64u;     // xs bytes per 32-element sub-block
@@ -151,8 +163,8 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
     const uint32_t n_items = active && nb > ks ? (nb - ks + KS - 1) / KS : 0;  // super-blocks ks, ks+KS, ...
     const uint32_t bars = smem_base + kOffBars + warp * NS * 8u;
     const uint32_t ring = smem_base + kOffRing + warp * NS * kSlotBytes;
-    // lanes 0..15 each own one W row of the block (clamped: rows past the end re-read the last row and are not stored)
-    const uint8_t* next_src = w + uint64_t{min(rb * 16u + (lane & 15u), rows - 1)} * w_stride + ks * 144u;
+    uint32_t next_x = ks * 144u;  // byte column of the next super-block to fetch
+    asm volatile("griddepcontrol.launch_dependents;");  // the next kernel in the stream may start filling its ring
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < NS; ++s) mbar_init(bars + s * 8u, 1);
@@ -161,14 +173,18 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
     __syncwarp();
     uint32_t fill_slot = 0, issued = 0;
     auto refill = [&]() {  // next super-block of this warp -> slot fill_slot
-        if (lane == 0) mbar_expect_tx(bars + fill_slot * 8u, kStageTx);
-        __syncwarp();
-        if (lane < 16) bulk_g2s(ring + fill_slot * kSlotBytes + lane * kSlotRow, next_src, 144u, bars + fill_slot * 8u);
-        next_src += KS * 144u;
+        if (lane == 0) {
+            mbar_expect_tx(bars + fill_slot * 8u, kStageTx);
+            tma_tile_g2s(ring + fill_slot * kSlotBytes, &wmap, next_x, rb * 16u, bars + fill_slot * 8u);
+        }
+        next_x += KS * 144u;
         fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
         ++issued;
     };
     for (uint32_t it = 0; it < NS && it < n_items; ++it) refill();
+    // Programmatic dependent launch: the weights never depend on the kernel before this one, so the ring is filled
+    // first; only now wait for that kernel's results (x may be one of them, and y may still be read by it).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- per-token power-of-two scale from the row's largest magnitude ------------------------------------------------
     float* s_scale = reinterpret_cast<float*>(smem + kOffScale);
@@ -280,7 +296,9 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
                 dmn[r] = __high2float(dd) * (16777216.0f * 32.0f);  // dmin * 2^24 * 32: and the /32 of the sums
             }
 
-            float cq[G][4], cm[G][4];
+            // kChains independent accumulator chains per column group keep the tensor pipe from waiting on its own
+            // result; MMA n of every 64-element group goes to chain n % kChains, and the chains are added in a fixed order.
+            float cq[G][kChains][4], cm[G][4];
             const uint8_t* xb[G];
 #pragma unroll
             for (int gi = 0; gi < G; ++gi) xb[gi] = xs_ptr[gi] + i * (8u * kSubStride);
@@ -317,11 +335,14 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
                 for (int gi = 0; gi < G; ++gi) {
                     const uint4 bl = *reinterpret_cast<const uint4*>(xb[gi] + (2 * j) * kSubStride);
                     const uint4 bh = *reinterpret_cast<const uint4*>(xb[gi] + (2 * j + 1) * kSubStride);
-                    if (j == 0) mma16816_first(cq[gi], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
-                    else mma16816(cq[gi], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
-                    mma16816(cq[gi], aLo[0][2], aLo[1][2], aLo[0][3], aLo[1][3], bl.z, bl.w);
-                    mma16816(cq[gi], aHi[0][0], aHi[1][0], aHi[0][1], aHi[1][1], bh.x, bh.y);
-                    mma16816(cq[gi], aHi[0][2], aHi[1][2], aHi[0][3], aHi[1][3], bh.z, bh.w);
+                    if (j == 0) mma16816_first(cq[gi][0], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
+                    else mma16816(cq[gi][0], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
+                    if (j == 0 && kChains > 1) mma16816_first(cq[gi][1 % kChains], aLo[0][2], aLo[1][2], aLo[0][3], aLo[1][3], bl.z, bl.w);
+                    else mma16816(cq[gi][1 % kChains], aLo[0][2], aLo[1][2], aLo[0][3], aLo[1][3], bl.z, bl.w);
+                    if (j == 0 && kChains > 2) mma16816_first(cq[gi][2 % kChains], aHi[0][0], aHi[1][0], aHi[0][1], aHi[1][1], bh.x, bh.y);
+                    else mma16816(cq[gi][2 % kChains], aHi[0][0], aHi[1][0], aHi[0][1], aHi[1][1], bh.x, bh.y);
+                    if (j == 0 && kChains > 3) mma16816_first(cq[gi][3 % kChains], aHi[0][2], aHi[1][2], aHi[0][3], aHi[1][3], bh.z, bh.w);
+                    else mma16816(cq[gi][3 % kChains], aHi[0][2], aHi[1][2], aHi[0][3], aHi[1][3], bh.z, bh.w);
                 }
             }
             // every byte of the slot has been consumed by the instructions above: hand it back to the copy engine
@@ -334,9 +355,16 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
             for (int gi = 0; gi < G; ++gi) {
                 const uint32_t bs = *reinterpret_cast<const uint32_t*>(sx_ptr[gi] + i * kSbStride);
                 mma16816_first(cm[gi], mpair[0], mpair[1], 0u, 0u, bs, 0u);
-                yacc[gi][0] = fmaf(dq[0], cq[gi][0] + cq[gi][1], yacc[gi][0]);
+                float cs[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if constexpr (kChains == 1) cs[k] = cq[gi][0][k];
+                    else if constexpr (kChains == 2) cs[k] = cq[gi][0][k] + cq[gi][1][k];
+                    else cs[k] = (cq[gi][0][k] + cq[gi][1][k]) + (cq[gi][2][k] + cq[gi][3][k]);
+                }
+                yacc[gi][0] = fmaf(dq[0], cs[0] + cs[1], yacc[gi][0]);
                 yacc[gi][0] = fmaf(-dmn[0], cm[gi][0] + cm[gi][1], yacc[gi][0]);
-                yacc[gi][1] = fmaf(dq[1], cq[gi][2] + cq[gi][3], yacc[gi][1]);
+                yacc[gi][1] = fmaf(dq[1], cs[2] + cs[3], yacc[gi][1]);
                 yacc[gi][1] = fmaf(-dmn[1], cm[gi][2] + cm[gi][3], yacc[gi][1]);
             }
         }
@@ -386,6 +414,222 @@ gemv_mma_q4k_kernel(const uint8_t* __restrict__ w, uint64_t w_stride, const floa
     }
 }
 
+// ---- the single-row specialist (variant gemv_mma_m1) -----------------------------------------------------------------
+// With one x row the eight MMA columns are free, and they are spent on the eight sub-blocks of a super-block: for
+// the MMAs of sub-block s only column s of B carries x (every other column reads zeros), so accumulator column s
+// ends up holding sum_{k in s} q_k x_k.  The weight side then needs NO multiply at all -- the masked nibble pair goes
+// straight into the A fragment -- and the 6-bit scales are applied to 2 accumulator columns per thread in fp32
+// (thread t of a quad owns sub-blocks 2t and 2t+1).  High-nibble sub-blocks carry 16 q, so their x is staged
+// pre-divided by 16 (exact).  x is again fp16 hi + lo (two MMAs per k-step).  The min term uses the exact fp32
+// sub-block sums of x.  A row's arithmetic differs from gemv_mma_f16x2, so the two are different numerics families.
+template <int KS, int NS>
+__global__ void __launch_bounds__(kRowBlocks * KS * 32, 1)
+gemv_mma_q4k_m1_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, float* __restrict__ y, uint32_t rows,
+                       uint32_t nb, uint32_t chunk_sb, uint32_t* __restrict__ error_word) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    constexpr uint32_t kThreads = kRowBlocks * KS * 32;
+    constexpr uint32_t kWarps = kRowBlocks * KS;
+    static_assert(kWarps <= kMaxWarps && NS <= 6, "shared-memory header layout");
+    constexpr uint32_t kOffData = kOffRing + kWarps * NS * kSlotBytes;  // its first 128 bytes stay zero
+    constexpr uint32_t kOffXs = kOffData + 128;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t rbl = warp % kRowBlocks, ks = warp / kRowBlocks;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t cols = nb * 256u;
+
+    const uint32_t rb = blockIdx.x * kRowBlocks + rbl;
+    const bool active = rb * 16u < rows;
+    const uint32_t n_items = active && nb > ks ? (nb - ks + KS - 1) / KS : 0;
+    const uint32_t bars = smem_base + kOffBars + warp * NS * 8u;
+    const uint32_t ring = smem_base + kOffRing + warp * NS * kSlotBytes;
+    uint32_t next_x = ks * 144u;
+    asm volatile("griddepcontrol.launch_dependents;");  // the next kernel in the stream may start filling its ring
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) mbar_init(bars + s * 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    uint32_t fill_slot = 0, issued = 0;
+    auto refill = [&]() {
+        if (lane == 0) {
+            mbar_expect_tx(bars + fill_slot * 8u, kStageTx);
+            tma_tile_g2s(ring + fill_slot * kSlotBytes, &wmap, next_x, rb * 16u, bars + fill_slot * 8u);
+        }
+        next_x += KS * 144u;
+        fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
+        ++issued;
+    };
+    for (uint32_t it = 0; it < NS && it < n_items; ++it) refill();
+    // Programmatic dependent launch: the weights never depend on the kernel before this one, so the ring is filled
+    // first; only now wait for that kernel's results (x may be one of them, and y may still be read by it).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- power-of-two scale from the largest magnitude of x -------------------------------------------------------------
+    float* s_scale = reinterpret_cast<float*>(smem + kOffScale);
+    float* s_inv = reinterpret_cast<float*>(smem + kOffInv);
+    float* s_red = reinterpret_cast<float*>(smem + kOffRed);
+    if (tid < 32) reinterpret_cast<uint32_t*>(smem + kOffData)[tid] = 0u;
+    {
+        const float4* xr = reinterpret_cast<const float4*>(x);
+        float m = 0.0f;
+        for (uint32_t i = tid; i < cols / 4; i += kThreads) {
+            const float4 v = xr[i];
+            m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+        if (lane == 0) s_red[warp] = m;
+        __syncthreads();
+        if (tid == 0) {
+            float a = 0.0f;
+            for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
+            int e = static_cast<int>((__float_as_uint(a) >> 23) & 0xFFu) - 127;
+            int se = (a > 0.0f && e < 128) ? 13 - e : 0;
+            se = max(-100, min(100, se));
+            s_scale[0] = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
+            s_inv[0] = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
+        }
+        __syncthreads();
+    }
+
+    // ---- per-lane B addressing: this lane feeds column g, which is live only for sub-block g of each super-block; for
+    // the other seven sub-blocks it reads the 16 zero bytes (step 0) ---------------------------------------------------
+    uint32_t b_base[8], b_step[8];
+#pragma unroll
+    for (int sblk = 0; sblk < 8; ++sblk) {
+        const bool mine = g == static_cast<uint32_t>(sblk);
+        b_base[sblk] = mine ? smem_base + kOffXs + sblk * 128u + t * 16u : smem_base + kOffData;
+        b_step[sblk] = mine ? 8u * 128u : 0u;
+    }
+    const uint32_t sx_base = smem_base + kOffXs + chunk_sb * 8u * 128u + t * 8u;  // fp32 sums of sub-blocks 2t, 2t+1
+
+    const uint32_t code_sel = (2 * t) | ((2 * t) << 4) | ((2 * t + 1) << 8) | ((2 * t + 1) << 12);
+    const uint8_t* frag = smem + kOffRing + warp * NS * kSlotBytes + g * kSlotRow + t * 8u;
+    const uint8_t* hdr = smem + kOffRing + warp * NS * kSlotBytes + g * kSlotRow;
+
+    float yacc0 = 0.0f, yacc1 = 0.0f;
+    uint32_t slot = 0, parity = 0;
+    bool lost = false;
+    for (uint32_t c0 = 0; c0 < nb; c0 += chunk_sb) {
+        const uint32_t n_sb = min(chunk_sb, nb - c0);
+        if (c0 != 0) __syncthreads();
+        {
+            const float4* xr = reinterpret_cast<const float4*>(x) + c0 * 64u;
+            const float s = s_scale[0];
+            for (uint32_t qd = tid; qd < n_sb * 64u; qd += kThreads) {
+                float4 v = xr[qd];
+                v.x *= s; v.y *= s; v.z *= s; v.w *= s;
+                const uint32_t sub = qd >> 3, in = qd & 7u;
+                float sum = (v.x + v.y) + (v.z + v.w);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                if (in == 0) *reinterpret_cast<float*>(smem + kOffXs + chunk_sb * 8u * 128u + sub * 4u) = sum;
+                if (sub & 1u) {  // a high-nibble sub-block: its A entries are 16 q
+                    v.x *= 0.0625f; v.y *= 0.0625f; v.z *= 0.0625f; v.w *= 0.0625f;
+                }
+                uint2 hi, lo;
+                split4(v, hi, lo);
+                uint8_t* dst = smem + kOffXs + sub * 128u + in * 8u;
+                *reinterpret_cast<uint2*>(dst) = hi;
+                *reinterpret_cast<uint2*>(dst + 64) = lo;
+            }
+        }
+        __syncthreads();
+        if (!active || lost) continue;
+
+        for (uint32_t i = (ks + KS - c0 % KS) % KS; i < n_sb; i += KS) {
+            if (!mbar_wait(bars + slot * 8u, parity)) {
+                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                lost = true;
+                break;
+            }
+            const uint8_t* fq = frag + slot * kSlotBytes;
+            const uint8_t* fh = hdr + slot * kSlotBytes;
+            float c[4];
+#pragma unroll
+            for (int sblk = 0; sblk < 8; ++sblk) {
+                const int j = sblk >> 1;
+                const uint32_t ba = b_base[sblk] + i * b_step[sblk];
+                uint4 bh, bl;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bh.x), "=r"(bh.y), "=r"(bh.z), "=r"(bh.w) : "r"(ba));
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+64];" : "=r"(bl.x), "=r"(bl.y), "=r"(bl.z), "=r"(bl.w) : "r"(ba));
+                const uint2 q0 = *reinterpret_cast<const uint2*>(fq + 16 + j * 32);
+                const uint2 q1 = *reinterpret_cast<const uint2*>(fq + 8 * kSlotRow + 16 + j * 32);
+                const uint32_t mask = (sblk & 1) ? 0x00F000F0u : 0x000F000Fu;
+                const uint32_t a0 = q0.x & mask, a1 = q1.x & mask, a2 = (q0.x >> 8) & mask, a3 = (q1.x >> 8) & mask;
+                const uint32_t e0 = q0.y & mask, e1 = q1.y & mask, e2 = (q0.y >> 8) & mask, e3 = (q1.y >> 8) & mask;
+                if (sblk == 0) mma16816_first(c, a0, a1, a2, a3, bh.x, bh.y);
+                else mma16816(c, a0, a1, a2, a3, bh.x, bh.y);
+                mma16816(c, e0, e1, e2, e3, bh.z, bh.w);
+                mma16816(c, a0, a1, a2, a3, bl.x, bl.y);
+                mma16816(c, e0, e1, e2, e3, bl.z, bl.w);
+            }
+            // ---- scales of this thread's two sub-blocks (2t, 2t+1), both rows, as fp32 --------------------------------------
+            const float2 sx = *reinterpret_cast<const float2*>(smem + (sx_base - smem_base) + i * 32u);
+            float part[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint4 h = *reinterpret_cast<const uint4*>(fh + r * 8 * kSlotRow);
+                const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+                const uint32_t m_lo = h.z & 0x3F3F3F3Fu, m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+                const uint32_t scp = prmt(sc_lo, sc_hi, code_sel), mp = prmt(m_lo, m_hi, code_sel);  // bytes 0 and 2 = codes 2t, 2t+1
+                // 0x4B000000 | code is the float 2^23 + code
+                const float sc0 = __uint_as_float(prmt(scp, 0x4B000000u, 0x7650u)) - 8388608.0f;
+                const float sc1 = __uint_as_float(prmt(scp, 0x4B000000u, 0x7652u)) - 8388608.0f;
+                const float m0 = __uint_as_float(prmt(mp, 0x4B000000u, 0x7650u)) - 8388608.0f;
+                const float m1 = __uint_as_float(prmt(mp, 0x4B000000u, 0x7652u)) - 8388608.0f;
+                const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+                const float dq = __low2float(dd) * 16777216.0f;  // undoes the 2^-24 of the subnormal encoding
+                const float dmn = __high2float(dd);
+                const float tq = fmaf(sc1, c[2 * r + 1], sc0 * c[2 * r]);
+                const float tm = fmaf(m1, sx.y, m0 * sx.x);
+                part[r] = fmaf(-dmn, tm, dq * tq);
+            }
+            yacc0 += part[0];
+            yacc1 += part[1];
+            __syncwarp();
+            slot = slot + 1 == NS ? 0 : slot + 1;
+            parity ^= (slot == 0);
+            if (issued < n_items) refill();
+        }
+    }
+    // the four threads of a quad hold the partial sums of different sub-block pairs: add them in a fixed order
+    yacc0 += __shfl_xor_sync(0xFFFFFFFFu, yacc0, 1);
+    yacc0 += __shfl_xor_sync(0xFFFFFFFFu, yacc0, 2);
+    yacc1 += __shfl_xor_sync(0xFFFFFFFFu, yacc1, 1);
+    yacc1 += __shfl_xor_sync(0xFFFFFFFFu, yacc1, 2);
+    if constexpr (KS > 1) {
+        __syncthreads();
+        float* red = reinterpret_cast<float*>(smem + kOffXs);
+        if (active && ks != 0) {
+            red[(((ks - 1) * kRowBlocks + rbl) * 32 + lane) * 2 + 0] = yacc0;
+            red[(((ks - 1) * kRowBlocks + rbl) * 32 + lane) * 2 + 1] = yacc1;
+        }
+        __syncthreads();
+        if (ks != 0) return;
+        if (active) {
+            for (int k = 1; k < KS; ++k) {
+                yacc0 += red[(((k - 1) * kRowBlocks + rbl) * 32 + lane) * 2 + 0];
+                yacc1 += red[(((k - 1) * kRowBlocks + rbl) * 32 + lane) * 2 + 1];
+            }
+        }
+    }
+    if (lost) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+        return;
+    }
+    if (!active || t != 0) return;
+    const float inv = s_inv[0];
+    const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
+    if (n0 < rows) y[n0] = yacc0 * inv;
+    if (n1 < rows) y[n1] = yacc1 * inv;
+}
+
 struct Plan {
     uint32_t chunk_sb;
     uint32_t smem_bytes;
@@ -399,6 +643,46 @@ Plan plan_for(uint32_t nb, uint32_t n_tok, uint32_t off_data, uint32_t reduce_by
     if (chunk == 0) chunk = 1;
     const uint32_t data = chunk * per_sb;  // the K-split reduction reuses this area
     return {chunk, off_data + (data > reduce_bytes ? data : reduce_bytes)};
+}
+
+/// Launch configuration with programmatic stream serialization: the kernel may begin (and prefetch weights) while the
+/// kernel before it in the stream drains; it orders itself with griddepcontrol.wait before touching x or y.
+cudaLaunchConfig_t pdl_config(uint32_t grid, uint32_t block, uint32_t smem, cudaStream_t s, cudaLaunchAttribute* attr) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+/// The weight matrix as a 2-D byte tensor {row_bytes, rows} with row pitch w_stride, tiled 160 x 16.
+int weight_map(const GemvCall& c, CUtensorMap* out) {
+    static EncodeTiledFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        HC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail(HALO_CUDA_E_BACKEND, "cuTensorMapEncodeTiled is not available");
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {c.row_bytes, c.rows};
+    const cuuint64_t strides[1] = {c.w_stride};
+    const cuuint32_t box[2] = {kSlotRow, 16};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(c.w), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(HALO_CUDA_E_KERNEL, "MATMUL: cannot describe the weight matrix to the copy engine (CUresult %d)", (int)r);
+    return 0;
 }
 
 template <int NTOK, int KS, int NS>
@@ -415,9 +699,12 @@ int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s)
     const uint32_t grid = (c.rows + 16u * kRowBlocks - 1) / (16u * kRowBlocks);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
-    gemv_mma_q4k_kernel<NTOK, KS, NS><<<grid, kRowBlocks * KS * 32, p.smem_bytes, s>>>(c.w, c.w_stride, x, c.x_stride, y, c.y_stride, c.rows,
-                                                                                       nb, p.chunk_sb, ctx->error_word_dev);
-    HC_CUDA(cudaGetLastError());
+    CUtensorMap wmap;
+    if (int rc = weight_map(c, &wmap)) return rc;
+    cudaLaunchAttribute attr[1];
+    const cudaLaunchConfig_t cfg = pdl_config(grid, kRowBlocks * KS * 32, p.smem_bytes, s, attr);
+    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<NTOK, KS, NS>, wmap, x, c.x_stride, y, c.y_stride, c.rows, nb, p.chunk_sb,
+                               ctx->error_word_dev));
     return 0;
 }
 
@@ -428,16 +715,59 @@ int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, uint32_t n
     if constexpr (NTOK > 16) {
         return fail(HALO_CUDA_E_KERNEL, "MATMUL: token tile of %u", n);
     } else {
-        if (n == NTOK) return launch_n<NTOK, 2, 3>(ctx, c, tok0, s);
+#ifndef HALO_MMA_KS
+#define HALO_MMA_KS 2
+#define HALO_MMA_NS 3
+#endif
+        if (n == NTOK) return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS>(ctx, c, tok0, s);
         return launch_tokens<NTOK + 1>(ctx, c, tok0, n, s);
     }
 }
 
+template <int KS, int NS>
+int launch_m1(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok, cudaStream_t s) {
+    const uint32_t nb = c.cols / 256u;
+    constexpr uint32_t off_xs = kOffRing + kRowBlocks * KS * NS * kSlotBytes + 128;
+    const uint32_t per_sb = 8u * 128u + 32u;
+    uint32_t chunk = (kSmemBudget - off_xs) / per_sb;
+    if (chunk > nb) chunk = nb;
+    const uint32_t data = chunk * per_sb, red = (KS - 1) * kRowBlocks * 32 * 2 * 4;
+    const uint32_t smem_bytes = off_xs + (data > red ? data : red);
+    static bool attr_set = false;
+    if (!attr_set) {
+        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_m1_kernel<KS, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)));
+        attr_set = true;
+    }
+    CUtensorMap wmap;
+    if (int rc = weight_map(c, &wmap)) return rc;
+    const uint32_t grid = (c.rows + 16u * kRowBlocks - 1) / (16u * kRowBlocks);
+    const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok} * c.x_stride);
+    float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok} * c.y_stride);
+    cudaLaunchAttribute attr[1];
+    const cudaLaunchConfig_t cfg = pdl_config(grid, kRowBlocks * KS * 32, smem_bytes, s, attr);
+    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_m1_kernel<KS, NS>, wmap, x, y, c.rows, nb, chunk, ctx->error_word_dev));
+    return 0;
+}
+
 }  // namespace
+
+int launch_gemv_mma_m1(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
+    // One launch per x row: the single-row kernel re-reads the weights for every row, which keeps each row bitwise
+    // its own n_vec == 1 result; batches belong to gemv_mma_f16x2.
+#ifndef HALO_M1_KS
+#define HALO_M1_KS 2
+#define HALO_M1_NS 3
+#endif
+    for (uint32_t t = 0; t < c.n_vec; ++t) {
+        if (int rc = launch_m1<HALO_M1_KS, HALO_M1_NS>(ctx, c, t, s)) return rc;
+    }
+    return 0;
+}
 
 bool gemv_mma_supports(const GemvCall& c) {
     if (c.wtype != HALO_CUDA_T_Q4_K || c.cols == 0) return false;
-    if (reinterpret_cast<uintptr_t>(c.w) % 16 != 0 || c.w_stride % 16 != 0) return false;  // 16-byte header loads
+    if (reinterpret_cast<uintptr_t>(c.w) % 16 != 0 || c.w_stride % 16 != 0) return false;  // tensor-map base and pitch
+    if (c.w_stride >= (uint64_t{1} << 40) || c.row_bytes >= (uint64_t{1} << 32)) return false;
     if (reinterpret_cast<uintptr_t>(c.x) % 16 != 0 || c.x_stride % 16 != 0) return false;  // float4 reads of x
     return true;
 }

@@ -75,6 +75,7 @@ int launch_gemv_exact8(const GemvCall& c, cudaStream_t s);
 int launch_gemv_warp_f32(const GemvCall& c, cudaStream_t s);
 bool gemv_warp_f32_supports(const GemvCall& c);
 int launch_gemv_mma(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_mma_m1(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_mma_supports(const GemvCall& c);
 int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s);
 bool gemm_tcgen05_supports(const GemvCall& c);

@@ -56,6 +56,8 @@ extern "C" {
 #define HALO_CUDA_GEMV_MMA_F16X2 3    /* tensor-core skinny kernel, x split into fp16 hi + lo */
 #define HALO_CUDA_GEMM_TCGEN05_F16 4  /* prefill: dequant to fp16 in shared memory + tcgen05 MMA */
 #define HALO_CUDA_GEMM_TCGEN05_BF16 5 /* same with bf16 operands */
+#define HALO_CUDA_GEMV_MMA_M1 6       /* tensor-core single-row specialist (one launch per x row) */
+#define HALO_CUDA_GEMV_VARIANT_MAX 6
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
 
@@ -77,7 +79,7 @@ typedef struct HaloCudaDeviceInfo {
 typedef struct HaloCudaVariant {
     uint32_t id;
     uint32_t op;
-    uint32_t family; /* 0 = fp32 exact order, 1 = fp32 reordered, 2 = fp16 tensor-core operands */
+    uint32_t family; /* 0 = fp32 exact order, 1 = fp32 reordered, 2 = tensor-core skinny, 3 = tensor-core single-row, 4 = fp16 GEMM */
     const char* name;
 } HaloCudaVariant;
 

@@ -48,7 +48,8 @@ def test_geometry_and_registry_need_no_device():
     n = C.c_uint32()
     assert lib.halo_cuda_variants(capi.OP_GEMV, arr, 16, C.byref(n)) == 0
     got = {arr[i].id: arr[i].name.decode() for i in range(n.value)}
-    assert got == {1: "gemv_exact8", 2: "gemv_warp_f32", 3: "gemv_mma_f16x2", 4: "gemm_tcgen05_f16", 5: "gemm_tcgen05_bf16"}
+    assert got == {1: "gemv_exact8", 2: "gemv_warp_f32", 3: "gemv_mma_f16x2", 4: "gemm_tcgen05_f16", 5: "gemm_tcgen05_bf16",
+                   6: "gemv_mma_m1"}
     assert lib.halo_cuda_variants(1, arr, 16, C.byref(n)) == capi.E_UNSUPPORTED  # RMS_NORM is not this backend's
 
 

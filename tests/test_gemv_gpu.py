@@ -107,12 +107,12 @@ def test_exact_variant_f32_weights_with_tail(hz, checker):
 
 # ---- the fast fp32 variant: bounded, batch-invariant, and not vacuous ------------------------------------------
 
-FAST = [capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2]
+FAST = [capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2, capi.GEMV_MMA_M1]
 MMA_TYPES = (synth.Q4_K,)
 
 
 def _skip_unless_supported(variant, t):
-    if variant == capi.GEMV_MMA_F16X2 and t not in MMA_TYPES:
+    if variant in (capi.GEMV_MMA_F16X2, capi.GEMV_MMA_M1) and t not in MMA_TYPES:
         pytest.skip("gemv_mma_f16x2 takes Q4_K weights")
 
 
