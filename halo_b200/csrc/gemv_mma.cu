@@ -36,7 +36,10 @@ namespace halo_cuda {
 
 namespace {
 
-constexpr int kRowBlocks = 8;         // 16-row blocks per CTA: a CTA covers 128 W rows
+#ifndef HALO_MMA_ROWBLOCKS
+#define HALO_MMA_ROWBLOCKS 8
+#endif
+constexpr int kRowBlocks = HALO_MMA_ROWBLOCKS;  // 16-row blocks per CTA (8: a CTA covers 128 W rows)
 constexpr uint32_t kSmemBudget = 220 * 1024;
 #ifndef HALO_MMA_CHAINS
 #define HALO_MMA_CHAINS 2
@@ -138,7 +141,7 @@ constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eig
 // KS: warps sharing one 16-row block; warp ks takes the super-blocks sb = ks (mod KS), a split that depends on
 // nothing but KS, and the KS partial sums are added in ks order.  NS: ring stages per warp.
 template <int NTOK, int KS, int NS>
-__global__ void __launch_bounds__(kRowBlocks * KS * 32, 1)
+__global__ void __launch_bounds__(kRowBlocks * KS * 32, kRowBlocks >= 8 ? 1 : 2)
 gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, uint64_t x_stride,
                     float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t chunk_sb,
                     uint32_t* __restrict__ error_word) {
@@ -423,7 +426,7 @@ gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __res
 // pre-divided by 16 (exact).  x is again fp16 hi + lo (two MMAs per k-step).  The min term uses the exact fp32
 // sub-block sums of x.  A row's arithmetic differs from gemv_mma_f16x2, so the two are different numerics families.
 template <int KS, int NS>
-__global__ void __launch_bounds__(kRowBlocks * KS * 32, 1)
+__global__ void __launch_bounds__(kRowBlocks * KS * 32, kRowBlocks >= 8 ? 1 : 2)
 gemv_mma_q4k_m1_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, float* __restrict__ y, uint32_t rows,
                        uint32_t nb, uint32_t chunk_sb, uint32_t* __restrict__ error_word) {
     extern __shared__ __align__(128) uint8_t smem[];
