@@ -5,13 +5,13 @@
 // (include/halo/backend/backend.h:300-304).  Same numerics here: W is dequantized in fp32 exactly as
 // tensor::dequantize_row does ((d*sc)*q - dmin*m, src/tensor/quant.cpp:247-269) and rounded ONCE to the 16-bit type.
 //
-// Structure (one 256-token x 256-row output tile per CTA, 320 threads):
+// Structure (one 256-token x 256-row output tile per CTA, 576 threads):
 //   warp 0      TMA producer: two 128 x 64 boxes of the 16-bit copy of X per stage (128-byte swizzle)
 //   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16; two accumulators = all 512 TMEM columns)
-//   warps 2-9   one W row per thread: read 32 bytes of quants + the block header, write 64 dequantized 16-bit
-//               values as one 128-byte swizzled row of the B tile; afterwards the same warps run the epilogue
+//   warps 2-17  two threads per W row: each reads 16 bytes of quants + the block header and writes 32 dequantized
+//               16-bit values, together one 128-byte swizzled row of the B tile; afterwards the same warps run the epilogue
 //               (tcgen05.ld -> fp32 y)
-// A three-stage ring of {A0, A1, B} tiles is tracked by mbarriers: full_a (TMA bytes), full_b (8 warp arrivals after
+// A three-stage ring of {A0, A1, B} tiles is tracked by mbarriers: full_a (TMA bytes), full_b (16 warp arrivals after
 // a proxy fence), empty (tcgen05.commit).  Each CTA dequantizes its W tile once for 256 tokens, which keeps the
 // CUDA-core work below the tensor-pipe time of the two MMAs it feeds.
 //
@@ -35,7 +35,8 @@ constexpr uint32_t kBM = 256, kBN = 256, kBK = 64, kStages = 3;
 constexpr uint32_t kTileA = 128 * kBK * 2;          // one 128-token box: 16 KiB
 constexpr uint32_t kTileB = kBN * kBK * 2;          // 32 KiB
 constexpr uint32_t kStageBytes = 2 * kTileA + kTileB;  // 64 KiB
-constexpr uint32_t kGemmThreads = 320;
+constexpr uint32_t kDeqWarps = 16;                  // two threads per W row: each unpacks 16 of the 32 quant bytes
+constexpr uint32_t kGemmThreads = 64 + kDeqWarps * 32;
 constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t kGemmWaitSpins = 1u << 16;
 
@@ -160,7 +161,7 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             g_mbar_init(full_a(s), 1);
-            g_mbar_init(full_b(s), 8);
+            g_mbar_init(full_b(s), kDeqWarps);
             g_mbar_init(empty(s), 1);
         }
         g_mbar_init(accum_bar, 1);
@@ -218,7 +219,7 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
         }
     } else {
         // ---- dequant producers: thread r writes W row n0 + r of the B tile ------------------------------------------------------
-        const uint32_t r = threadIdx.x - 64;
+        const uint32_t r = (threadIdx.x - 64) >> 1, hf = threadIdx.x & 1u;  // row of the tile, and which 16 quant bytes
         const bool valid = n0 + r < rows;
         const uint8_t* row = w + uint64_t{valid ? n0 + r : 0} * w_stride;
         const uint32_t sw = r & 7u;
@@ -235,8 +236,7 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
                 const uint8_t* blk = row + (kb >> 2) * 144u;
                 const uint32_t j = kb & 3u;
                 const uint4 h = *reinterpret_cast<const uint4*>(blk);
-                const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + j * 32);
-                const uint4 qb = *reinterpret_cast<const uint4*>(blk + 32 + j * 32);
+                const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + j * 32 + hf * 16);
                 // 6-bit codes of sub-blocks 2j (low nibbles) and 2j+1 (high nibbles), src/tensor/quant.cpp:236-244
                 const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
                 uint32_t sc0, mn0, sc1, mn1;
@@ -254,10 +254,11 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
                 const float d = __low2float(dd), dmin = __high2float(dd);
                 const float d1 = d * static_cast<float>(sc0), m1 = dmin * static_cast<float>(mn0);
                 const float d2 = d * static_cast<float>(sc1) * 0.0625f, m2 = dmin * static_cast<float>(mn1);
-                const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                const uint32_t q[4] = {qa.x, qa.y, qa.z, qa.w};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // 16-byte chunk c: elements 8c..8c+7 of the low-nibble sub-block, c+4: of the high one
-                    const uint32_t u0 = q[2 * c], u1 = q[2 * c + 1];
+                for (int cc = 0; cc < 2; ++cc) {  // 16-byte chunk c: elements 8c..8c+7 of the low-nibble sub-block, c+4: of the high one
+                    const uint32_t c = 2 * hf + cc;
+                    const uint32_t u0 = q[2 * cc], u1 = q[2 * cc + 1];
                     uint4 lo, hi;
                     lo.x = deq_pair<BF16>(u0 & 0x000F000Fu, d1, m1);
                     lo.y = deq_pair<BF16>((u0 >> 8) & 0x000F000Fu, d1, m1);
@@ -267,12 +268,12 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
                     hi.y = deq_pair<BF16>((u0 >> 8) & 0x00F000F0u, d2, m2);
                     hi.z = deq_pair<BF16>(u1 & 0x00F000F0u, d2, m2);
                     hi.w = deq_pair<BF16>((u1 >> 8) & 0x00F000F0u, d2, m2);
-                    *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ sw) << 4)) = lo;
-                    *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c + 4) ^ sw) << 4)) = hi;
+                    *reinterpret_cast<uint4*>(dst + ((c ^ sw) << 4)) = lo;
+                    *reinterpret_cast<uint4*>(dst + (((c + 4) ^ sw) << 4)) = hi;
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (c << 4)) = make_uint4(0, 0, 0, 0);
+                for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + ((4 * hf + c) << 4)) = make_uint4(0, 0, 0, 0);
             }
             // make the generic-proxy stores visible to the tensor core's (async-proxy) reads, then one arrival per warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -286,11 +287,12 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t quarter = warp & 3u, half = (warp - 2) >> 2;  // TMEM lanes 32*quarter.., accumulator `half`
+            // TMEM lanes 32*quarter.. (fixed by warp id % 4), accumulator `half`, and which 128 of its 256 columns
+            const uint32_t quarter = warp & 3u, half = ((warp - 2) >> 2) & 1u, chalf = (warp - 2) >> 3;
             const uint32_t token = m0 + half * 128u + quarter * 32u + lane;
             float* yr = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{token} * y_stride) + n0;
 #pragma unroll 1
-            for (uint32_t c = 0; c < kBN / 32; ++c) {
+            for (uint32_t c = chalf * (kBN / 64); c < (chalf + 1) * (kBN / 64); ++c) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + half * 256u + c * 32u;
                 asm volatile(
