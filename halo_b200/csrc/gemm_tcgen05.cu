@@ -224,8 +224,21 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
         const uint8_t* row = w + uint64_t{valid ? n0 + r : 0} * w_stride;
         const uint32_t sw = r & 7u;
         bool ok = true;
+        // the quants of the next K block are requested one iteration ahead, so that their latency hides behind the
+        // unpacking of the current block and the wait for a free stage
+        uint4 h_next = make_uint4(0, 0, 0, 0), q_next = make_uint4(0, 0, 0, 0);
+        if (valid) {
+            h_next = *reinterpret_cast<const uint4*>(row);
+            q_next = *reinterpret_cast<const uint4*>(row + 16 + hf * 16);
+        }
         for (uint32_t kb = 0; kb < nkb; ++kb) {
             const uint32_t s = kb % kStages, use = kb / kStages;
+            const uint4 h = h_next, qa = q_next;
+            if (valid && kb + 1 < nkb) {
+                const uint8_t* nblk = row + ((kb + 1) >> 2) * 144u;
+                h_next = *reinterpret_cast<const uint4*>(nblk);
+                q_next = *reinterpret_cast<const uint4*>(nblk + 16 + ((kb + 1) & 3u) * 32 + hf * 16);
+            }
             if (use > 0) {
                 ok = g_mbar_wait(empty(s), (use - 1) & 1u);
                 ok = __all_sync(0xFFFFFFFFu, ok);
@@ -233,10 +246,7 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
             }
             uint8_t* dst = smem + s * kStageBytes + 2 * kTileA + r * 128u;
             if (valid) {
-                const uint8_t* blk = row + (kb >> 2) * 144u;
                 const uint32_t j = kb & 3u;
-                const uint4 h = *reinterpret_cast<const uint4*>(blk);
-                const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + j * 32 + hf * 16);
                 // 6-bit codes of sub-blocks 2j (low nibbles) and 2j+1 (high nibbles), src/tensor/quant.cpp:236-244
                 const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
                 uint32_t sc0, mn0, sc1, mn1;
