@@ -1,0 +1,45 @@
+#pragma once
+/// \file
+/// The B200 matmul backend behind HALO's Backend interface (include/halo/backend/backend.h of the reference).
+///
+/// Scope: MATMUL (gemv), LM_HEAD, GET_ROWS, COPY, upload / download, over libhalo_cuda.so (include/halo_cuda.h).
+/// Every other operator of the interface raises Error(Unsupported): this backend never computes on the host and
+/// never silently ignores an argument (norm_w, gates, status words and the ids scatter are refused like the CPU
+/// backend refuses what it does not implement, src/backend/cpu_backend.cpp:341-342).
+///
+/// Contracts kept from the CPU backend (src/backend/cpu_backend.cpp:98-162) and the device adapters
+/// (include/halo/backend/hip_backend.h:20-46): operands must belong to this backend, outputs must be writable and must
+/// not overlap inputs, validation happens before anything is enqueued, allocate() zero-fills, import_host_readonly()
+/// copies to the device, import_host() is refused, buffers are not host-addressable, data errors of GET_ROWS surface
+/// at the next Stream::wait(), a wait that exceeds its budget raises Error(Backend) and makes lost() true.
+///
+/// Variant ids (KernelChoice) are those of include/halo_cuda.h; 0 = the shape heuristic or the installed plan.
+#include <cstdint>
+#include <memory>
+
+#include "halo/backend/backend.h"
+
+namespace halo::backend {
+
+/// Kind has no CUDA enumerator yet (backend.h:64); the model only special-cases Kind::Vulkan.
+inline constexpr Kind kKindCuda = static_cast<Kind>(4);
+
+struct CudaBackendOptions {
+    int device_ordinal = 0;
+    std::uint32_t default_gemv_variant = 0;  ///< variant run for KernelChoice{}; Error(Config) if not registered
+    std::uint64_t wait_timeout_ns = 0;       ///< Stream::wait budget, 0 = unlimited
+};
+
+/// One (shape bucket -> variant) decision of the autotuner, installed for KernelChoice{} calls.
+struct CudaPlanEntry {
+    DType wtype = DType::Q4_K;
+    std::uint32_t rows = 0, cols = 0, n_vec_lo = 1, n_vec_hi = 1, variant_id = 0;
+};
+
+/// Throws Error(Device) when no sm_100 device is usable, Error(Config) for an unknown default variant.
+[[nodiscard]] std::unique_ptr<Backend> make_cuda_backend(const CudaBackendOptions& options = {});
+
+/// Installs tuner decisions on a backend made by make_cuda_backend (Error(Api) for any other backend).
+void cuda_backend_set_plan(Backend& backend, std::span<const CudaPlanEntry> plan);
+
+}  // namespace halo::backend
