@@ -155,6 +155,78 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# BASELINE config 3, one layer of each kind: (name, type, N, K, split).  GDN layers: qkv / z / beta / alpha / out; GQA layers:
+# q / k / v / o; every layer: FFN gate / up / down.  attn_v and ffn_down are Q6_K, everything else Q4_K.
+def sweep_layers():
+    from halo_b200 import synth
+    q4, q6 = synth.Q4_K, synth.Q6_K
+    ffn = [("ffn_gate", q4, 17408, 5120, "column"), ("ffn_up", q4, 17408, 5120, "column"), ("ffn_down", q6, 5120, 17408, "row")]
+    gdn = [("gdn_qkv", q4, 10240, 5120, "column"), ("gdn_z", q4, 6144, 5120, "column"), ("gdn_beta", q4, 48, 5120, "column"),
+           ("gdn_alpha", q4, 48, 5120, "column"), ("gdn_out", q4, 5120, 6144, "row")] + ffn
+    gqa = [("attn_q", q4, 5120, 5120, "column"), ("attn_k", q4, 1024, 5120, "column"), ("attn_v", q6, 1024, 5120, "column"),
+           ("attn_o", q4, 5120, 5120, "row")] + ffn
+    return gdn, gqa
+
+
+def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
+    """Per-token decode weight sweep over an 8-layer slice (6 Gated-DeltaNet + 2 GQA layers) of the 64-layer stack of
+    BASELINE config 3, tensor-parallel over `world` GPUs: column split for qkv / gate / up, row split + NCCL all-reduce
+    for out / o / down.  Aggregate weight GB/s includes the collectives."""
+    import torch
+    import torch.distributed as dist
+
+    from halo_b200 import synth, tp_cuda
+    rt = tp_cuda.CudaTp(local_rank, rank, world)
+    gdn, gqa = sweep_layers()
+    host = {}
+    layers, total_bytes = [], 0
+    for li in range(8):
+        projs = []
+        for name, wtype, n, k, mode in (gqa if li % 4 == 3 else gdn):
+            key = (wtype, n, k)
+            if key not in host:
+                host[key] = synth.quant_weights(wtype, n, k, 7, len(host) + 1)
+            projs.append((name, rt.load(wtype, host[key], n, k, mode)))
+            total_bytes += n * synth.row_bytes(wtype, k)
+        layers.append(projs)
+    out = {}
+    for m in (1, 4):
+        xs = {}
+        for projs in layers:
+            for _, p in projs:
+                kk = p.shard.cols
+                if kk not in xs:
+                    xs[kk] = torch.randn((m, kk), device="cuda", dtype=torch.float32)
+
+        def one_token():
+            for projs in layers:
+                for _, p in projs:
+                    p(xs[p.shard.cols])
+
+        for _ in range(3):
+            one_token()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one_token()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out[f"m{m}"] = {"ms_per_token_slice": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9,
+                        "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if world > 1 else 0}
+    out["workload"] = (f"cfg3 slice: 8 of 64 layers (6 GDN + 2 GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K weights in total, "
+                       f"tp={world}: column split qkv/gate/up, row split + all-reduce out/o/down")
+    out["scaling"] = "strong"
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -308,6 +380,12 @@ def run_ours(args) -> None:
                                 "traffic": None, "peak_source": pkk["source"], "flops_per_launch": flops},
                    "l2": "operands larger than L2: W 50 MB + x 42 MB + y 143 MB per call", "gpu_launches": 2 * psteps}
 
+    sweep = None
+    if not args.profile:
+        for b in wbufs[1:] + ybufs[1:]:
+            b.free()
+        sweep = tp_sweep(local_rank, rank, world, max(3, min(args.steps, 20)))
+
     launches_per_step = COPIES
     total_launches = args.steps * launches_per_step
     launch_us = ms * 1e3 / total_launches
@@ -336,6 +414,7 @@ def run_ours(args) -> None:
                 "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": total_launches,
         "prefill": prefill,
+        "tp_sweep": sweep,
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -1,0 +1,119 @@
+"""Host logic of the tensor-parallel split on CPU: partitions, shard extraction, and a world_size-2 gloo run in which
+the local products come from the checker.  The single-rank result is the oracle for every split."""
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from conftest import bits
+from halo_b200 import synth, tp
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_partitions():
+    assert tp.column_ranges(17408, 8) == [(i * 2176, (i + 1) * 2176) for i in range(8)]
+    # K = 5120 is 20 super-blocks: 8 ranks get 3,3,3,3,2,2,2,2
+    r = tp.row_ranges(synth.Q4_K, 5120, 8)
+    assert [(e - b) // 256 for b, e in r] == [3, 3, 3, 3, 2, 2, 2, 2] and r[0][0] == 0 and r[-1][1] == 5120
+    # K = 17408 is 68 super-blocks: 9,9,9,9,8,8,8,8
+    assert [(e - b) // 256 for b, e in tp.row_ranges(synth.Q6_K, 17408, 8)] == [9, 9, 9, 9, 8, 8, 8, 8]
+    assert tp.row_ranges(synth.Q8_0, 17408, 4) == [(i * 4352, (i + 1) * 4352) for i in range(4)]
+    with pytest.raises(ValueError):
+        tp.row_ranges(synth.Q4_K, 1000, 2)
+    assert tp.column_ranges(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+
+
+@pytest.mark.parametrize("wtype", [synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q4_0])
+def test_shards_reassemble_and_match_the_single_rank_result(oracle_c, wtype):
+    rows, cols, m, n_ranks = 48, 2048, 3, 3
+    w = synth.quant_weights(wtype, rows, cols, 21, 1)
+    x = synth.activations(m, cols, 21, 2)
+    full = oracle_c.gemv(wtype, w, x, rows, cols)
+
+    def matmul(s, xl):
+        return oracle_c.gemv(s.wtype, s.weights, np.ascontiguousarray(xl), s.rows, s.cols)
+
+    # column split: concatenated rank outputs are bitwise the single-rank result
+    parts = [tp.TpProjection(tp.shard_weight(wtype, w, rows, cols, "column", r, n_ranks), matmul)(x) for r in range(n_ranks)]
+    assert np.array_equal(bits(np.concatenate(parts, axis=1)), bits(full))
+    # row split: shard bytes are exactly the block ranges, and the summed partials agree within the summation bound
+    shards = [tp.shard_weight(wtype, w, rows, cols, "row", r, n_ranks) for r in range(n_ranks)]
+    assert sum(s.cols for s in shards) == cols
+    assert np.array_equal(np.concatenate([s.weights for s in shards], axis=1), w)
+    acc = np.zeros_like(full)
+    for s in shards:
+        acc += tp.TpProjection(s, matmul, all_reduce=lambda y: None)(x)
+    wf = oracle_c.dequantize(wtype, w, rows * cols).reshape(rows, cols).astype(np.float64)
+    bound = 2 * (cols // 8 + 8) * 2.0**-24 * (np.abs(x.astype(np.float64)) @ np.abs(wf).T)
+    assert np.all(np.abs(acc.astype(np.float64) - full) <= bound)
+
+
+def test_merge_argmax_is_the_single_call_answer(oracle_c):
+    V, E, n, ranks = 4096, 256, 4, 4
+    w = synth.quant_weights(synth.Q8_0, V, E, 22, 1)
+    x = synth.activations(n, E, 22, 2)
+    x[2, 0] = np.nan
+    full, _, _ = oracle_c.lm_head(synth.Q8_0, w, x, V, E, want_logits=False)
+    triples = []
+    for r in range(ranks):
+        s = tp.shard_weight(synth.Q8_0, w, V, E, "column", r, ranks)
+        res, _, _ = oracle_c.lm_head(synth.Q8_0, s.weights, x, s.rows, E, want_logits=False)
+        res = res.copy()
+        ok = res[:, 0] != 0xFFFFFFFF
+        res[ok, 0] += s.row0  # what halo_cuda_lm_head does with row_offset
+        triples.append(res)
+    assert np.array_equal(tp.merge_argmax(triples), full)
+
+
+def _worker(rank: int, world: int, port: int, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    chk = oracle.Oracle()
+    rows, cols, m = 40, 2560, 2
+    w = synth.quant_weights(synth.Q4_K, rows, cols, 23, 1)
+    x = synth.activations(m, cols, 23, 2)
+
+    def matmul(s, xl):
+        return torch.from_numpy(chk.gemv(s.wtype, s.weights, np.ascontiguousarray(xl), s.rows, s.cols, threads=1))
+
+    up = tp.TpProjection(tp.shard_weight(synth.Q4_K, w, rows, cols, "column", rank, world), matmul)
+    down = tp.TpProjection(tp.shard_weight(synth.Q4_K, w, rows, cols, "row", rank, world), matmul, all_reduce=lambda y: dist.all_reduce(y))
+    y_col = up(x)
+    gathered = [torch.zeros_like(y_col) for _ in range(world)]
+    dist.all_gather(gathered, y_col)
+    y_row = down(x)
+    q.put((rank, torch.cat(gathered, dim=1).numpy(), y_row.numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_column_and_row_split(oracle_c):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    rows, cols, m = 40, 2560, 2
+    w = synth.quant_weights(synth.Q4_K, rows, cols, 23, 1)
+    x = synth.activations(m, cols, 23, 2)
+    full = oracle_c.gemv(synth.Q4_K, w, x, rows, cols)
+    for _, y_col, y_row in results:
+        assert np.array_equal(bits(y_col), bits(full))                       # column split: bitwise
+        assert np.max(np.abs(y_row - full)) <= 1e-5 * np.max(np.abs(full))   # row split + all-reduce: bounded
+    assert np.array_equal(bits(results[0][2]), bits(results[1][2]))          # every rank holds the same reduced y
