@@ -206,12 +206,31 @@ def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
         for _ in range(3):
             one_token()
         torch.cuda.synchronize()
+        # The token pass is launch-bound when issued from Python: capture it once as a CUDA graph and replay it.
+        replay, graphed = one_token, False
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                one_token()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    one_token()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            replay, graphed = graph.replay, True
+        except Exception as exc:  # noqa: BLE001 - fall back to eager launches and say so
+            sys.stderr.write(f"tp_sweep: CUDA graph capture failed ({exc!r}); timing eager launches\n")
+            torch.cuda.synchronize()
+        for _ in range(2):
+            replay()
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            one_token()
+            replay()
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
@@ -220,7 +239,8 @@ def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         out[f"m{m}"] = {"ms_per_token_slice": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9,
-                        "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if world > 1 else 0}
+                        "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if world > 1 else 0,
+                        "cuda_graph": graphed}
     out["workload"] = (f"cfg3 slice: 8 of 64 layers (6 GDN + 2 GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K weights in total, "
                        f"tp={world}: column split qkv/gate/up, row split + all-reduce out/o/down")
     out["scaling"] = "strong"
