@@ -91,6 +91,87 @@ __device__ __forceinline__ void split4(float4 v, uint2& hi, uint2& lo) {
     lo.y = static_cast<uint32_t>(__half_as_ushort(l1)) | (static_cast<uint32_t>(__half_as_ushort(l3)) << 16);
 }
 
+
+/// Power-of-two scale of one x row from its largest magnitude a: s = 2^(13 - floor(log2 a)) for a normal finite a, else 1;
+/// the exponent is clamped so that s and 1/s stay normal.
+__device__ __forceinline__ void row_scale(float a, float& s, float& inv) {
+    int e = static_cast<int>((__float_as_uint(a) >> 23) & 0xFFu) - 127;
+    int se = (a > 0.0f && e < 128) ? 13 - e : 0;
+    se = max(-100, min(100, se));
+    s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
+    inv = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
+}
+
+/// Converts super-blocks [c0, c0 + n_sb) of one x row into MMA-fragment order: fp16 hi / lo of x * s per 32-element
+/// sub-block (`sub_stride` bytes apart, this token's columns at byte `col_off`), and the sub-block sums / 32 as fp16
+/// hi / lo (`sb_stride` bytes per super-block, this token's columns at byte `col_off / 4`).  Called by every thread of
+/// a CTA (`nthreads` a multiple of 32); the arithmetic does not depend on who calls it or on the chunking.
+__device__ __forceinline__ void stage_row(uint8_t* xs, uint8_t* sx, const float* xrow, float s, uint32_t c0, uint32_t n_sb,
+                                          uint32_t sub_stride, uint32_t sb_stride, uint32_t col_off, uint32_t tid, uint32_t nthreads) {
+    const float4* xr = reinterpret_cast<const float4*>(xrow) + c0 * 64u;
+    for (uint32_t qd = tid; qd < n_sb * 64u; qd += nthreads) {
+        float4 v = xr[qd];
+        v.x *= s; v.y *= s; v.z *= s; v.w *= s;
+        uint2 hi, lo;
+        split4(v, hi, lo);
+        const uint32_t sub = qd >> 3, in = qd & 7u;  // 8 quads per 32-element sub-block
+        uint8_t* dst = xs + sub * sub_stride + col_off + in * 8u;
+        *reinterpret_cast<uint2*>(dst) = hi;
+        *reinterpret_cast<uint2*>(dst + 64) = lo;
+        float sum = (v.x + v.y) + (v.z + v.w);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+        if (in == 0) {
+            sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
+            const __half h = __float2half_rn(sum);
+            const __half l = __float2half_rn(sum - __half2float(h));
+            uint8_t* sd = sx + (sub >> 3) * sb_stride + (col_off >> 2) + (sub & 7u) * 2u;
+            *reinterpret_cast<__half*>(sd) = h;
+            *reinterpret_cast<__half*>(sd + 16) = l;
+        }
+    }
+}
+
+/// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on an mbarrier.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+/// Pre-staging kernel for batches: one CTA per x row converts the whole row once into global scratch laid out exactly
+/// like the in-kernel staging area ([sub-block][column][64 B], then [super-block][column][16 B], then 1/s per row), so
+/// that the matmul CTAs fetch their K chunks with bulk copies instead of each converting x again.
+__global__ void __launch_bounds__(512) stage_x_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
+                                                      uint32_t nb, uint32_t n_tok) {
+    __shared__ float red[16];
+    __shared__ float sc[2];
+    const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t cols = nb * 256u, kcols = 2 * n_tok;
+    const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    float m = 0.0f;
+    for (uint32_t i = tid; i < cols / 4; i += 512) {
+        const float4 v = reinterpret_cast<const float4*>(xrow)[i];
+        m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.0f;
+        for (int i = 0; i < 16; ++i) a = fmaxf(a, red[i]);
+        row_scale(a, sc[0], sc[1]);
+    }
+    __syncthreads();
+    uint8_t* xs = scratch;
+    uint8_t* sx = scratch + uint64_t{nb} * 8u * kcols * 64u;
+    float* inv = reinterpret_cast<float*>(sx + uint64_t{nb} * kcols * 16u);
+    stage_row(xs, sx, xrow, sc[0], 0, nb, kcols * 64u, kcols * 16u, 2 * tk * 64u, tid, 512);
+    if (tid == 0) inv[tk] = sc[1];
+}
+
 // ---- shared-memory weight ring -------------------------------------------------------------------------------------
 // Each warp streams its own rows: per pipeline stage one TMA tile copy (cp.async.bulk.tensor.2d over a tensor map of
 // the weight matrix as rows of bytes) brings the 144-byte super-block of its 16 W rows into a 16 x 160-byte slot and
@@ -134,17 +215,19 @@ __device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* ma
 // Shared-memory layout (byte offsets from the dynamic base), for `ncols` = 2 * tokens columns:
 //   [0, 16) unused | scales | partial maxima | mbarriers | weight ring |
 //   xs:  [sub-block][column][64 B] fp16 x in slot order    sx: [super-block][column][16 B] sub-block sums / 32
-constexpr uint32_t kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
+constexpr uint32_t kOffXBar = 0, kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
 constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eight bytes per warp and stage (<= 6 stages)
 
 // NTOK: x rows of this launch (1..16), i.e. 2 * NTOK B columns in G = ceil(NTOK / 4) MMA column groups.
 // KS: warps sharing one 16-row block; warp ks takes the super-blocks sb = ks (mod KS), a split that depends on
 // nothing but KS, and the KS partial sums are added in ks order.  NS: ring stages per warp.
-template <int NTOK, int KS, int NS>
+// PRE: x was converted once by stage_x_kernel into `xstage`; the CTA fetches each K chunk by bulk copy.  Otherwise the CTA
+// converts its chunks itself (no scratch memory; the path of single-row calls).  Both give the same bits.
+template <int NTOK, int KS, int NS, bool PRE>
 __global__ void __launch_bounds__(kRowBlocks * KS * 32, kRowBlocks >= 8 ? 1 : 2)
 gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, uint64_t x_stride,
                     float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t chunk_sb,
-                    uint32_t* __restrict__ error_word) {
+                    uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     constexpr int G = (NTOK + 3) / 4;
@@ -193,28 +276,33 @@ gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __res
     float* s_scale = reinterpret_cast<float*>(smem + kOffScale);
     float* s_inv = reinterpret_cast<float*>(smem + kOffInv);
     float* s_red = reinterpret_cast<float*>(smem + kOffRed);  // kWarps partial maxima
-    for (uint32_t tk = 0; tk < NTOK; ++tk) {
-        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-        float m = 0.0f;
-        for (uint32_t i = tid; i < cols / 4; i += kThreads) {
-            const float4 v = xr[i];
-            m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-        if (lane == 0) s_red[warp] = m;
-        __syncthreads();
+    const uint32_t xbar = smem_base + kOffXBar;
+    if constexpr (PRE) {
         if (tid == 0) {
-            float a = 0.0f;
-            for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
-            // s = 2^(13 - floor(log2 a)) for a normal finite a, else 1; exponent clamped so that s and 1/s stay normal
-            int e = static_cast<int>((__float_as_uint(a) >> 23) & 0xFFu) - 127;
-            int se = (a > 0.0f && e < 128) ? 13 - e : 0;
-            se = max(-100, min(100, se));
-            s_scale[tk] = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
-            s_inv[tk] = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
+            mbar_init(xbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
+        if (tid < NTOK) s_inv[tid] = reinterpret_cast<const float*>(xstage + uint64_t{nb} * (8u * kSubStride + kSbStride))[tid];
         __syncthreads();
+    } else {
+        for (uint32_t tk = 0; tk < NTOK; ++tk) {
+            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+            float m = 0.0f;
+            for (uint32_t i = tid; i < cols / 4; i += kThreads) {
+                const float4 v = xr[i];
+                m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+            if (lane == 0) s_red[warp] = m;
+            __syncthreads();
+            if (tid == 0) {
+                float a = 0.0f;
+                for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
+                row_scale(a, s_scale[tk], s_inv[tk]);
+            }
+            __syncthreads();
+        }
     }
 
     // ---- B fragment pointers.  MMA columns are independent, so a lane whose column carries no token simply reads
@@ -243,32 +331,24 @@ gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __res
     for (uint32_t c0 = 0; c0 < nb; c0 += chunk_sb) {
         const uint32_t n_sb = min(chunk_sb, nb - c0);
         if (c0 != 0) __syncthreads();  // everyone is done reading the previous chunk
-        // ---- stage x[:, chunk] as fp16 hi / lo in slot order, and the sub-block sums ------------------------------------------
-        for (uint32_t tk = 0; tk < NTOK; ++tk) {
-            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride) + c0 * 64u;
-            const float s = s_scale[tk];
-            for (uint32_t qd = tid; qd < n_sb * 64u; qd += kThreads) {
-                float4 v = xr[qd];
-                v.x *= s; v.y *= s; v.z *= s; v.w *= s;
-                uint2 hi, lo;
-                split4(v, hi, lo);
-                const uint32_t sub = qd >> 3, in = qd & 7u;  // 8 quads per 32-element sub-block
-                uint8_t* dst = smem + kOffData + sub * kSubStride + (2 * tk) * 64u + in * 8u;
-                *reinterpret_cast<uint2*>(dst) = hi;
-                *reinterpret_cast<uint2*>(dst + 64) = lo;
-                float sum = (v.x + v.y) + (v.z + v.w);
-                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-                if (in == 0) {
-                    sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
-                    const __half h = __float2half_rn(sum);
-                    const __half l = __float2half_rn(sum - __half2float(h));
-                    uint8_t* sd = smem + kOffData + chunk_sb * 8u * kSubStride + (sub >> 3) * kSbStride + (2 * tk) * 16u + (sub & 7u) * 2u;
-                    *reinterpret_cast<__half*>(sd) = h;
-                    *reinterpret_cast<__half*>(sd + 16) = l;
-                }
+        // ---- x[:, chunk] as fp16 hi / lo in slot order, and the sub-block sums: fetched, or converted here -------------------------
+        if constexpr (PRE) {
+            if (tid == 0) {
+                const uint32_t xs_bytes = n_sb * 8u * kSubStride, sx_bytes = n_sb * kSbStride;
+                mbar_expect_tx(xbar, xs_bytes + sx_bytes);
+                bulk_g2s(smem_base + kOffData, xstage + uint64_t{c0} * 8u * kSubStride, xs_bytes, xbar);
+                bulk_g2s(smem_base + kOffData + chunk_sb * 8u * kSubStride, xstage + uint64_t{nb} * 8u * kSubStride + uint64_t{c0} * kSbStride,
+                         sx_bytes, xbar);
             }
+            if (!mbar_wait(xbar, (c0 / chunk_sb) & 1u)) {
+                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                lost = true;
+            }
+        } else {
+            for (uint32_t tk = 0; tk < NTOK; ++tk)
+                stage_row(smem + kOffData, smem + kOffData + chunk_sb * 8u * kSubStride,
+                          reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), s_scale[tk], c0, n_sb,
+                          kSubStride, kSbStride, 2 * tk * 64u, tid, kThreads);
         }
         __syncthreads();
         if (!active || lost) continue;
@@ -488,11 +568,7 @@ gemv_mma_q4k_m1_kernel(const __grid_constant__ CUtensorMap wmap, const float* __
         if (tid == 0) {
             float a = 0.0f;
             for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
-            int e = static_cast<int>((__float_as_uint(a) >> 23) & 0xFFu) - 127;
-            int se = (a > 0.0f && e < 128) ? 13 - e : 0;
-            se = max(-100, min(100, se));
-            s_scale[0] = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
-            s_inv[0] = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
+            row_scale(a, s_scale[0], s_inv[0]);
         }
         __syncthreads();
     }
@@ -688,14 +764,16 @@ int weight_map(const GemvCall& c, CUtensorMap* out) {
     return 0;
 }
 
-template <int NTOK, int KS, int NS>
+constexpr uint32_t kInternalNoScratch = HALO_CUDA_GEMV_FLAG_NO_SCRATCH;
+
+template <int NTOK, int KS, int NS, bool PRE>
 int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s) {
     constexpr int G = (NTOK + 3) / 4;
     const uint32_t nb = c.cols / 256u;
     const Plan p = plan_for(nb, NTOK, kOffRing + kRowBlocks * KS * NS * kSlotBytes, (KS - 1) * kRowBlocks * 32 * 2 * G * 4);
     static bool attr_set = false;
     if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_kernel<NTOK, KS, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_kernel<NTOK, KS, NS, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kSmemBudget)));
         attr_set = true;
     }
@@ -704,10 +782,19 @@ int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s)
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
     CUtensorMap wmap;
     if (int rc = weight_map(c, &wmap)) return rc;
+    const uint8_t* xstage = nullptr;
+    if constexpr (PRE) {
+        void* ws = nullptr;
+        const uint64_t bytes = uint64_t{nb} * (8u * 2 * NTOK * 64u + 2 * NTOK * 16u) + 64;
+        if (int rc = workspace(ctx, 0, bytes, s, &ws)) return rc;
+        stage_x_kernel<<<NTOK, 512, 0, s>>>(x, c.x_stride, static_cast<uint8_t*>(ws), nb, NTOK);
+        HC_CUDA(cudaGetLastError());
+        xstage = static_cast<const uint8_t*>(ws);
+    }
     cudaLaunchAttribute attr[1];
     const cudaLaunchConfig_t cfg = pdl_config(grid, kRowBlocks * KS * 32, p.smem_bytes, s, attr);
-    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<NTOK, KS, NS>, wmap, x, c.x_stride, y, c.y_stride, c.rows, nb, p.chunk_sb,
-                               ctx->error_word_dev));
+    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<NTOK, KS, NS, PRE>, wmap, x, c.x_stride, y, c.y_stride, c.rows, nb, p.chunk_sb,
+                               ctx->error_word_dev, xstage));
     return 0;
 }
 
@@ -722,7 +809,11 @@ int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, uint32_t n
 #define HALO_MMA_KS 2
 #define HALO_MMA_NS 3
 #endif
-        if (n == NTOK) return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS>(ctx, c, tok0, s);
+        if (n == NTOK) {
+            // batches convert x once into context scratch; single rows (and callers that forbid scratch) convert in the CTA
+            if (NTOK >= 2 && (c.flags & kInternalNoScratch) == 0) return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS, true>(ctx, c, tok0, s);
+            return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS, false>(ctx, c, tok0, s);
+        }
         return launch_tokens<NTOK + 1>(ctx, c, tok0, n, s);
     }
 }

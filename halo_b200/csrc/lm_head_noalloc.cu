@@ -76,6 +76,7 @@ extern "C" int halo_cuda_lm_head_noalloc(HaloCudaCtx* ctx, const HaloCudaLmHead*
     // flag is dropped so that the matmul stays inside the variants that take no context scratch.
     HaloCudaGemv g = a->gemv;
     g.flags &= ~HALO_CUDA_GEMV_FLAG_ALLOW_GEMM;
+    g.flags |= HALO_CUDA_GEMV_FLAG_NO_SCRATCH;  // batches convert x inside the matmul CTAs instead of in context scratch
     if (c.rows != 0) {
         if (int rc = halo_cuda_gemv(ctx, &g, stream)) return rc;
     }
