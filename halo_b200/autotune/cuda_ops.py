@@ -28,6 +28,9 @@ class CudaGemvTunable:
             copies = max(1, min(16, int(3 * 126e6 // max(wbytes, 1)) + 1))
         self.launches = max(launches_per_run, copies)
         self.wb = [be.import_host_readonly(w.reshape(-1)) for _ in range(copies)]
+        self.wr = []  # the same matrices in the repacked layout, where the type has one (read by gemv_mma_r only)
+        if wtype in (synth.Q6_K, synth.Q8_0, synth.Q4_0) and cols % 256 == 0:
+            self.wr = [be.repack(self.st, wtype, hb.TensorRef.of(b), rows, cols) for b in self.wb]
         self.xb = be.import_host_readonly(synth.activations(n_vec, cols, seed, 2))
         self.yb = be.allocate(n_vec * rows * 4)
         self.yref = be.allocate(n_vec * rows * 4)
@@ -38,7 +41,8 @@ class CudaGemvTunable:
         lib.halo_cuda_event_create(ctx, C.byref(self.e1))
         self.family = {i: fam for i, _, fam in be.variants(capi.OP_GEMV)}
 
-    def _args(self, wbuf, ybuf, variant: int) -> hb.GemvArgs:
+    def _args(self, i: int, ybuf, variant: int) -> hb.GemvArgs:
+        wbuf = self.wr[i] if variant == capi.GEMV_MMA_R else self.wb[i]
         return hb.GemvArgs(self.wtype, hb.TensorRef.of(wbuf), hb.TensorRef.of(self.xb), hb.TensorRef.of(ybuf), self.rows, self.cols,
                            self.n_vec, variant, allow_gemm=self.allow_gemm)
 
@@ -49,12 +53,14 @@ class CudaGemvTunable:
                 continue  # the fp16 GEMM numerics need the caller's consent (GemvArgs::allow_gemm)
             if name == "gemv_mma_m1" and self.n_vec > 4:
                 continue  # one launch per row: not a candidate for wide batches
+            if vid == capi.GEMV_MMA_R and not self.wr:
+                continue  # no repacked layout for this type
             out.append(Candidate.of(variant=vid))
         return out
 
     def _reference(self) -> np.ndarray:
         if self._ref is None:
-            self.be.gemv(self.st, self._args(self.wb[0], self.yref, capi.GEMV_EXACT8))
+            self.be.gemv(self.st, self._args(0, self.yref, capi.GEMV_EXACT8))
             ref = np.empty((self.n_vec, self.rows), np.float32)
             self.be.download(self.st, hb.TensorRef.of(self.yref), ref)
             self.st.wait()
@@ -63,7 +69,7 @@ class CudaGemvTunable:
 
     def validate(self, c: Candidate) -> bool:
         try:
-            self.be.gemv(self.st, self._args(self.wb[0], self.yb, c.get("variant")))
+            self.be.gemv(self.st, self._args(0, self.yb, c.get("variant")))
         except hb.HaloError:
             return False  # the variant does not take this type / shape
         y = np.empty((self.n_vec, self.rows), np.float32)
@@ -75,7 +81,7 @@ class CudaGemvTunable:
 
     def run(self, c: Candidate) -> float:
         lib, ctx, st = self.be.lib, self.be.ctx, self.st
-        structs = [self.be._gemv_struct(self._args(self.wb[i % len(self.wb)], self.yb, c.get("variant")), "MATMUL", False)
+        structs = [self.be._gemv_struct(self._args(i % len(self.wb), self.yb, c.get("variant")), "MATMUL", False)
                    for i in range(self.launches)]
         lib.halo_cuda_event_record(ctx, self.e0, st.handle)
         for g in structs:

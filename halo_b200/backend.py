@@ -281,7 +281,10 @@ class CudaBackend:
         if a.gates_n_v != 0:
             raise HaloError(capi.E_UNSUPPORTED, f"{op}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only")
         rb = C.c_uint64()
-        _check(self.lib.halo_cuda_row_bytes(a.wtype, a.cols, C.byref(rb)))
+        if a.variant_id == capi.GEMV_MMA_R:  # W is in the repacked row layout
+            _check(self.lib.halo_cuda_repacked_row_bytes(a.wtype, a.cols, C.byref(rb)))
+        else:
+            _check(self.lib.halo_cuda_row_bytes(a.wtype, a.cols, C.byref(rb)))
         g = capi.Gemv()
         g.wtype, g.variant_id = a.wtype, a.variant_id
         g.w = self._resolve(a.w, self._extent(a.rows, rb.value, a.w.row_stride), "w", op) or None
@@ -335,6 +338,23 @@ class CudaBackend:
         g.n_rows, g.cols, g.n_ids = a.n_rows, a.cols, a.n_ids
         g.status = status.ptr if status is not None else None
         _check(self.lib.halo_cuda_get_rows(self.ctx, C.byref(g), s.handle))
+
+    def repacked_row_bytes(self, wtype: int, cols: int) -> int:
+        rb = C.c_uint64()
+        _check(self.lib.halo_cuda_repacked_row_bytes(wtype, cols, C.byref(rb)))
+        return rb.value
+
+    def repack(self, s: Stream, wtype: int, src: TensorRef, rows: int, cols: int) -> Buffer:
+        """Raw GGUF rows -> a new read-only buffer in the repacked layout gemv_mma_r reads (what a loader does once per
+        weight, like tensor::gemv_repack for the reference's Vulkan backend)."""
+        raw = C.c_uint64()
+        _check(self.lib.halo_cuda_row_bytes(wtype, cols, C.byref(raw)))
+        prb = self.repacked_row_bytes(wtype, cols)
+        p = self._resolve(src, self._extent(rows, raw.value, src.row_stride), "src", "repack")
+        dst = self.allocate(max(rows * prb, 16), zero=False)
+        _check(self.lib.halo_cuda_repack_rows(self.ctx, wtype, p, src.row_stride, dst.ptr, 0, rows, cols, s.handle))
+        dst.writable = False
+        return dst
 
     def plan_set(self, wtype: int, rows: int, cols: int, n_vec_lo: int, n_vec_hi: int, variant_id: int) -> None:
         _check(self.lib.halo_cuda_plan_set(self.ctx, wtype, rows, cols, n_vec_lo, n_vec_hi, variant_id))

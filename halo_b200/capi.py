@@ -17,7 +17,7 @@ ERROR_NAMES = {E_MODEL: "Model", E_MEMORY: "Memory", E_BACKEND: "Backend", E_KER
                E_DEVICE: "Device", E_UNSUPPORTED: "Unsupported"}
 
 OP_GET_ROWS, OP_GEMV, OP_LM_HEAD = 0, 3, 14
-GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16, GEMV_MMA_M1 = 0, 1, 2, 3, 4, 5, 6
+GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16, GEMV_MMA_M1, GEMV_MMA_R = 0, 1, 2, 3, 4, 5, 6, 7
 FLAG_ALLOW_GEMM = 1
 
 
@@ -80,6 +80,8 @@ SYMBOLS = {
     "halo_cuda_lm_head": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_get_rows": (C.c_int, [_P, C.POINTER(GetRows), _P]),
     "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),
+    "halo_cuda_repacked_row_bytes": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "halo_cuda_repack_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P]),
 }
 
 _lib = None

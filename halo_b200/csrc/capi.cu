@@ -19,6 +19,7 @@ constexpr HaloCudaVariant kGemvVariants[] = {
     {HALO_CUDA_GEMM_TCGEN05_F16, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_f16"},
     {HALO_CUDA_GEMM_TCGEN05_BF16, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_bf16"},
     {HALO_CUDA_GEMV_MMA_M1, HALO_CUDA_OP_GEMV, 3, "gemv_mma_m1"},
+    {HALO_CUDA_GEMV_MMA_R, HALO_CUDA_OP_GEMV, 5, "gemv_mma_r"},
 };
 constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
 constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
@@ -89,6 +90,11 @@ int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCa
     c->n_vec = a->n_vec;
     c->flags = a->flags;
     c->row_bytes = uint64_t{a->cols} / ti.block_elems * ti.block_bytes;
+    if (a->variant_id == HALO_CUDA_GEMV_MMA_R) {  // the W operand is in the repacked layout: its rows have another size
+        if (repacked_row_bytes(a->wtype, 256) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "%s: gemv_mma_r takes repacked Q4_0 / Q8_0 / Q6_K weights", op);
+        if (a->cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "%s: %u elements is not a multiple of the repacked group size 256", op, a->cols);
+        c->row_bytes = repacked_row_bytes(a->wtype, a->cols);
+    }
     c->w = static_cast<const uint8_t*>(a->w);
     c->x = a->x;
     c->y = a->y;
@@ -170,6 +176,10 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
             if (!gemv_mma_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_m1 needs Q4_K weights in dense 16-byte-aligned rows");
             return launch_gemv_mma_m1(ctx, c, s);
+        case HALO_CUDA_GEMV_MMA_R:
+            if (!gemv_mma_r_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_r needs repacked 16-byte-aligned rows, cols %% 256 == 0 and 16-byte-aligned x");
+            return launch_gemv_mma_r(ctx, c, s);
         case HALO_CUDA_GEMM_TCGEN05_F16:
         case HALO_CUDA_GEMM_TCGEN05_BF16:
             if (!gemm_tcgen05_supports(c))
@@ -469,6 +479,30 @@ int halo_cuda_plan_clear(HaloCudaCtx* ctx) {
     if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
     ctx->plan.clear();
     return 0;
+}
+
+int halo_cuda_repacked_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes) {
+    if (bytes == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    if (repacked_row_bytes(wtype, 256) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "weight type id %u has no repacked layout", wtype);
+    if (cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "%llu elements is not a multiple of the repacked group size 256", (unsigned long long)cols);
+    *bytes = repacked_row_bytes(wtype, cols);
+    return 0;
+}
+
+int halo_cuda_repack_rows(HaloCudaCtx* ctx, uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride,
+                          uint32_t rows, uint32_t cols, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    uint64_t raw = 0, packed = 0;
+    if (int rc = halo_cuda_row_bytes(wtype, cols, &raw)) return rc;
+    if (int rc = halo_cuda_repacked_row_bytes(wtype, cols, &packed)) return rc;
+    if (rows == 0 || cols == 0) return 0;
+    if (src == nullptr || dst == nullptr) return fail(HALO_CUDA_E_KERNEL, "repack: null pointer");
+    const uint64_t ss = src_stride != 0 ? src_stride : raw, ds = dst_stride != 0 ? dst_stride : packed;
+    if ((rows > 1 && (ss < raw || ds < packed)) || reinterpret_cast<uintptr_t>(dst) % 16 != 0 || ds % 16 != 0)
+        return fail(HALO_CUDA_E_KERNEL, "repack: strides below the row size, or a destination that is not 16-byte aligned");
+    if (ranges_overlap(dst, (uint64_t{rows} - 1) * ds + packed, src, (uint64_t{rows} - 1) * ss + raw))
+        return fail(HALO_CUDA_E_KERNEL, "repack: output dst overlaps operand src");
+    return launch_repack(wtype, src, ss, dst, ds, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
 size_t halo_cuda_last_error(char* buf, size_t len) {

@@ -31,192 +31,14 @@
 #include <cstring>
 
 #include "internal.h"
+#include "mma_common.cuh"
 
 namespace halo_cuda {
 
 namespace {
 
-#ifndef HALO_MMA_ROWBLOCKS
-#define HALO_MMA_ROWBLOCKS 8
-#endif
-constexpr int kRowBlocks = HALO_MMA_ROWBLOCKS;  // 16-row blocks per CTA (8: a CTA covers 128 W rows)
-constexpr uint32_t kSmemBudget = 220 * 1024;
-#ifndef HALO_MMA_CHAINS
-#define HALO_MMA_CHAINS 2
-#endif
-constexpr int kChains = HALO_MMA_CHAINS;  // part of a row's arithmetic: the same for every token count
+using namespace mma;
 
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-/// The first MMA of a chain: C = 0 comes from the zero register, no accumulator clearing needed.
-__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
-__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hsub2_bits(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
-/// fp16 hi / lo split of four scaled activations, packed in MMA slot order (e0, e2 | e1, e3).
-__device__ __forceinline__ void split4(float4 v, uint2& hi, uint2& lo) {
-    const __half h0 = __float2half_rn(v.x), h1 = __float2half_rn(v.y), h2 = __float2half_rn(v.z), h3 = __float2half_rn(v.w);
-    const __half l0 = __float2half_rn(v.x - __half2float(h0)), l1 = __float2half_rn(v.y - __half2float(h1));
-    const __half l2 = __float2half_rn(v.z - __half2float(h2)), l3 = __float2half_rn(v.w - __half2float(h3));
-    hi.x = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h2)) << 16);
-    hi.y = static_cast<uint32_t>(__half_as_ushort(h1)) | (static_cast<uint32_t>(__half_as_ushort(h3)) << 16);
-    lo.x = static_cast<uint32_t>(__half_as_ushort(l0)) | (static_cast<uint32_t>(__half_as_ushort(l2)) << 16);
-    lo.y = static_cast<uint32_t>(__half_as_ushort(l1)) | (static_cast<uint32_t>(__half_as_ushort(l3)) << 16);
-}
-
-
-/// Power-of-two scale of one x row from its largest magnitude a: s = 2^(13 - floor(log2 a)) for a normal finite a, else 1;
-/// the exponent is clamped so that s and 1/s stay normal.
-__device__ __forceinline__ void row_scale(float a, float& s, float& inv) {
-    int e = static_cast<int>((__float_as_uint(a) >> 23) & 0xFFu) - 127;
-    int se = (a > 0.0f && e < 128) ? 13 - e : 0;
-    se = max(-100, min(100, se));
-    s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
-    inv = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
-}
-
-/// Converts super-blocks [c0, c0 + n_sb) of one x row into MMA-fragment order: fp16 hi / lo of x * s per 32-element
-/// sub-block (`sub_stride` bytes apart, this token's columns at byte `col_off`), and the sub-block sums / 32 as fp16
-/// hi / lo (`sb_stride` bytes per super-block, this token's columns at byte `col_off / 4`).  Called by every thread of
-/// a CTA (`nthreads` a multiple of 32); the arithmetic does not depend on who calls it or on the chunking.
-__device__ __forceinline__ void stage_row(uint8_t* xs, uint8_t* sx, const float* xrow, float s, uint32_t c0, uint32_t n_sb,
-                                          uint32_t sub_stride, uint32_t sb_stride, uint32_t col_off, uint32_t tid, uint32_t nthreads) {
-    const float4* xr = reinterpret_cast<const float4*>(xrow) + c0 * 64u;
-    for (uint32_t qd = tid; qd < n_sb * 64u; qd += nthreads) {
-        float4 v = xr[qd];
-        v.x *= s; v.y *= s; v.z *= s; v.w *= s;
-        uint2 hi, lo;
-        split4(v, hi, lo);
-        const uint32_t sub = qd >> 3, in = qd & 7u;  // 8 quads per 32-element sub-block
-        uint8_t* dst = xs + sub * sub_stride + col_off + in * 8u;
-        *reinterpret_cast<uint2*>(dst) = hi;
-        *reinterpret_cast<uint2*>(dst + 64) = lo;
-        float sum = (v.x + v.y) + (v.z + v.w);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-        if (in == 0) {
-            sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
-            const __half h = __float2half_rn(sum);
-            const __half l = __float2half_rn(sum - __half2float(h));
-            uint8_t* sd = sx + (sub >> 3) * sb_stride + (col_off >> 2) + (sub & 7u) * 2u;
-            *reinterpret_cast<__half*>(sd) = h;
-            *reinterpret_cast<__half*>(sd + 16) = l;
-        }
-    }
-}
-
-/// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on an mbarrier.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-/// Pre-staging kernel for batches: one CTA per x row converts the whole row once into global scratch laid out exactly
-/// like the in-kernel staging area ([sub-block][column][64 B], then [super-block][column][16 B], then 1/s per row), so
-/// that the matmul CTAs fetch their K chunks with bulk copies instead of each converting x again.
-__global__ void __launch_bounds__(512) stage_x_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
-                                                      uint32_t nb, uint32_t n_tok) {
-    __shared__ float red[16];
-    __shared__ float sc[2];
-    const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t cols = nb * 256u, kcols = 2 * n_tok;
-    const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-    float m = 0.0f;
-    for (uint32_t i = tid; i < cols / 4; i += 512) {
-        const float4 v = reinterpret_cast<const float4*>(xrow)[i];
-        m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    if (tid == 0) {
-        float a = 0.0f;
-        for (int i = 0; i < 16; ++i) a = fmaxf(a, red[i]);
-        row_scale(a, sc[0], sc[1]);
-    }
-    __syncthreads();
-    uint8_t* xs = scratch;
-    uint8_t* sx = scratch + uint64_t{nb} * 8u * kcols * 64u;
-    float* inv = reinterpret_cast<float*>(sx + uint64_t{nb} * kcols * 16u);
-    stage_row(xs, sx, xrow, sc[0], 0, nb, kcols * 64u, kcols * 16u, 2 * tk * 64u, tid, 512);
-    if (tid == 0) inv[tk] = sc[1];
-}
-
-// ---- shared-memory weight ring -------------------------------------------------------------------------------------
-// Each warp streams its own rows: per pipeline stage one TMA tile copy (cp.async.bulk.tensor.2d over a tensor map of
-// the weight matrix as rows of bytes) brings the 144-byte super-block of its 16 W rows into a 16 x 160-byte slot and
-// completes on that stage's mbarrier.  The box is 160 bytes wide: the 16 extra bytes (the next block's header, or
-// zero fill past the row end) only pad the slot so that the fragment reads below are bank-conflict-free.  Rows past
-// the end of the matrix are zero-filled by the copy engine.  Nothing but the owning warp touches a slot, so the
-// only synchronisation is the mbarrier (data arrived) and program order (slot consumed before it is refilled).
-constexpr uint32_t kSlotRow = 160, kSlotBytes = 16 * kSlotRow, kStageTx = kSlotBytes;
-constexpr uint32_t kWaitSpins = 1u << 14;  // try_wait polls (each blocks for a short hardware-defined time) before a stage is declared lost
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-/// Bounded wait: false after kWaitSpins polls (the caller then raises the error word and leaves).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitSpins; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-/// One tile of the tensor map: bytes [x, x + 160) of rows [y, y + 16).  x must be a multiple of 16.
-__device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                 "l"(map), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-
-// Shared-memory layout (byte offsets from the dynamic base), for `ncols` = 2 * tokens columns:
-//   [0, 16) unused | scales | partial maxima | mbarriers | weight ring |
-//   xs:  [sub-block][column][64 B] fp16 x in slot order    sx: [super-block][column][16 B] sub-block sums / 32
-constexpr uint32_t kOffXBar = 0, kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
-constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eight bytes per warp and stage (<= 6 stages)
 
 // NTOK: x rows of this launch (1..16), i.e. 2 * NTOK B columns in G = ceil(NTOK / 4) MMA column groups.
 // KS: warps sharing one 16-row block; warp ks takes the super-blocks sb = ks (mod KS), a split that depends on
@@ -785,7 +607,7 @@ int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s)
     const uint8_t* xstage = nullptr;
     if constexpr (PRE) {
         void* ws = nullptr;
-        const uint64_t bytes = uint64_t{nb} * (8u * 2 * NTOK * 64u + 2 * NTOK * 16u) + 64;
+        const uint64_t bytes = stage_scratch_bytes(nb, NTOK);
         if (int rc = workspace(ctx, 0, bytes, s, &ws)) return rc;
         stage_x_kernel<<<NTOK, 512, 0, s>>>(x, c.x_stride, static_cast<uint8_t*>(ws), nb, NTOK);
         HC_CUDA(cudaGetLastError());

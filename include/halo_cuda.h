@@ -57,7 +57,8 @@ extern "C" {
 #define HALO_CUDA_GEMM_TCGEN05_F16 4  /* prefill: dequant to fp16 in shared memory + tcgen05 MMA */
 #define HALO_CUDA_GEMM_TCGEN05_BF16 5 /* same with bf16 operands */
 #define HALO_CUDA_GEMV_MMA_M1 6       /* tensor-core single-row specialist (one launch per x row) */
-#define HALO_CUDA_GEMV_VARIANT_MAX 6
+#define HALO_CUDA_GEMV_MMA_R 7        /* tensor-core skinny kernel over REPACKED Q6_K / Q8_0 / Q4_0 rows (halo_cuda_repack_rows) */
+#define HALO_CUDA_GEMV_VARIANT_MAX 7
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
 #define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch (same results, batches run slower) */
@@ -176,6 +177,14 @@ int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t
                        uint32_t variant_id);
 int halo_cuda_plan_clear(HaloCudaCtx* ctx);
 size_t halo_cuda_last_error(char* buf, size_t len);
+/* The repacked row layout of variant HALO_CUDA_GEMV_MMA_R: a byte permutation (plus padding for Q6_K) of every 256-weight
+ * group that makes the rows fetchable by the copy engine, the counterpart of tensor::gemv_repack
+ * (include/halo/tensor/repack.h:11-36) and of the kGemvRepacked variant (backend.h:178-183).  cols must be a multiple
+ * of 256.  halo_cuda_repacked_row_bytes gives the size of a repacked row (E_UNSUPPORTED for types without one);
+ * halo_cuda_repack_rows converts `rows` raw GGUF rows (any alignment) into 16-byte aligned repacked rows on the device. */
+int halo_cuda_repacked_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes);
+int halo_cuda_repack_rows(HaloCudaCtx* ctx, uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride,
+                          uint32_t rows, uint32_t cols, HaloCudaStream stream);
 
 /* ---- the operators ------------------------------------------------------------------------------ */
 int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);

@@ -115,9 +115,9 @@ bool bitwise(const std::vector<float>& a, const std::vector<float>& b) {
 
 void test_registry(Pair& p, Report& r) {
     const auto v = p.gpu->variants(hb::OpId::Gemv);
-    const char* names[] = {"gemv_exact8", "gemv_warp_f32", "gemv_mma_f16x2", "gemm_tcgen05_f16", "gemm_tcgen05_bf16", "gemv_mma_m1"};
-    r.expect(v.size() == 6, "MATMUL has six registered variants");
-    for (std::size_t i = 0; i < v.size() && i < 6; ++i)
+    const char* names[] = {"gemv_exact8", "gemv_warp_f32", "gemv_mma_f16x2", "gemm_tcgen05_f16", "gemm_tcgen05_bf16", "gemv_mma_m1", "gemv_mma_r"};
+    r.expect(v.size() == 7, "MATMUL has seven registered variants");
+    for (std::size_t i = 0; i < v.size() && i < 7; ++i)
         r.expect(v[i].id == i + 1 && v[i].name == names[i] && v[i].op == hb::OpId::Gemv, std::format("variant id {} is {}", i + 1, names[i]));
     r.expect(code_of([&] { (void)p.gpu->variants(hb::OpId::RmsNorm); }) == static_cast<int>(ErrorCode::Unsupported), "variants(RMS_NORM) is Unsupported");
     r.expect(p.gpu->kind() == hb::kKindCuda && !p.gpu->lost(), "kind and lost()");
