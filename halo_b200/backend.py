@@ -102,6 +102,9 @@ class GemvArgs:
     norm_w: TensorRef = field(default_factory=TensorRef)
     allow_gemm: bool = False
     gates_n_v: int = 0
+    #: cuda extension: the call may not touch context scratch (the statically partitioned kernels; what
+    #: halo_cuda_lm_head_noalloc computes)
+    no_scratch: bool = False
 
 
 @dataclass
@@ -294,7 +297,7 @@ class CudaBackend:
         g.y = self._resolve(a.y, self._extent(a.n_vec, a.rows * 4, a.y.row_stride), "y", op, write=True) or None
         g.y_stride = a.y.row_stride
         g.rows, g.cols, g.n_vec = a.rows, a.cols, a.n_vec
-        g.flags = capi.FLAG_ALLOW_GEMM if a.allow_gemm else 0
+        g.flags = (capi.FLAG_ALLOW_GEMM if a.allow_gemm else 0) | (capi.FLAG_NO_SCRATCH if a.no_scratch else 0)
         return g
 
     def gemv(self, s: Stream, a: GemvArgs) -> None:

@@ -22,7 +22,7 @@ LIB = PKG / "libhalo_cuda.so"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wextra,-Wno-unused-parameter", f"-I{INCLUDE}", f"-I{CSRC}",
-          "--expt-relaxed-constexpr", "-Xptxas", "-v" if os.environ.get("HALO_PTXAS_V") else "-warn-spills"]
+          "--expt-relaxed-constexpr", *os.environ.get("HALO_NVCC_EXTRA", "").split(), "-Xptxas", "-v" if os.environ.get("HALO_PTXAS_V") else "-warn-spills"]
 
 
 def _newer(src: Path, dst: Path, deps: list[Path]) -> bool:

@@ -61,7 +61,7 @@ int enter(HaloCudaCtx* ctx) {
     return 0;
 }
 
-int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out) {
+int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out, bool zeroed) {
     if (bytes > ctx->workspace_bytes[slot]) {
         // Work already enqueued may still read the old block: drain before releasing it.
         HC_CUDA(cudaStreamSynchronize(stream));
@@ -71,6 +71,7 @@ int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, v
         const uint64_t want = (bytes + (1u << 20) - 1) & ~uint64_t{(1u << 20) - 1};
         HC_CUDA(cudaMalloc(&ctx->workspace[slot], want));
         ctx->workspace_bytes[slot] = want;
+        if (zeroed) HC_CUDA(cudaMemsetAsync(ctx->workspace[slot], 0, want, stream));
     }
     *out = ctx->workspace[slot];
     return 0;
@@ -171,7 +172,10 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
         case HALO_CUDA_GEMV_MMA_F16X2:
             if (!gemv_mma_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_f16x2 needs Q4_K weights in dense 16-byte-aligned rows");
-            return launch_gemv_mma(ctx, c, s);
+            // context scratch holds the balanced kernels' partial sums and staged x; calls that may not touch it
+            // take the statically partitioned kernel (same arithmetic per tile, another summation order over K)
+            if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return launch_gemv_mma(ctx, c, s);
+            return launch_gemv_sk_q4k(ctx, c, s);
         case HALO_CUDA_GEMV_MMA_M1:
             if (!gemv_mma_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_m1 needs Q4_K weights in dense 16-byte-aligned rows");

@@ -1,0 +1,196 @@
+// Host side of the balanced skinny kernels: tensor map, scratch, kernel choice.  Included by one .cu per weight format
+// (so the formats compile in parallel); each defines its launch_gemv_sk_<format>().
+#pragma once
+#include "gemv_mma_sk.cuh"
+
+namespace halo_cuda {
+namespace sk {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+/// The weight matrix as a 2-D tensor {row elements, rows} with row pitch w_stride, tiled (slot pitch) x 16 rows.
+/// Tiles reaching past the end of a row or of the matrix are zero-filled by the copy engine.
+template <class F>
+int weight_map(const GemvCall& c, CUtensorMap* out) {
+    static EncodeTiledFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        HC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail(HALO_CUDA_E_BACKEND, "cuTensorMapEncodeTiled is not available");
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {c.row_bytes / F::kMapElemBytes, c.rows};
+    const cuuint64_t strides[1] = {c.w_stride};
+    const cuuint32_t box[2] = {F::kBoxInner, 16};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(out, F::kMapElemBytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2,
+                              const_cast<uint8_t*>(c.w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(HALO_CUDA_E_KERNEL, "MATMUL: cannot describe the weight matrix to the copy engine (CUresult %d)", (int)r);
+    return 0;
+}
+
+inline cudaLaunchConfig_t pdl_config(uint32_t grid, uint32_t smem, cudaStream_t s, cudaLaunchAttribute* attr) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kSkWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+
+/// The partition of one call: which K slicing, the column ranges of the CTAs, and the scratch of the reduction.
+struct Geometry {
+    uint32_t nb, ks;
+    SkTable table;
+    void *counters, *partials;
+};
+
+/// Columns one CTA walks at most under `ks` slices with whole units per CTA (0: not possible) and with an even split.
+/// The choice is a function of (rows, cols, SM count) alone, so every batch size of a shape gets the same partition.
+inline void plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool allow_slices, Geometry* g) {
+    const uint64_t n_rb = (uint64_t{rows} + 15) / 16;
+    sms = std::min(sms, kSkMaxCtas);
+    // candidate A: 2 slices, whole units per CTA.  candidate B: 1 slice, even split of the columns, where a CTA pays
+    // roughly three columns' time for the cross-CTA reduction of the units its range cuts.
+    const uint64_t units_a = (n_rb + 7) / 8, cpu_a = (nb + 1) / 2, parts_a = std::min<uint64_t>(sms, units_a);
+    const uint64_t time_a = (units_a + parts_a - 1) / parts_a * cpu_a;
+    const uint64_t units_b = (n_rb + 15) / 16, cols_b = units_b * nb, parts_b = std::min<uint64_t>(sms, cols_b);
+    const uint64_t time_b = (cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : 3);
+    SkTable& t = g->table;
+    if (allow_slices && nb >= 2 && time_a <= time_b) {
+        g->ks = 2;
+        t.parts = static_cast<uint32_t>(parts_a);
+        t.cols_per_unit = static_cast<uint32_t>(cpu_a);
+        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * units_a / parts_a * cpu_a);
+    } else {
+        g->ks = 1;
+        t.parts = static_cast<uint32_t>(parts_b);
+        t.cols_per_unit = nb;
+        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * cols_b / parts_b);
+    }
+}
+
+template <class F, int NTOK>
+int geometry(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s, Geometry* g) {
+    constexpr int G = (NTOK + 3) / 4;
+    g->nb = c.cols / 256u;
+    const uint64_t n_rb = (uint64_t{c.rows} + 15) / 16;
+    if (n_rb * g->nb >= (1ull << 30)) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: more than 2^30 (16-row, 256-column) tiles");
+    plan_partition(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), F::kAllowSlices, g);
+    if (int rc = workspace(ctx, 2, n_rb * 4, s, &g->counters, /*zeroed=*/true)) return rc;
+    return workspace(ctx, 3, uint64_t{g->table.parts} * 2 * kSkWarps * 32 * 2 * G * 4, s, &g->partials);
+}
+
+template <class F, int NTOK, int NS, int KS>
+int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
+    constexpr bool PRE = NTOK >= 2;
+    using L = SkLayout<F, NTOK, NS, KS>;
+    if constexpr (L::kOffData >= kSmemBudget) {
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: ring of %d stages does not fit", NS);
+    } else {
+        const uint32_t smem_bytes = L::kOffData + g.nb * L::kRec;
+        static bool attr_set = false;
+        if (!attr_set) {
+            HC_CUDA(cudaFuncSetAttribute(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmemBudget)));
+            attr_set = true;
+        }
+        const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
+        float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
+        CUtensorMap wmap;
+        if (int rc = weight_map<F>(c, &wmap)) return rc;
+        const uint8_t* xstage = nullptr;
+        if constexpr (PRE) {
+            void* ws = nullptr;
+            if (int rc = workspace(ctx, 0, stage_rec_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
+            stage_x_rec_kernel<<<NTOK, 512, 0, s>>>(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK);
+            HC_CUDA(cudaGetLastError());
+            xstage = static_cast<const uint8_t*>(ws);
+        }
+        cudaLaunchAttribute attr[1];
+        const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
+        HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb,
+                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage));
+        return 0;
+    }
+}
+
+template <class F, int NTOK, int KS>
+int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
+    // the deepest ring that leaves room for two columns of x at the widest batch
+    constexpr int NS = SkLayout<F, 16, 3, KS>::kOffData + 2 * KS * XRec<16>::kBytes <= kSmemBudget ? 3 : 2;
+    using L = SkLayout<F, NTOK, NS, KS>;
+    constexpr uint32_t kXSlot = KS * L::kRec;
+    static_assert(L::kOffData + 2 * kXSlot <= kSmemBudget, "two columns of x must fit next to the ring");
+    const uint32_t xs_cols = std::min<uint32_t>(kMaxXSlots / 2, (kSmemBudget - L::kOffData) / kXSlot / 2);
+    const uint32_t smem_bytes = L::kOffData + 2 * xs_cols * kXSlot;
+    static bool attr_set = false;
+    if (!attr_set) {
+        HC_CUDA(cudaFuncSetAttribute(gemv_sk_streamed_kernel<F, NTOK, NS, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kSmemBudget)));
+        attr_set = true;
+    }
+    const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
+    float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
+    CUtensorMap wmap;
+    if (int rc = weight_map<F>(c, &wmap)) return rc;
+    void* ws = nullptr;
+    if (int rc = workspace(ctx, 0, stage_rec_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
+    stage_x_rec_kernel<<<NTOK, 512, 0, s>>>(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK);
+    HC_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
+    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_streamed_kernel<F, NTOK, NS, KS>, wmap, g.table, y, c.y_stride, c.rows, g.nb, xs_cols,
+                               static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev,
+                               static_cast<const uint8_t*>(ws)));
+    return 0;
+}
+
+constexpr int kResidentMaxTok = 4;  // larger batches always stream x
+
+/// n rows starting at tok0: the resident kernel with the deepest ring that leaves room for x, else the streamed one.
+template <class F, int NTOK, int KS>
+int launch_sliced(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
+    if constexpr (NTOK <= kResidentMaxTok) {
+        const uint64_t x_bytes = uint64_t{g.nb} * XRec<NTOK>::kBytes;
+        if (SkLayout<F, NTOK, 3, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, 3, KS>(ctx, c, g, tok0, s);
+        if (SkLayout<F, NTOK, 2, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, 2, KS>(ctx, c, g, tok0, s);
+    }
+    return launch_streamed<F, NTOK, KS>(ctx, c, g, tok0, s);
+}
+
+template <class F, int NTOK>
+int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, uint32_t n, cudaStream_t s) {
+    if constexpr (NTOK > 16) {
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: token tile of %u", n);
+    } else {
+        if (n != NTOK) return launch_tokens<F, NTOK + 1>(ctx, c, tok0, n, s);
+        Geometry g{};
+        if (int rc = geometry<F, NTOK>(ctx, c, s, &g)) return rc;
+        if constexpr (F::kAllowSlices) {
+            if (g.ks == 2) return launch_sliced<F, NTOK, 2>(ctx, c, g, tok0, s);
+        }
+        return launch_sliced<F, NTOK, 1>(ctx, c, g, tok0, s);
+    }
+}
+
+template <class F>
+int launch_format(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
+    // Token tiles of 16 (four MMA column groups); the remainder takes the smallest instantiation that holds it.
+    for (uint32_t t0 = 0; t0 < c.n_vec; t0 += 16) {
+        const uint32_t n = c.n_vec - t0 < 16 ? c.n_vec - t0 : 16;
+        if (int rc = launch_tokens<F, 1>(ctx, c, t0, n, s)) return rc;
+    }
+    return 0;
+}
+
+}  // namespace sk
+}  // namespace halo_cuda

@@ -41,9 +41,11 @@ struct HaloCudaCtx {
     bool lost = false;
     // Scratch for kernels that need global memory beyond their operands (activation staging, split-K
     // partials).  Grown on demand, reused in stream order; one thread drives a context.
-    // Slot 0 serves the matmul kernels, slot 1 the LM head (its logits and argmax partials live across a matmul).
-    void* workspace[2] = {nullptr, nullptr};
-    uint64_t workspace_bytes[2] = {0, 0};
+    // Slot 0 serves the matmul kernels, slot 1 the LM head (its logits and argmax partials live across a matmul),
+    // slot 2 the row-block counters of the balanced kernels (zeroed when allocated, left zeroed by every kernel),
+    // slot 3 their partial sums.
+    void* workspace[4] = {nullptr, nullptr, nullptr, nullptr};
+    uint64_t workspace_bytes[4] = {0, 0, 0, 0};
     std::vector<halo_cuda::PlanEntry> plan;
     // One word of mapped pinned host memory that kernels OR error bits into (bit 0: a bounded device-side wait
     // expired).  The host reads it after every stream wait; a set bit marks the context lost.
@@ -55,8 +57,9 @@ namespace halo_cuda {
 
 /// Makes ctx's device current; E_API for a null ctx, E_DEVICE once the context is lost.
 int enter(HaloCudaCtx* ctx);
-/// Returns ctx scratch of at least `bytes` (grows with cudaMalloc; earlier contents are dropped).
-int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out);
+/// Returns ctx scratch of at least `bytes` (grows with cudaMalloc; earlier contents are dropped; `zeroed` clears a
+/// newly allocated block in stream order).
+int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out, bool zeroed = false);
 
 /// A validated gemv: strides resolved to bytes, geometry checked.
 struct GemvCall {
@@ -78,6 +81,10 @@ int launch_gemv_mma(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_mma_m1(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_mma_supports(const GemvCall& c);
 int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s);
+int launch_gemv_sk_q4k(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_sk_q40r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_sk_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_sk_q6kr(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_mma_r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout

@@ -201,5 +201,80 @@ __device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* ma
 constexpr uint32_t kOffXBar = 0, kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
 constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eight bytes per warp and stage (<= 6 stages)
 
+// ---- balanced work partition -----------------------------------------------------------------------------------------
+// The work of a skinny matmul is the grid of items (16-row block, super-block).  A CTA has kSkWarps = 16 warps,
+// arranged as R row blocks x KS interleaved K slices (R * KS = 16): warp (r, ks) of a CTA working on unit u owns row
+// block u * R + r and, of that block's super-blocks, sb = k * KS + ks for the unit's columns k = 0 .. ceil(nb / KS) - 1.
+// The columns of all units form one sequence (unit-major); a persistent grid of at most one CTA per SM cuts it into
+// contiguous ranges, one per CTA, given by a table the host computes from (rows, cols, SM count) alone:
+//   * whole units per CTA when that keeps the SMs evenly loaded (no row block is shared between CTAs), else
+//   * an even split of the columns, where a unit cut by a range boundary is finished by whichever of its CTAs
+//     arrives last: each stores its partial sums, bumps the row block's counter, and the last one adds the partials
+//     IN CTA ORDER, so the sum does not depend on arrival order.
+// Within a CTA the KS slices of a row block are added in ks order through shared memory.  All warps of a CTA walk the
+// same columns, so they can share a stream of x.  Nothing here depends on the batch size.
+constexpr uint32_t kSkWarps = 16;   // warps per CTA of the persistent kernels
+constexpr uint32_t kSkMaxCtas = 160;
+
+struct SkTable {
+    uint32_t parts;                   // CTAs of the grid
+    uint32_t cols_per_unit;           // ceil(nb / KS)
+    uint32_t start[kSkMaxCtas + 1];   // CTA c owns columns [start[c], start[c + 1])
+};
+
+/// Sums of one row block (this lane: rows g and g + 8 for its G token columns) -> y: directly when this CTA covered
+/// all of the unit's columns, else through the partial store and the last-arriver reduction.  `part` holds 2 records
+/// per CTA and row-block slot r (record 0: the unit the CTA's range starts in, record 1: the unit it ends in) of
+/// 32 lanes x 2G floats; `counters` one zeroed word per row block, left zeroed.
+template <int G, int NTOK, int R>
+__device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
+                                         uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane) {
+    const uint32_t g = lane >> 2, t = lane & 3u, rb = unit * R + r;
+    const uint32_t u_lo = unit * tb.cols_per_unit, u_hi = u_lo + tb.cols_per_unit;  // the unit's columns
+    uint32_t c_lo = cta, c_hi = cta;
+    while (c_lo > 0 && tb.start[c_lo] > u_lo) --c_lo;
+    while (c_hi + 1 < tb.parts && tb.start[c_hi + 1] < u_hi) ++c_hi;
+    auto record = [&](uint32_t c) {
+        const uint32_t rec = tb.start[c] >= u_lo ? 0u : 1u;  // the range starts inside this unit, or ends in it
+        return reinterpret_cast<float2*>(part) + (((uint64_t{c} * 2 + rec) * R + r) * 32 + lane) * G;
+    };
+    float sum[G][2];
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi) sum[gi][0] = acc[gi][0], sum[gi][1] = acc[gi][1];
+    if (c_lo != c_hi) {
+        float2* mine = record(cta);
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) __stcg(mine + gi, make_float2(acc[gi][0], acc[gi][1]));
+        __threadfence();
+        __syncwarp();
+        uint32_t old = 0;
+        if (lane == 0) old = atomicAdd(counters + rb, 1u);
+        old = __shfl_sync(0xFFFFFFFFu, old, 0);
+        if (old != c_hi - c_lo) return;  // another CTA will finish this block
+        __threadfence();
+        for (uint32_t c = c_lo; c <= c_hi; ++c) {
+            const float2* p = record(c);
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                const float2 v = __ldcg(p + gi);
+                if (c == c_lo) sum[gi][0] = v.x, sum[gi][1] = v.y;
+                else sum[gi][0] += v.x, sum[gi][1] += v.y;
+            }
+        }
+        if (lane == 0) counters[rb] = 0;
+    }
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi) {
+        const uint32_t tk = 4u * gi + t;
+        if (tk < NTOK) {
+            const float inv = s_inv[tk];
+            float* yr = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{tk} * y_stride);
+            const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
+            if (n0 < rows) yr[n0] = sum[gi][0] * inv;
+            if (n1 < rows) yr[n1] = sum[gi][1] * inv;
+        }
+    }
+}
+
 }  // namespace mma
 }  // namespace halo_cuda

@@ -1,0 +1,399 @@
+// Weight formats of the balanced tensor-core skinny kernels: for each, how one 16-row x 256-column tile ("item") sits
+// in a ring slot and the arithmetic that folds it into the row sums.  The kernels around these (gemv_mma_sk.cu) only
+// move data and walk the partition.
+//
+// Shared arithmetic: A holds unsigned quant codes as fp16 subnormals (code * 2^-24, exact), B holds x as fp16 hi + lo
+// columns, fp32 accumulation in mma.sync m16n8k16; a lane (g = lane / 4, t = lane % 4) owns rows g and g + 8 of the
+// tile and the B columns 2t, 2t + 1 of every 8-column group.
+//
+// x record of one super-block for NTOK rows (what stage_row_rec writes and an item reads), kRec = 1120 * NTOK bytes:
+//   [sub-block 0..7][column 0..2*NTOK-1][64 B]   fp16 hi (even column) / lo (odd column) of x * s, in quads of 8 bytes
+//   [column][16 B]                               sum of each 32-element sub-block / 32 as fp16 hi / lo (Q4_K min term)
+//   [16-element group 0..15][row] fp32           sums of x * s over 16 elements (zero points of the other formats)
+#pragma once
+#include "halo_cuda.h"
+#include "mma_common.cuh"
+
+namespace halo_cuda {
+namespace mma {
+
+template <int NTOK>
+struct XRec {
+    static constexpr uint32_t kCols = 2 * NTOK, kSubStride = kCols * 64u, kSbStride = kCols * 16u, kSx16Bytes = 64u * NTOK;
+    static constexpr uint32_t kOffSums = 8u * kSubStride, kOffSx16 = kOffSums + kSbStride, kBytes = kOffSx16 + kSx16Bytes;
+};
+inline constexpr uint32_t xrec_bytes(uint32_t n_tok) { return 1120u * n_tok; }
+
+/// Lane-constant byte offsets into an x record: B fragments and sums of this lane's column in each column group.
+/// A lane whose column carries no row reads the last real column; what it computes is never stored.
+template <int G>
+struct XLane {
+    uint32_t xs[G], sums[G], tok[G], g, t;
+};
+template <int NTOK, uint32_t LaneBytes>
+__device__ __forceinline__ XLane<(NTOK + 3) / 4> make_xlane(uint32_t g, uint32_t t) {
+    XLane<(NTOK + 3) / 4> xl;
+    xl.g = g, xl.t = t;
+#pragma unroll
+    for (int gi = 0; gi < (NTOK + 3) / 4; ++gi) {
+        const uint32_t col = min(8u * gi + g, XRec<NTOK>::kCols - 1);
+        xl.xs[gi] = col * 64u + t * LaneBytes;
+        xl.sums[gi] = XRec<NTOK>::kOffSums + col * 16u + t * 4u;
+        xl.tok[gi] = min(4u * gi + t, static_cast<uint32_t>(NTOK - 1));
+    }
+    return xl;
+}
+
+/// One quad (4 consecutive elements, index qd within the row) of x * s into the records at `area`: fp16 hi / lo, and its
+/// share of the 16- and 32-element sums.  The eight lanes that hold a sub-block's quads must call it together.
+__device__ __forceinline__ void stage_quad(uint8_t* area, float4 v, float s, uint32_t qd, uint32_t n_tok, uint32_t tok) {
+    const uint32_t rec = xrec_bytes(n_tok), sub_stride = 128u * n_tok;
+    v.x *= s; v.y *= s; v.z *= s; v.w *= s;
+    uint2 hi, lo;
+    split4(v, hi, lo);
+    const uint32_t sb = qd >> 6, sub = (qd >> 3) & 7u, in = qd & 7u;  // 8 quads per 32-element sub-block
+    uint8_t* base = area + sb * rec;
+    uint8_t* dst = base + sub * sub_stride + tok * 128u + in * 8u;
+    *reinterpret_cast<uint2*>(dst) = hi;
+    *reinterpret_cast<uint2*>(dst + 64) = lo;
+    float sum = (v.x + v.y) + (v.z + v.w);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    uint8_t* sums = base + 8u * sub_stride;
+    if ((in & 3u) == 0) reinterpret_cast<float*>(sums + 32u * n_tok)[(sub * 2u + (in >> 2)) * n_tok + tok] = sum;
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+    if (in == 0) {
+        sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
+        const __half h = __float2half_rn(sum);
+        const __half l = __float2half_rn(sum - __half2float(h));
+        uint8_t* sd = sums + tok * 32u + sub * 2u;
+        *reinterpret_cast<__half*>(sd) = h;
+        *reinterpret_cast<__half*>(sd + 16) = l;
+    }
+}
+
+/// Converts super-blocks [0, n_sb) of one x row into records starting at `area`.  Called by every thread of a block
+/// (`nthreads` a multiple of 32); the arithmetic does not depend on who calls it.
+__device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, float s, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t tid,
+                                              uint32_t nthreads) {
+    const float4* xr = reinterpret_cast<const float4*>(xrow);
+    for (uint32_t qd = tid; qd < n_sb * 64u; qd += nthreads) stage_quad(area, xr[qd], s, qd, n_tok, tok);
+}
+
+/// Bytes of global scratch stage_x_rec_kernel fills: the records of all super-blocks, then 16 reciprocal scales.
+inline uint64_t stage_rec_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * xrec_bytes(n_tok) + 64; }
+
+/// One block per x row: the row's power-of-two scale, then its records.
+static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
+                                                                 uint32_t nb, uint32_t n_tok) {
+    __shared__ float red[16];
+    __shared__ float sc[2];
+    const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    float m = 0.0f;
+    for (uint32_t i = tid; i < nb * 64u; i += 512) {
+        const float4 v = reinterpret_cast<const float4*>(xrow)[i];
+        m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.0f;
+        for (int i = 0; i < 16; ++i) a = fmaxf(a, red[i]);
+        row_scale(a, sc[0], sc[1]);
+    }
+    __syncthreads();
+    stage_row_rec(scratch, xrow, sc[0], nb, n_tok, tk, tid, 512);
+    if (tid == 0) reinterpret_cast<float*>(scratch + uint64_t{nb} * xrec_bytes(n_tok))[tk] = sc[1];
+}
+
+// ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows ----------------------------------------------------
+// A holds the bare 4-bit codes (low nibbles as q * 2^-24, high nibbles in place as 16 q * 2^-24).  Every 32-element
+// sub-block s gets a fresh fp32 accumulator S_s (two MMAs), and the 6-bit scales enter in fp32:
+//     a_p = fma(w_{4+p}, S_{4+p}, w_p * S_p)   p = 0..3      (w_s = sc_s, or sc_s / 16 for the high-nibble sub-blocks)
+//     T   = (a_0 + a_1) + (a_2 + a_3)
+//     y  += (d * 2^24) * T  -  (dmin * 2^24 * 32) * M
+// where M, the min term sum_s m_s * (sum of x over sub-block s) / 32, comes from one extra MMA whose A holds the 6-bit min
+// codes and whose B holds the sub-block sums of x.  That operation order is the same for every batch size; a call
+// with ONE x row gets it with a quarter of the scale work by placing x in the column pair (2p, 2p + 1) of B for the
+// sub-blocks s = p (mod 4) (the other columns read zeros), so that one accumulator tile carries four sub-blocks and
+// lane t of a row finishes sub-blocks t and 4 + t; two shuffles build T.  Adding exact zeros leaves S_s bit-identical.
+struct Q4Kf {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1, kXLaneBytes = 16;
+    static constexpr bool kAllowSlices = true;  // two K slices per row block fit in shared memory at every batch size
+    static constexpr uint32_t kZeroBytes = 1024;  // zeros a single-row call reads for the B columns that carry nothing
+
+    /// int byte `idx` of `word` as float (times 1/16 with `sixteenth`) through a 2^23 (2^19) + code bit pattern: exact.
+    __device__ static __forceinline__ float code_to_float(uint32_t word, uint32_t idx, bool sixteenth) {
+        const uint32_t bits = prmt(word, sixteenth ? 0x49000000u : 0x4B000000u, idx | (4u << 4) | (5u << 8) | (7u << 12));
+        return __uint_as_float(bits) - (sixteenth ? 524288.0f : 8388608.0f);
+    }
+
+    template <int G, int NTOK, class Release>
+    __device__ static __forceinline__ void item(const uint8_t* row, uint32_t t, const uint8_t* rec, const XLane<G>& xl, const uint8_t* zeros,
+                                                float (&yacc)[G][2], Release&& release) {
+        constexpr uint32_t kSubStride = XRec<NTOK>::kSubStride;
+        const uint8_t* fq = row + t * 8u;
+        const uint32_t m_sel = (2 * t) | ((2 * t) << 4) | ((2 * t + 1) << 8) | ((2 * t + 1) << 12);
+        // 6-bit codes of both rows, four per word (SWAR form of src/tensor/quant.cpp:236-244)
+        uint32_t sc_lo[2], sc_hi[2], mpair[2];
+        float dq[2], dmn[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint4 h = *reinterpret_cast<const uint4*>(row + r * 8 * kPitch);
+            sc_lo[r] = h.y & 0x3F3F3F3Fu;                                 // sc0..sc3
+            sc_hi[r] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);  // sc4..sc7
+            const uint32_t m_lo = h.z & 0x3F3F3F3Fu;
+            const uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            mpair[r] = prmt(m_lo, m_hi, m_sel) & 0x00FF00FFu;  // (m_2t, m_2t+1) as fp16 subnormals
+            const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+            dq[r] = __low2float(dd) * 16777216.0f;              // d * 2^24: undoes the subnormal encoding of A
+            dmn[r] = __high2float(dd) * (16777216.0f * 32.0f);  // dmin * 2^24 * 32: and the / 32 of the sums
+        }
+        // A fragments of sub-block pair j: [row][quad-pair registers], low nibbles (sub-block 2j) and high (2j + 1)
+        auto load_a = [&](int j, uint32_t (&aLo)[2][4], uint32_t (&aHi)[2][4]) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint2 q = *reinterpret_cast<const uint2*>(fq + r * 8 * kPitch + 16 + j * 32);
+                const uint32_t qa = q.x, qb = q.y, qa8 = qa >> 8, qb8 = qb >> 8;
+                aLo[r][0] = qa & 0x000F000Fu, aLo[r][1] = qa8 & 0x000F000Fu, aLo[r][2] = qb & 0x000F000Fu, aLo[r][3] = qb8 & 0x000F000Fu;
+                aHi[r][0] = qa & 0x00F000F0u, aHi[r][1] = qa8 & 0x00F000F0u, aHi[r][2] = qb & 0x00F000F0u, aHi[r][3] = qb8 & 0x00F000F0u;
+            }
+        };
+        float T[G][2];  // the item's scaled sums per column group: rows g, g + 8
+        if constexpr (NTOK == 1) {
+            // B base per sub-block phase p: the lane whose column pair is p reads x (hi for even g, lo for odd g), the others zeros
+            const uint8_t* real = rec + (xl.g & 1u) * 64u + t * 16u;
+            const uint8_t* zb = zeros + t * 16u;
+            const uint8_t* bp[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) bp[p] = (xl.g >> 1) == static_cast<uint32_t>(p) ? real : zb;
+            float c[2][4];  // tile h: sub-blocks 4h .. 4h + 3
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t aLo[2][4], aHi[2][4];
+                load_a(j, aLo, aHi);
+                const int h = j >> 1, pl = (2 * j) & 3, ph = (2 * j + 1) & 3;
+                const uint4 bl = *reinterpret_cast<const uint4*>(bp[pl] + (2 * j) * kSubStride);
+                const uint4 bh = *reinterpret_cast<const uint4*>(bp[ph] + (2 * j + 1) * kSubStride);
+                if ((j & 1) == 0) mma16816_first(c[h], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
+                else mma16816(c[h], aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
+                mma16816(c[h], aLo[0][2], aLo[1][2], aLo[0][3], aLo[1][3], bl.z, bl.w);
+                mma16816(c[h], aHi[0][0], aHi[1][0], aHi[0][1], aHi[1][1], bh.x, bh.y);
+                mma16816(c[h], aHi[0][2], aHi[1][2], aHi[0][3], aHi[1][3], bh.z, bh.w);
+            }
+            release();  // every byte of the slot has been consumed
+            // lane t holds S_t (tile 0) and S_{4+t} (tile 1) of rows g and g + 8 in its column pair (hi, lo)
+            const bool odd = (t & 1u) != 0;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float w0 = code_to_float(sc_lo[r], t, odd), w1 = code_to_float(sc_hi[r], t, odd);
+                float a = fmaf(w1, c[1][2 * r] + c[1][2 * r + 1], w0 * (c[0][2 * r] + c[0][2 * r + 1]));
+                a += __shfl_xor_sync(0xFFFFFFFFu, a, 1);
+                a += __shfl_xor_sync(0xFFFFFFFFu, a, 2);
+                T[0][r] = a;
+            }
+        } else {
+            float a[G][2][4];  // a_p per column group and row half: w_p * S_p after sub-block p, completed by sub-block 4 + p
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t aLo[2][4], aHi[2][4];
+                load_a(j, aLo, aHi);
+                float wl[2], wh[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    wl[r] = code_to_float(j < 2 ? sc_lo[r] : sc_hi[r], (2 * j) & 3, false);
+                    wh[r] = code_to_float(j < 2 ? sc_lo[r] : sc_hi[r], (2 * j + 1) & 3, true);
+                }
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const uint4 bl = *reinterpret_cast<const uint4*>(rec + xl.xs[gi] + (2 * j) * kSubStride);
+                    const uint4 bh = *reinterpret_cast<const uint4*>(rec + xl.xs[gi] + (2 * j + 1) * kSubStride);
+                    float cl[4], ch[4];
+                    mma16816_first(cl, aLo[0][0], aLo[1][0], aLo[0][1], aLo[1][1], bl.x, bl.y);
+                    mma16816(cl, aLo[0][2], aLo[1][2], aLo[0][3], aLo[1][3], bl.z, bl.w);
+                    mma16816_first(ch, aHi[0][0], aHi[1][0], aHi[0][1], aHi[1][1], bh.x, bh.y);
+                    mma16816(ch, aHi[0][2], aHi[1][2], aHi[0][3], aHi[1][3], bh.z, bh.w);
+                    const int pl = (2 * j) & 3, ph = (2 * j + 1) & 3;
+                    if (j < 2) {
+                        a[gi][0][pl] = wl[0] * (cl[0] + cl[1]), a[gi][1][pl] = wl[1] * (cl[2] + cl[3]);
+                        a[gi][0][ph] = wh[0] * (ch[0] + ch[1]), a[gi][1][ph] = wh[1] * (ch[2] + ch[3]);
+                    } else {
+                        a[gi][0][pl] = fmaf(wl[0], cl[0] + cl[1], a[gi][0][pl]), a[gi][1][pl] = fmaf(wl[1], cl[2] + cl[3], a[gi][1][pl]);
+                        a[gi][0][ph] = fmaf(wh[0], ch[0] + ch[1], a[gi][0][ph]), a[gi][1][ph] = fmaf(wh[1], ch[2] + ch[3], a[gi][1][ph]);
+                    }
+                }
+            }
+            release();
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                T[gi][0] = (a[gi][0][0] + a[gi][0][1]) + (a[gi][0][2] + a[gi][0][3]);
+                T[gi][1] = (a[gi][1][0] + a[gi][1][1]) + (a[gi][1][2] + a[gi][1][3]);
+            }
+        }
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            const uint32_t bs = *reinterpret_cast<const uint32_t*>(rec + xl.sums[gi]);
+            float cm[4];
+            mma16816_first(cm, mpair[0], mpair[1], 0u, 0u, bs, 0u);
+            yacc[gi][0] = fmaf(dq[0], T[gi][0], yacc[gi][0]);
+            yacc[gi][0] = fmaf(-dmn[0], cm[0] + cm[1], yacc[gi][0]);
+            yacc[gi][1] = fmaf(dq[1], T[gi][1], yacc[gi][1]);
+            yacc[gi][1] = fmaf(-dmn[1], cm[2] + cm[3], yacc[gi][1]);
+        }
+    }
+};
+
+// ---- repacked formats (layouts: gemv_mma_grouped.cu) ------------------------------------------------------------------------
+// Every scale group (a 32-element block, or 16 elements of Q6_K) gets a fresh fp32 accumulator; the group's scale
+// and zero point are applied in fp32:  y += scale_g * (acc_g - zero * sum_g(x)).
+template <class T>
+struct GroupedItem {
+    static constexpr uint32_t kZeroBytes = 0;
+    template <int G, int NTOK, class Release>
+    __device__ static __forceinline__ void item(const uint8_t* r0, uint32_t t, const uint8_t* rec, const XLane<G>& xl, const uint8_t* /*zeros*/,
+                                                float (&yacc)[G][2], Release&& release) {
+        constexpr uint32_t kSubStride = XRec<NTOK>::kSubStride;
+        const uint8_t* r1 = r0 + 8 * T::kPitch;
+        typename T::Frag f0, f1;
+        T::load(f0, r0, t);
+        T::load(f1, r1, t);
+        typename T::Scales s0, s1;
+        T::load_scales(s0, r0);
+        T::load_scales(s1, r1);
+        release();  // fragments and scales are in registers
+        const float* sx16 = reinterpret_cast<const float*>(rec + XRec<NTOK>::kOffSx16);
+#pragma unroll
+        for (int sg = 0; sg < static_cast<int>(T::kScaleGroups); ++sg) {
+            float c[G][4];
+#pragma unroll
+            for (int s = 0; s < static_cast<int>(T::kStepsPerGroup); ++s) {
+                uint32_t a0, a1, a2, a3;
+                T::pairs(f0, sg, s, a0, a2);
+                T::pairs(f1, sg, s, a1, a3);
+                // the 16 elements of this step inside x: 32-element sub-block `sub`, half `lh`
+                const int sub = T::kStepsPerGroup == 2 ? sg : sg >> 1, lh = T::kStepsPerGroup == 2 ? s : sg & 1;
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const uint2 b = *reinterpret_cast<const uint2*>(rec + xl.xs[gi] + sub * kSubStride + lh * 32);
+                    if (s == 0) mma16816_first(c[gi], a0, a1, a2, a3, b.x, b.y);
+                    else mma16816(c[gi], a0, a1, a2, a3, b.x, b.y);
+                }
+            }
+            // m = scale * 2^24 undoes the subnormal encoding of A; the zero point enters as -zero * 2^-24 * sum(x)
+            const float m0 = T::scale(s0, sg), m1 = T::scale(s1, sg);
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                float sx;
+                if constexpr (T::kStepsPerGroup == 2) sx = sx16[(2 * sg) * NTOK + xl.tok[gi]] + sx16[(2 * sg + 1) * NTOK + xl.tok[gi]];
+                else sx = sx16[sg * NTOK + xl.tok[gi]];
+                const float z = sx * (-T::kZero / 16777216.0f);
+                yacc[gi][0] = fmaf(m0, (c[gi][0] + c[gi][1]) + z, yacc[gi][0]);
+                yacc[gi][1] = fmaf(m1, (c[gi][2] + c[gi][3]) + z, yacc[gi][1]);
+            }
+        }
+    }
+};
+
+struct Q40r : GroupedItem<Q40r> {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kGroupBytes = 144, kPitch = 192, kScaleGroups = 8, kStepsPerGroup = 2;
+    static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
+    static constexpr bool kAllowSlices = true;
+    static constexpr float kZero = 8.0f;
+    struct Frag {
+        uint4 q[2];  // chunk c: words of blocks 4c..4c+3
+    };
+    struct Scales {
+        uint4 d;  // eight fp16
+    };
+    __device__ static void load(Frag& f, const uint8_t* row, uint32_t t) {
+        f.q[0] = *reinterpret_cast<const uint4*>(row + 16 + t * 16);
+        f.q[1] = *reinterpret_cast<const uint4*>(row + 16 + 64 + t * 16);
+    }
+    __device__ static void load_scales(Scales& s, const uint8_t* row) { s.d = *reinterpret_cast<const uint4*>(row); }
+    /// A pair registers (elements 4t+0, 4t+2 | 4t+1, 4t+3) of scale group g, k-step s (0: low nibbles, 1: high nibbles)
+    __device__ static void pairs(const Frag& f, int g, int s, uint32_t& p02, uint32_t& p13) {
+        const uint4 c = f.q[g >> 2];
+        const uint32_t w = (g & 3) == 0 ? c.x : (g & 3) == 1 ? c.y : (g & 3) == 2 ? c.z : c.w;
+        p02 = (w >> (4 * s)) & 0x000F000Fu;
+        p13 = (w >> (8 + 4 * s)) & 0x000F000Fu;
+    }
+    __device__ static float scale(const Scales& s, int g) {
+        const uint32_t w = (g >> 1) == 0 ? s.d.x : (g >> 1) == 1 ? s.d.y : (g >> 1) == 2 ? s.d.z : s.d.w;
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(g & 1 ? w >> 16 : w & 0xFFFFu))) * 16777216.0f;
+    }
+};
+
+struct Q80r : GroupedItem<Q80r> {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kGroupBytes = 272, kPitch = 320, kScaleGroups = 8, kStepsPerGroup = 2;
+    static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
+    static constexpr bool kAllowSlices = false;  // the 5 KB slots leave no room for two columns of x
+    static constexpr float kZero = 128.0f;
+    struct Frag {
+        uint4 q[4];  // chunk c: (block 2c, step 0), (block 2c, step 1), (block 2c+1, step 0), (block 2c+1, step 1)
+    };
+    using Scales = Q40r::Scales;
+    __device__ static void load(Frag& f, const uint8_t* row, uint32_t t) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) f.q[c] = *reinterpret_cast<const uint4*>(row + 16 + c * 64 + t * 16);
+    }
+    __device__ static void load_scales(Scales& s, const uint8_t* row) { s.d = *reinterpret_cast<const uint4*>(row); }
+    __device__ static void pairs(const Frag& f, int g, int s, uint32_t& p02, uint32_t& p13) {
+        const uint4 c = f.q[g >> 1];
+        const int i = (g & 1) * 2 + s;
+        const uint32_t w = i == 0 ? c.x : i == 1 ? c.y : i == 2 ? c.z : c.w;
+        // int8 + 128 as an unsigned byte: flip the sign bit; the 128 comes back out through the zero point
+        p02 = (w & 0x00FF00FFu) ^ 0x00800080u;
+        p13 = ((w >> 8) & 0x00FF00FFu) ^ 0x00800080u;
+    }
+    __device__ static float scale(const Scales& s, int g) { return Q40r::scale(s, g); }
+};
+
+struct Q6Kr : GroupedItem<Q6Kr> {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kGroupBytes = 224, kPitch = 224, kScaleGroups = 16, kStepsPerGroup = 1;
+    static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
+    static constexpr bool kAllowSlices = true;
+    static constexpr float kZero = 32.0f;
+    struct Frag {
+        uint4 ql[2];  // half n: words (b, lh) = (0,0), (0,1), (1,0), (1,1)
+        uint4 qh;     // words (n, lh) = (0,0), (0,1), (1,0), (1,1)
+    };
+    struct Scales {
+        uint4 sc;   // sixteen int8
+        float d24;  // d * 2^24
+    };
+    __device__ static void load(Frag& f, const uint8_t* row, uint32_t t) {
+        f.ql[0] = *reinterpret_cast<const uint4*>(row + 32 + t * 16);
+        f.ql[1] = *reinterpret_cast<const uint4*>(row + 32 + 64 + t * 16);
+        f.qh = *reinterpret_cast<const uint4*>(row + 32 + 128 + t * 16);
+    }
+    __device__ static void load_scales(Scales& s, const uint8_t* row) {
+        s.sc = *reinterpret_cast<const uint4*>(row);
+        s.d24 = __half2float(*reinterpret_cast<const __half*>(row + 16)) * 16777216.0f;
+    }
+    /// scale group g = 8n + 2*quarter + lh: elements 128n + 32*quarter + 16*lh + (4t .. 4t+3)
+    __device__ static void pairs(const Frag& f, int g, int /*s*/, uint32_t& p02, uint32_t& p13) {
+        const int n = g >> 3, quarter = (g >> 1) & 3, lh = g & 1, b = quarter & 1, nib = quarter >> 1;
+        const uint4 c = f.ql[n];
+        const int wi = b * 2 + lh, hi = n * 2 + lh;
+        const uint32_t w = wi == 0 ? c.x : wi == 1 ? c.y : wi == 2 ? c.z : c.w;
+        const uint32_t h = hi == 0 ? f.qh.x : hi == 1 ? f.qh.y : hi == 2 ? f.qh.z : f.qh.w;
+        // 6-bit code = nibble | two high bits << 4, both halves of a pair at once
+        const int sh02 = 2 * quarter - 4, sh13 = 8 + 2 * quarter - 4;
+        const uint32_t h02 = sh02 >= 0 ? h >> sh02 : h << -sh02;
+        const uint32_t h13 = h >> sh13;
+        p02 = ((w >> (4 * nib)) & 0x000F000Fu) | (h02 & 0x00300030u);
+        p13 = ((w >> (8 + 4 * nib)) & 0x000F000Fu) | (h13 & 0x00300030u);
+    }
+    /// d * 2^24 * sc_g; the int8 goes to float through the 2^23 + 128 + sc bit pattern (exact, no conversion instruction)
+    __device__ static float scale(const Scales& s, int g) {
+        const uint32_t w = (g >> 2) == 0 ? s.sc.x : (g >> 2) == 1 ? s.sc.y : (g >> 2) == 2 ? s.sc.z : s.sc.w;
+        const uint32_t bits = prmt(w ^ 0x80808080u, 0x4B000000u, (g & 3) | (4u << 4) | (5u << 8) | (7u << 12));
+        return (__uint_as_float(bits) - 8388736.0f) * s.d24;
+    }
+};
+
+}  // namespace mma
+}  // namespace halo_cuda

@@ -61,7 +61,9 @@ extern "C" {
 #define HALO_CUDA_GEMV_VARIANT_MAX 7
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
-#define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch (same results, batches run slower) */
+#define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch: the tensor-core variants then take their
+                                                       statically partitioned kernels (another summation order over K, so the
+                                                       last bits differ from the default; batches run slower) */
 
 typedef struct HaloCudaCtx HaloCudaCtx; /* one per device, opaque */
 typedef void* HaloCudaStream;           /* a cudaStream_t */

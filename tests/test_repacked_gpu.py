@@ -91,7 +91,9 @@ def test_repack_is_a_byte_permutation(be, t):
 
 @pytest.mark.parametrize("t,n,k,m", [(synth.Q6_K, 5120, 17408, 1), (synth.Q6_K, 5120, 17408, 4), (synth.Q6_K, 5120, 17408, 8),
                                      (synth.Q8_0, 5120, 17408, 1), (synth.Q8_0, 5120, 17408, 8), (synth.Q4_0, 17408, 5120, 16),
-                                     (synth.Q6_K, 37, 512, 3), (synth.Q8_0, 130, 256, 21), (synth.Q4_0, 13, 5120, 17), (synth.Q4_0, 1000, 2560, 5)])
+                                     (synth.Q6_K, 37, 512, 3), (synth.Q8_0, 130, 256, 21), (synth.Q4_0, 13, 5120, 17), (synth.Q4_0, 1000, 2560, 5),
+                                     # more tiles than warps: several passes per warp, sums carried from one pass to the next
+                                     (synth.Q4_0, 40000, 256, 2), (synth.Q6_K, 50000, 768, 5), (synth.Q8_0, 60001, 512, 16)])
 def test_repacked_kernel_within_summation_bound(be, checker, t, n, k, m):
     from gpu_util import summation_bound
     w = synth.quant_weights(t, n, k, 0, 1)

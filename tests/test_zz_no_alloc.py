@@ -15,14 +15,14 @@ from halo_b200 import capi, synth
 pytestmark = pytest.mark.gpu
 
 
-def _run(be, st, entry, wtype, w, x, rows, cols, valid_rows=0, variant=0):
+def _run(be, st, entry, wtype, w, x, rows, cols, valid_rows=0, variant=0, no_scratch=False):
     n_vec = x.shape[0]
     wb = be.import_host_readonly(w.reshape(-1))
     xb = be.import_host_readonly(x)
     lb = be.allocate(n_vec * rows * 4)
     rb = be.allocate(n_vec * 12)
     ib = be.allocate(n_vec * 4)
-    g = hb.GemvArgs(wtype, hb.TensorRef.of(wb), hb.TensorRef.of(xb), hb.TensorRef.of(lb), rows, cols, n_vec, variant)
+    g = hb.GemvArgs(wtype, hb.TensorRef.of(wb), hb.TensorRef.of(xb), hb.TensorRef.of(lb), rows, cols, n_vec, variant, no_scratch=no_scratch)
     a = hb.LmHeadArgs(g, hb.TensorRef.of(rb), valid_rows, hb.TensorRef.of(ib))
     entry(st, a)
     res = np.zeros((n_vec, 3), np.uint32)
@@ -44,13 +44,19 @@ def test_noalloc_lm_head_equals_regular_lm_head_twice_in_a_row():
         w = synth.quant_weights(wtype, rows, cols, 91 + wtype, 1)
         x = synth.activations(n_vec, cols, 91 + wtype, 2)
         x[n_vec - 1, 3] = np.nan  # one poisoned vector: the NaN flag travels through the partials too
-        want = _run(be, st, be.lm_head, wtype, w, x, rows, cols, valid, variant)
+        # the regular entry point under the no-scratch flag takes the kernels the allocation-free one is limited to
+        want = _run(be, st, be.lm_head, wtype, w, x, rows, cols, valid, variant, no_scratch=True)
         got = _run(be, st, be.lm_head_noalloc, wtype, w, x, rows, cols, valid, variant)
         # same kernels, same order of operations: bit-identical words, logits and ids (the suite's bar for integer work)
         assert np.array_equal(got[0], want[0])
         assert np.array_equal(got[1].view(np.uint32), want[1].view(np.uint32))
         assert np.array_equal(got[2], want[2])
         assert got[0][n_vec - 1, 2] == 1 and got[2][n_vec - 1] == 0
+        # and the default kernels (context scratch allowed) agree with it to rounding: same ids, logits within 1e-5 of the largest
+        free = _run(be, st, be.lm_head, wtype, w, x, rows, cols, valid, variant)
+        ok = np.isfinite(want[1])
+        assert np.array_equal(free[2], want[2])
+        assert np.max(np.abs(free[1][ok] - want[1][ok])) <= 1e-5 * np.max(np.abs(want[1][ok]))
 
 
 def test_noalloc_lm_head_rejects_what_does_not_fit_and_needs_a_logits_buffer():
