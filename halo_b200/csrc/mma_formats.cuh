@@ -247,15 +247,22 @@ struct Q4Kf {
 };
 
 // ---- repacked formats (layouts: gemv_mma_grouped.cu) ------------------------------------------------------------------------
-// Every scale group (a 32-element block, or 16 elements of Q6_K) gets a fresh fp32 accumulator; the group's scale
-// and zero point are applied in fp32:  y += scale_g * (acc_g - zero * sum_g(x)).
+// Every scale group sg (a 32-element block, or 16 elements of Q6_K) gets a fresh fp32 accumulator S_sg; the group's
+// scale and zero point are applied in fp32, in this order for every batch size:
+//     P_p = sum over the groups sg = p (mod 4), ascending, of m_sg * (S_sg - zero * 2^-24 * sum_sg(x))     (an fma chain)
+//     y  += (P_0 + P_1) + (P_2 + P_3)                               m_sg = scale_sg * 2^24
+// A call with ONE x row places x in the column pair (2p, 2p + 1) of B for the groups sg = p (mod 4) (the other columns
+// read zeros), so one accumulator tile carries four groups and lane t of a row owns P_t; two shuffles build the sum.
 template <class T>
 struct GroupedItem {
-    static constexpr uint32_t kZeroBytes = 0;
+    static constexpr uint32_t kZeroBytes = 1024;
+
     template <int G, int NTOK, class Release>
-    __device__ static __forceinline__ void item(const uint8_t* r0, uint32_t t, const uint8_t* rec, const XLane<G>& xl, const uint8_t* /*zeros*/,
+    __device__ static __forceinline__ void item(const uint8_t* r0, uint32_t t, const uint8_t* rec, const XLane<G>& xl, const uint8_t* zeros,
                                                 float (&yacc)[G][2], Release&& release) {
         constexpr uint32_t kSubStride = XRec<NTOK>::kSubStride;
+        constexpr int kGroups = static_cast<int>(T::kScaleGroups), kSteps = static_cast<int>(T::kStepsPerGroup);
+        constexpr float kZ = -T::kZero / 16777216.0f;
         const uint8_t* r1 = r0 + 8 * T::kPitch;
         typename T::Frag f0, f1;
         T::load(f0, r0, t);
@@ -265,33 +272,84 @@ struct GroupedItem {
         T::load_scales(s1, r1);
         release();  // fragments and scales are in registers
         const float* sx16 = reinterpret_cast<const float*>(rec + XRec<NTOK>::kOffSx16);
+        // the 16 elements of step s of group sg inside x: 32-element sub-block `sub`, half `lh`
+        auto sub_of = [](int sg, int s) { return kSteps == 2 ? sg : sg >> 1; };
+        auto lh_of = [](int sg, int s) { return kSteps == 2 ? s : sg & 1; };
+        if constexpr (NTOK == 1) {
+            const uint8_t* real = rec + (xl.g & 1u) * 64u + t * 8u;
+            const uint8_t* zb = zeros + t * 8u;
+            const uint8_t* bp[4];
 #pragma unroll
-        for (int sg = 0; sg < static_cast<int>(T::kScaleGroups); ++sg) {
-            float c[G][4];
+            for (int p = 0; p < 4; ++p) bp[p] = (xl.g >> 1) == static_cast<uint32_t>(p) ? real : zb;
+            float P0 = 0.0f, P1 = 0.0f;  // this lane's P_t for rows g and g + 8
 #pragma unroll
-            for (int s = 0; s < static_cast<int>(T::kStepsPerGroup); ++s) {
-                uint32_t a0, a1, a2, a3;
-                T::pairs(f0, sg, s, a0, a2);
-                T::pairs(f1, sg, s, a1, a3);
-                // the 16 elements of this step inside x: 32-element sub-block `sub`, half `lh`
-                const int sub = T::kStepsPerGroup == 2 ? sg : sg >> 1, lh = T::kStepsPerGroup == 2 ? s : sg & 1;
+            for (int q = 0; q < kGroups / 4; ++q) {
+                float c[4];
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+#pragma unroll
+                    for (int s = 0; s < kSteps; ++s) {
+                        const int sg = 4 * q + p;
+                        uint32_t a0, a1, a2, a3;
+                        T::pairs(f0, sg, s, a0, a2);
+                        T::pairs(f1, sg, s, a1, a3);
+                        const uint2 b = *reinterpret_cast<const uint2*>(bp[p] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * 32);
+                        if (p == 0 && s == 0) mma16816_first(c, a0, a1, a2, a3, b.x, b.y);
+                        else mma16816(c, a0, a1, a2, a3, b.x, b.y);
+                    }
+                }
+                // lane t finishes group 4q + t
+                const float m0 = T::scale_lane(s0, q, t), m1 = T::scale_lane(s1, q, t);
+                float sx;
+                if constexpr (kSteps == 2) sx = sx16[2 * (4 * q + t)] + sx16[2 * (4 * q + t) + 1];
+                else sx = sx16[4 * q + t];
+                const float z = sx * kZ;
+                if (q == 0) P0 = m0 * ((c[0] + c[1]) + z), P1 = m1 * ((c[2] + c[3]) + z);
+                else P0 = fmaf(m0, (c[0] + c[1]) + z, P0), P1 = fmaf(m1, (c[2] + c[3]) + z, P1);
+            }
+            P0 += __shfl_xor_sync(0xFFFFFFFFu, P0, 1);
+            P1 += __shfl_xor_sync(0xFFFFFFFFu, P1, 1);
+            P0 += __shfl_xor_sync(0xFFFFFFFFu, P0, 2);
+            P1 += __shfl_xor_sync(0xFFFFFFFFu, P1, 2);
+            yacc[0][0] += P0;
+            yacc[0][1] += P1;
+        } else {
+            float P[G][2][4];
+#pragma unroll
+            for (int sg = 0; sg < kGroups; ++sg) {
+                float c[G][4];
+#pragma unroll
+                for (int s = 0; s < kSteps; ++s) {
+                    uint32_t a0, a1, a2, a3;
+                    T::pairs(f0, sg, s, a0, a2);
+                    T::pairs(f1, sg, s, a1, a3);
+#pragma unroll
+                    for (int gi = 0; gi < G; ++gi) {
+                        const uint2 b = *reinterpret_cast<const uint2*>(rec + xl.xs[gi] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * 32);
+                        if (s == 0) mma16816_first(c[gi], a0, a1, a2, a3, b.x, b.y);
+                        else mma16816(c[gi], a0, a1, a2, a3, b.x, b.y);
+                    }
+                }
+                const float m0 = T::scale(s0, sg), m1 = T::scale(s1, sg);
 #pragma unroll
                 for (int gi = 0; gi < G; ++gi) {
-                    const uint2 b = *reinterpret_cast<const uint2*>(rec + xl.xs[gi] + sub * kSubStride + lh * 32);
-                    if (s == 0) mma16816_first(c[gi], a0, a1, a2, a3, b.x, b.y);
-                    else mma16816(c[gi], a0, a1, a2, a3, b.x, b.y);
+                    float sx;
+                    if constexpr (kSteps == 2) sx = sx16[(2 * sg) * NTOK + xl.tok[gi]] + sx16[(2 * sg + 1) * NTOK + xl.tok[gi]];
+                    else sx = sx16[sg * NTOK + xl.tok[gi]];
+                    const float z = sx * kZ;
+                    if (sg < 4) {
+                        P[gi][0][sg & 3] = m0 * ((c[gi][0] + c[gi][1]) + z);
+                        P[gi][1][sg & 3] = m1 * ((c[gi][2] + c[gi][3]) + z);
+                    } else {
+                        P[gi][0][sg & 3] = fmaf(m0, (c[gi][0] + c[gi][1]) + z, P[gi][0][sg & 3]);
+                        P[gi][1][sg & 3] = fmaf(m1, (c[gi][2] + c[gi][3]) + z, P[gi][1][sg & 3]);
+                    }
                 }
             }
-            // m = scale * 2^24 undoes the subnormal encoding of A; the zero point enters as -zero * 2^-24 * sum(x)
-            const float m0 = T::scale(s0, sg), m1 = T::scale(s1, sg);
 #pragma unroll
             for (int gi = 0; gi < G; ++gi) {
-                float sx;
-                if constexpr (T::kStepsPerGroup == 2) sx = sx16[(2 * sg) * NTOK + xl.tok[gi]] + sx16[(2 * sg + 1) * NTOK + xl.tok[gi]];
-                else sx = sx16[sg * NTOK + xl.tok[gi]];
-                const float z = sx * (-T::kZero / 16777216.0f);
-                yacc[gi][0] = fmaf(m0, (c[gi][0] + c[gi][1]) + z, yacc[gi][0]);
-                yacc[gi][1] = fmaf(m1, (c[gi][2] + c[gi][3]) + z, yacc[gi][1]);
+                yacc[gi][0] += (P[gi][0][0] + P[gi][0][1]) + (P[gi][0][2] + P[gi][0][3]);
+                yacc[gi][1] += (P[gi][1][0] + P[gi][1][1]) + (P[gi][1][2] + P[gi][1][3]);
             }
         }
     }
@@ -324,6 +382,11 @@ struct Q40r : GroupedItem<Q40r> {
         const uint32_t w = (g >> 1) == 0 ? s.d.x : (g >> 1) == 1 ? s.d.y : (g >> 1) == 2 ? s.d.z : s.d.w;
         return __half2float(__ushort_as_half(static_cast<unsigned short>(g & 1 ? w >> 16 : w & 0xFFFFu))) * 16777216.0f;
     }
+    /// scale(s, 4 * q + t) for a lane-dependent t
+    __device__ static float scale_lane(const Scales& s, int q, uint32_t t) {
+        const uint32_t w = q == 0 ? (t & 2u ? s.d.y : s.d.x) : (t & 2u ? s.d.w : s.d.z);
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(t & 1u ? w >> 16 : w & 0xFFFFu))) * 16777216.0f;
+    }
 };
 
 struct Q80r : GroupedItem<Q80r> {
@@ -349,6 +412,7 @@ struct Q80r : GroupedItem<Q80r> {
         p13 = ((w >> 8) & 0x00FF00FFu) ^ 0x00800080u;
     }
     __device__ static float scale(const Scales& s, int g) { return Q40r::scale(s, g); }
+    __device__ static float scale_lane(const Scales& s, int q, uint32_t t) { return Q40r::scale_lane(s, q, t); }
 };
 
 struct Q6Kr : GroupedItem<Q6Kr> {
@@ -391,6 +455,11 @@ struct Q6Kr : GroupedItem<Q6Kr> {
     __device__ static float scale(const Scales& s, int g) {
         const uint32_t w = (g >> 2) == 0 ? s.sc.x : (g >> 2) == 1 ? s.sc.y : (g >> 2) == 2 ? s.sc.z : s.sc.w;
         const uint32_t bits = prmt(w ^ 0x80808080u, 0x4B000000u, (g & 3) | (4u << 4) | (5u << 8) | (7u << 12));
+        return (__uint_as_float(bits) - 8388736.0f) * s.d24;
+    }
+    __device__ static float scale_lane(const Scales& s, int q, uint32_t t) {
+        const uint32_t w = q == 0 ? s.sc.x : q == 1 ? s.sc.y : q == 2 ? s.sc.z : s.sc.w;
+        const uint32_t bits = prmt(w ^ 0x80808080u, 0x4B000000u, t | (4u << 4) | (5u << 8) | (7u << 12));
         return (__uint_as_float(bits) - 8388736.0f) * s.d24;
     }
 };

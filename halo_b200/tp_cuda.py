@@ -12,7 +12,7 @@ import torch
 import torch.distributed as dist
 
 from . import backend as hb
-from . import capi, tp
+from . import capi, synth, tp
 
 
 class CudaTp:
@@ -28,9 +28,18 @@ class CudaTp:
     def load(self, wtype: int, w: np.ndarray, rows: int, cols: int, mode: str) -> tp.TpProjection:
         shard = tp.shard_weight(wtype, w, rows, cols, mode, self.rank, self.world)
         buf = self.be.import_host_readonly(shard.weights.reshape(-1))
+        variant = 0
+        if wtype in (synth.Q6_K, synth.Q8_0, synth.Q4_0) and shard.cols % 256 == 0 and shard.rows > 0:
+            # what a loader does once per weight: the repacked row layout of the tensor-core kernel for these types
+            st = hb.Stream(self.be, self.stream())
+            packed = self.be.repack(st, wtype, hb.TensorRef.of(buf), shard.rows, shard.cols)
+            torch.cuda.current_stream(self.device).synchronize()
+            buf.free()
+            buf, variant = packed, capi.GEMV_MMA_R
         self._weights[id(shard)] = buf
         shard.weights = np.empty((0, 0), np.uint8)  # the host copy is not needed any more
-        return tp.TpProjection(shard, lambda s, x, _b=buf: self.matmul(s, _b, x), self.all_reduce if mode == "row" else None)
+        return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v),
+                               self.all_reduce if mode == "row" else None)
 
     def matmul(self, s: tp.Shard, wbuf: hb.Buffer, x: torch.Tensor, variant: int = 0) -> torch.Tensor:
         x = x.contiguous()
