@@ -32,6 +32,8 @@ sys.path.insert(0, str(ROOT))
 N_ROWS, K_COLS = 17408, 5120
 COPIES = 16
 PREFILL_M = 2048
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel on this shape (ncu, see profiles/)
+NCU_DRAM_BYTES_PER_LAUNCH = 50_198_000
 FALLBACK_HBM_GBS, FALLBACK_TFLOPS = 6650.0, 1590.0
 
 
@@ -56,7 +58,7 @@ class ClockSampler:
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -247,6 +249,91 @@ def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
     return out
 
 
+def decode_shapes(be, st, rank: int, world: int, reps: int):
+    """The other decode-shaped configurations, one line each: BASELINE config 1 (Q6_K / Q8_0 down projection, M = 1, 4, 8)
+    and config 4 (Q4_0 MTP head: FFN shape and the vocabulary-split output head with an all-gather of the logits,
+    M = 16).  Weights of these three types are repacked once at load, like any loader of this backend does; a
+    step cycles enough distinct weight copies to exceed L2.  Timed with CUDA events on the launching stream."""
+    import torch
+    import torch.distributed as dist
+
+    from halo_b200 import backend as hb
+    from halo_b200 import capi, synth
+    lib, ctx = be.lib, be.ctx
+    pk = peaks()
+    vocab = 151936
+    cases = [("cfg1 q6_k down", synth.Q6_K, 5120, 17408, (1, 4, 8), False), ("cfg1 q8_0 down", synth.Q8_0, 5120, 17408, (1, 4, 8), False),
+             ("cfg4 q4_0 ffn", synth.Q4_0, 17408, 5120, (16,), False), ("cfg4 q4_0 head, vocab split", synth.Q4_0, vocab // world, 5120, (16,), True)]
+    out = []
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.halo_cuda_event_create(ctx, C.byref(e0))
+    lib.halo_cuda_event_create(ctx, C.byref(e1))
+    for name, wtype, n, k, ms_list, gather in cases:
+        w = synth.quant_weights(wtype, n, k, 11 + rank, 1)
+        wbytes = w.nbytes
+        copies = max(1, min(4, int(300e6 // wbytes)))
+        raw = be.import_host_readonly(w.reshape(-1))
+        packed = [be.repack(st, wtype, hb.TensorRef.of(raw), n, k) for _ in range(copies)]
+        st.wait()
+        for m in ms_list:
+            x = synth.activations(m, k, 11 + rank, 2)
+            xb = be.import_host_readonly(x)
+            yb = be.allocate(m * n * 4)
+            structs = [be._gemv_struct(hb.GemvArgs(wtype, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, capi.GEMV_MMA_R),
+                                       "MATMUL", False) for b in packed]
+            yt = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            full = torch.empty((world, m, n), dtype=torch.float32, device="cuda") if gather and world > 1 else None
+            ts = torch.cuda.ExternalStream(st.handle)
+
+            def one():
+                for g in structs:
+                    rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+                    if rc != 0:
+                        raise hb.HaloError(rc, capi.last_error())
+                    if full is not None:  # the logits of every shard on every rank
+                        lib.halo_cuda_memcpy_d2d_async(ctx, C.c_void_p(yt.data_ptr()), g.y, m * n * 4, st.handle)
+                        with torch.cuda.stream(ts):
+                            dist.all_gather_into_tensor(full, yt)
+
+            for _ in range(3):
+                one()
+            st.wait()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            lib.halo_cuda_event_record(ctx, e0, st.handle)
+            for _ in range(reps):
+                one()
+            lib.halo_cuda_event_record(ctx, e1, st.handle)
+            st.wait()
+            torch.cuda.synchronize()
+            ns = C.c_uint64()
+            lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+            us = ns.value / 1e3 / (reps * copies)
+            if world > 1:
+                t = torch.tensor([us], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                us = float(t.item())
+            # parity of what was timed: against the exact-order kernel on the raw rows
+            y = np.empty((m, n), np.float32)
+            be.download(st, hb.TensorRef.of(yb), y)
+            be.gemv(st, hb.GemvArgs(wtype, hb.TensorRef.of(raw), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, capi.GEMV_EXACT8))
+            ye = np.empty((m, n), np.float32)
+            be.download(st, hb.TensorRef.of(yb), ye)
+            st.wait()
+            shards = world if gather else 1  # the FFN / down shapes are per-GPU work (weak), the head is one job split over the ranks
+            gbs = shards * wbytes / (us * 1e-6) / 1e9
+            out.append({"shape": name, "wtype": synth.TYPE_NAMES[wtype], "rows_per_gpu": n, "cols": k, "m": m, "us_per_call": us,
+                        "weight_gbs": gbs, "frac_of_hbm_per_gpu": gbs / shards / pk["hbm_gbs"], "all_gather": bool(full is not None),
+                        "rel_err_vs_exact": float(np.max(np.abs(y - ye)) / np.max(np.abs(ye)))})
+            xb.free()
+            yb.free()
+        for b in packed:
+            b.free()
+        raw.free()
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -265,6 +352,10 @@ def run_ours(args) -> None:
     be = hb.CudaBackend(local_rank)
     st = be.create_stream()
     lib, ctx = be.lib, be.ctx
+    if args.profile and args.shapes:
+        for r in decode_shapes(be, st, rank, world, max(1, args.steps)):
+            print(json.dumps(r), flush=True)
+        return
 
     # ---- inputs: rank r holds its own column shard (distinct seed), COPIES distinct copies resident in HBM
     w, x = make_inputs(rank)
@@ -346,8 +437,6 @@ def run_ours(args) -> None:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
-
     # ---- parity spot check of what was timed (the last copy's y against the exact-order variant on the device)
     y_fast = np.empty(N_ROWS, np.float32)
     be.download(st, hb.TensorRef.of(ybufs[-1]), y_fast)
@@ -400,11 +489,29 @@ def run_ours(args) -> None:
                                 "traffic": None, "peak_source": pkk["source"], "flops_per_launch": flops},
                    "l2": "operands larger than L2: W 50 MB + x 42 MB + y 143 MB per call", "gpu_launches": 2 * psteps}
 
-    sweep = None
+        if world > 1:  # the same GEMM with N column-split over the ranks (strong scaling; no collective: each rank keeps its columns)
+            n_split = N_ROWS // world
+            sargs = hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[0]), hb.TensorRef.of(xpb), hb.TensorRef.of(ypb), n_split, K_COLS, pm, 0,
+                                allow_gemm=True)
+            sstruct = be._gemv_struct(sargs, "MATMUL", False)
+
+            def split_pass():
+                rc = lib.halo_cuda_gemv(ctx, C.byref(sstruct), st.handle)
+                if rc != 0:
+                    raise hb.HaloError(rc, capi.last_error())
+
+            for _ in range(3):
+                split_pass()
+            sms = timed(split_pass, psteps) / psteps
+            prefill["column_split"] = {"rows_per_gpu": n_split, "ms_per_call": sms, "tflops": flops / (sms * 1e-3) / 1e12, "scaling": "strong"}
+
+    sweep = shapes = None
     if not args.profile:
         for b in wbufs[1:] + ybufs[1:]:
             b.free()
+        shapes = decode_shapes(be, st, rank, world, max(3, min(args.steps, 20)))
         sweep = tp_sweep(local_rank, rank, world, max(3, min(args.steps, 20)))
+    clocks = sampler.stop() if rank == 0 else None
 
     launches_per_step = COPIES
     total_launches = args.steps * launches_per_step
@@ -427,13 +534,15 @@ def run_ours(args) -> None:
                    "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
                    "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                     "traffic": None, "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of this kernel and shape, profiles/",
+                     "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": algo_bytes},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COPIES * K_COLS * 4, "d2h_bytes_per_step": COPIES * N_ROWS * 4,
                 "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": total_launches,
         "prefill": prefill,
+        "decode_shapes": shapes,
         "tp_sweep": sweep,
         "clocks": clocks,
     }
@@ -452,6 +561,7 @@ def main() -> None:
     ap.add_argument("--variant", type=int, default=0, help="kernel variant id (0 = what the backend selects)")
     ap.add_argument("--prefill", action="store_true", help="with --profile: also run the M = 2048 GEMM")
     ap.add_argument("--profile", action="store_true", help="small run for ncu: no CPU baseline, no e2e leg, warm-up as given")
+    ap.add_argument("--shapes", action="store_true", help="with --profile: run only the config-1 / config-4 decode shapes (1 GPU)")
     args = ap.parse_args()
     globals()["COPIES"] = args.copies
     if args.impl == "reference":
