@@ -532,6 +532,58 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
     return run_gemv(ctx, c, args->variant_id, static_cast<cudaStream_t>(stream));
 }
 
+int halo_cuda_gemv_reduce(HaloCudaCtx* ctx, const HaloCudaGemv* args, const HaloCudaPeerReduce* peers, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    GemvCall c{};
+    if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
+    if (args->variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
+        return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
+    if (peers == nullptr) return fail(HALO_CUDA_E_API, "MATMUL: null peer description");
+    if (peers->world == 0 || peers->world > HALO_CUDA_MAX_PEERS || peers->rank >= peers->world)
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: rank %u of %u peers (at most %d)", peers->rank, peers->world, HALO_CUDA_MAX_PEERS);
+    if (peers->epoch == nullptr || peers->done == nullptr) return fail(HALO_CUDA_E_KERNEL, "MATMUL: peer reduction without its counters");
+    for (uint32_t p = 0; p < peers->world; ++p)
+        if (peers->slots[p] == nullptr || peers->flags[p] == nullptr)
+            return fail(HALO_CUDA_E_KERNEL, "MATMUL: receive buffer or flags of peer %u are not mapped", p);
+    if (uint64_t{c.rows} * c.n_vec > peers->capacity)
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x %u results exceed the peers' slot capacity of %u floats", c.n_vec, c.rows, peers->capacity);
+    if (c.rows == 0 || c.n_vec == 0) return 0;  // every rank sees the same shape, so every rank skips
+    if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the peer epilogue belongs to the kernels that use context scratch");
+    const uint32_t v = resolve_variant(ctx, c, args->variant_id);
+    const bool pushes = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c));
+    if (!pushes) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7) have the peer epilogue");
+    c.peer = peers;
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = run_gemv(ctx, c, v, s)) return rc;
+    return launch_peer_finish(ctx, *peers, c.y, c.y_stride, c.rows, c.n_vec, s);
+}
+
+int halo_cuda_ipc_export(HaloCudaCtx* ctx, void* ptr, uint8_t handle[64]) {
+    if (int rc = enter(ctx)) return rc;
+    if (ptr == nullptr || handle == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size of the C ABI");
+    cudaIpcMemHandle_t h;
+    HC_CUDA(cudaIpcGetMemHandle(&h, ptr));
+    std::memcpy(handle, &h, 64);
+    return 0;
+}
+
+int halo_cuda_ipc_open(HaloCudaCtx* ctx, const uint8_t handle[64], void** ptr) {
+    if (int rc = enter(ctx)) return rc;
+    if (ptr == nullptr || handle == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    HC_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return 0;
+}
+
+int halo_cuda_ipc_close(HaloCudaCtx* ctx, void* ptr) {
+    if (int rc = enter(ctx)) return rc;
+    if (ptr == nullptr) return 0;
+    HC_CUDA(cudaIpcCloseMemHandle(ptr));
+    return 0;
+}
+
 int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* a, HaloCudaStream stream) {
     if (int rc = enter(ctx)) return rc;
     if (a == nullptr) return fail(HALO_CUDA_E_API, "LM_HEAD: null argument struct");

@@ -61,7 +61,7 @@ __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) { a
 template <int G, int NTOK, int KS>
 __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit, uint32_t r, uint32_t ks, float* red, const SkTable& tb, uint32_t cta,
                                              float* part, uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows,
-                                             uint32_t lane) {
+                                             uint32_t lane, const PeerPush& peer) {
     constexpr int R = kSkWarps / KS;
     if constexpr (KS > 1) {
         if (ks != 0) {
@@ -79,7 +79,7 @@ __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit,
         }
         named_barrier(1 + r, KS * 32);  // the slices may overwrite `red` at their next block only after slice 0 has read it
     }
-    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, s_inv, y, y_stride, rows, lane);
+    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, s_inv, y, y_stride, rows, lane, peer);
 #pragma unroll
     for (int gi = 0; gi < G; ++gi) yacc[gi][0] = yacc[gi][1] = 0.0f;
 }
@@ -101,7 +101,8 @@ template <class F, int NTOK, int NS, int KS, bool PRE>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
                         float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, float* __restrict__ partials,
-                        uint32_t* __restrict__ counters, uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage) {
+                        uint32_t* __restrict__ counters, uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage,
+                        const __grid_constant__ PeerPush peer) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     using L = SkLayout<F, NTOK, NS, KS>;
@@ -240,7 +241,7 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                 refill();  // keeps the producer in step
             }
             if (cons.k + 1 == cpu || cons.col + 1 == cons.end)  // the row block, or this CTA's share of it, is done
-                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane);
+                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, peer);
         } else {
             refill();
         }
@@ -255,7 +256,7 @@ template <class F, int NTOK, int NS, int KS>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, float* __restrict__ y, uint64_t y_stride,
                         uint32_t rows, uint32_t nb, uint32_t xs_cols, float* __restrict__ partials, uint32_t* __restrict__ counters,
-                        uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage) {
+                        uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage, const __grid_constant__ PeerPush peer) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     using L = SkLayout<F, NTOK, NS, KS>;
@@ -345,7 +346,7 @@ gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                     refill();
                 }
                 if (cons.k + 1 == cpu || c + 1 == col_hi)
-                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane);
+                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, peer);
             } else {
                 refill();
             }

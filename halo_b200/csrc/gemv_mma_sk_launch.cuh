@@ -46,6 +46,17 @@ inline cudaLaunchConfig_t pdl_config(uint32_t grid, uint32_t smem, cudaStream_t 
     return cfg;
 }
 
+/// The kernel-side view of a call's peer description (none: world = 0).
+inline PeerPush peer_push(const GemvCall& c) {
+    PeerPush pp{};
+    if (c.peer == nullptr) return pp;
+    pp.world = c.peer->world, pp.rank = c.peer->rank, pp.capacity = c.peer->capacity;
+    pp.n_rb = (c.rows + 15u) / 16u;
+    for (uint32_t i = 0; i < c.peer->world && i < kMaxPeers; ++i) pp.slots[i] = c.peer->slots[i], pp.flags[i] = c.peer->flags[i];
+    pp.epoch = c.peer->epoch, pp.done = c.peer->done;
+    return pp;
+}
+
 /// The partition of one call: which K slicing, the column ranges of the CTAs, and the scratch of the reduction.
 struct Geometry {
     uint32_t nb, ks;
@@ -118,7 +129,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         cudaLaunchAttribute attr[1];
         const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
         HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb,
-                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage));
+                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, peer_push(c)));
         return 0;
     }
 }
@@ -150,7 +161,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
     HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_streamed_kernel<F, NTOK, NS, KS>, wmap, g.table, y, c.y_stride, c.rows, g.nb, xs_cols,
                                static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev,
-                               static_cast<const uint8_t*>(ws)));
+                               static_cast<const uint8_t*>(ws), peer_push(c)));
     return 0;
 }
 

@@ -69,6 +69,7 @@ struct GemvCall {
     float* y;
     uint64_t w_stride, x_stride, y_stride;  // bytes
     uint64_t row_bytes;
+    const HaloCudaPeerReduce* peer = nullptr;  // row-split tensor parallelism: push the result rows to the peers instead of storing y
 };
 int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* out);
 uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested);
@@ -85,6 +86,7 @@ int launch_gemv_sk_q4k(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q40r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q6kr(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, cudaStream_t s);
 int launch_gemv_mma_r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout

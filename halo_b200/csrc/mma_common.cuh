@@ -222,13 +222,35 @@ struct SkTable {
     uint32_t start[kSkMaxCtas + 1];   // CTA c owns columns [start[c], start[c + 1])
 };
 
+/// Row-split tensor parallelism: instead of storing a finished row block to y, push it into slot `rank` of every
+/// peer's receive buffer (peer-mapped memory, plain stores over NVLink), count the row blocks done, and let the last
+/// one raise this rank's arrival flag on every peer.  world == 0: not in use.
+/// Receive buffer of a rank: [2 ping-pong sets][world slots][capacity floats]; flags: [2 sets][world] words holding the
+/// number of the reduction they belong to; *epoch counts the reductions this rank has finished.
+constexpr uint32_t kMaxPeers = 8;
+struct PeerPush {
+    uint32_t world, rank, capacity, n_rb;
+    float* slots[kMaxPeers];
+    uint32_t* flags[kMaxPeers];
+    const uint32_t* epoch;
+    uint32_t* done;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 /// Sums of one row block (this lane: rows g and g + 8 for its G token columns) -> y: directly when this CTA covered
 /// all of the unit's columns, else through the partial store and the last-arriver reduction.  `part` holds 2 records
 /// per CTA and row-block slot r (record 0: the unit the CTA's range starts in, record 1: the unit it ends in) of
 /// 32 lanes x 2G floats; `counters` one zeroed word per row block, left zeroed.
 template <int G, int NTOK, int R>
 __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
-                                         uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane) {
+                                         uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
+                                         const PeerPush& peer) {
     const uint32_t g = lane >> 2, t = lane & 3u, rb = unit * R + r;
     const uint32_t u_lo = unit * tb.cols_per_unit, u_hi = u_lo + tb.cols_per_unit;  // the unit's columns
     uint32_t c_lo = cta, c_hi = cta;
@@ -252,16 +274,55 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
         old = __shfl_sync(0xFFFFFFFFu, old, 0);
         if (old != c_hi - c_lo) return;  // another CTA will finish this block
         __threadfence();
-        for (uint32_t c = c_lo; c <= c_hi; ++c) {
-            const float2* p = record(c);
+        // the partials are added in CTA order; they are fetched kBatch contributors at a time so that the loads overlap
+        constexpr uint32_t kBatch = G <= 1 ? 8 : G == 2 ? 4 : 2;
+        for (uint32_t c0 = c_lo; c0 <= c_hi; c0 += kBatch) {
+            float2 v[kBatch][G];
 #pragma unroll
-            for (int gi = 0; gi < G; ++gi) {
-                const float2 v = __ldcg(p + gi);
-                if (c == c_lo) sum[gi][0] = v.x, sum[gi][1] = v.y;
-                else sum[gi][0] += v.x, sum[gi][1] += v.y;
+            for (uint32_t i = 0; i < kBatch; ++i) {
+                if (c0 + i <= c_hi) {
+                    const float2* p = record(c0 + i);
+#pragma unroll
+                    for (int gi = 0; gi < G; ++gi) v[i][gi] = __ldcg(p + gi);
+                }
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < kBatch; ++i) {
+                if (c0 + i <= c_hi) {
+#pragma unroll
+                    for (int gi = 0; gi < G; ++gi) {
+                        if (c0 + i == c_lo) sum[gi][0] = v[i][gi].x, sum[gi][1] = v[i][gi].y;
+                        else sum[gi][0] += v[i][gi].x, sum[gi][1] += v[i][gi].y;
+                    }
+                }
             }
         }
         if (lane == 0) counters[rb] = 0;
+    }
+    if (peer.world != 0) {
+        const uint32_t next = *peer.epoch + 1u, set = next & 1u;
+        const uint64_t slot = (uint64_t{set} * peer.world + peer.rank) * peer.capacity;
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            const uint32_t tk = 4u * gi + t;
+            if (tk < NTOK) {
+                const float inv = s_inv[tk];
+                const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
+                const uint64_t at = slot + uint64_t{tk} * rows;  // the pushed rows are dense: [x row][W row]
+                for (uint32_t p = 0; p < peer.world; ++p) {
+                    if (n0 < rows) peer.slots[p][at + n0] = sum[gi][0] * inv;
+                    if (n1 < rows) peer.slots[p][at + n1] = sum[gi][1] * inv;
+                }
+            }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && atomicAdd(peer.done, 1u) == peer.n_rb - 1u) {  // every row block of this rank is on every peer
+            *peer.done = 0;
+            __threadfence_system();
+            for (uint32_t p = 0; p < peer.world; ++p) st_release_sys(peer.flags[p] + set * peer.world + peer.rank, next);
+        }
+        return;
     }
 #pragma unroll
     for (int gi = 0; gi < G; ++gi) {

@@ -85,10 +85,11 @@ class TpProjection:
     all_reduce(y)                       sums y in place over the group (row split only).
     """
 
-    def __init__(self, shard: Shard, matmul: Callable, all_reduce: Callable | None = None):
-        if shard.mode == "row" and shard.tp > 1 and all_reduce is None:
+    def __init__(self, shard: Shard, matmul: Callable, all_reduce: Callable | None = None, fused: bool = False):
+        """fused: `matmul` already returns the sum over the group (a kernel with a reduction epilogue)."""
+        if shard.mode == "row" and shard.tp > 1 and all_reduce is None and not fused:
             raise ValueError("a row split needs an all-reduce")
-        self.shard, self.matmul, self.all_reduce = shard, matmul, all_reduce
+        self.shard, self.matmul, self.all_reduce, self.fused = shard, matmul, all_reduce, fused
 
     def local_x(self, x):
         """The slice of a full-width x this rank multiplies (row split), or x itself (column split)."""
@@ -100,7 +101,7 @@ class TpProjection:
     def __call__(self, x):
         s = self.shard
         y = self.matmul(s, self.local_x(x))
-        if s.mode == "row" and s.tp > 1:
+        if s.mode == "row" and s.tp > 1 and not self.fused:
             self.all_reduce(y)
         return y
 

@@ -15,12 +15,65 @@ from . import backend as hb
 from . import capi, synth, tp
 
 
+def variant_pushes(wtype: int, variant: int) -> bool:
+    """Whether the kernel a projection runs has the peer epilogue: the tensor-core skinny variants."""
+    return variant == capi.GEMV_MMA_R or (variant == 0 and wtype == synth.Q4_K)
+
+
 class CudaTp:
     def __init__(self, device: int, rank: int, world: int):
         self.be = hb.CudaBackend(device)
         self.rank, self.world = rank, world
         self.device = torch.device("cuda", device)
         self._weights: dict[int, hb.Buffer] = {}
+        self.peers: capi.PeerReduce | None = None
+        self._peer_bufs: list[hb.Buffer] = []
+        self._peer_maps: list[int] = []
+
+    def enable_peer_reduce(self, capacity: int) -> None:
+        """Sets up the peer-memory all-reduce epilogue of the row-split projections: a receive buffer of 2 x world slots of
+        `capacity` floats and 2 x world arrival flags per rank, exchanged as IPC handles over torch.distributed."""
+        if self.world == 1 or self.peers is not None:
+            return
+        lib, ctx = self.be.lib, self.be.ctx
+        slots = self.be.allocate(2 * self.world * capacity * 4)
+        flags = self.be.allocate(2 * self.world * 4 + 64)
+        words = self.be.allocate(64)
+        self._peer_bufs = [slots, flags, words]
+        torch.cuda.synchronize(self.device)
+        mine = []
+        for b in (slots, flags):
+            h = C.create_string_buffer(64)
+            rc = lib.halo_cuda_ipc_export(ctx, C.c_void_p(b.ptr), h)
+            if rc != 0:
+                raise hb.HaloError(rc, capi.last_error())
+            mine.append(bytes(h.raw))
+        everyone: list = [None] * self.world
+        dist.all_gather_object(everyone, mine)
+        pr = capi.PeerReduce()
+        pr.world, pr.rank, pr.capacity = self.world, self.rank, capacity
+        for p, (hs, hf) in enumerate(everyone):
+            if p == self.rank:
+                pr.slots[p], pr.flags[p] = slots.ptr, flags.ptr
+                continue
+            for handle, arr in ((hs, pr.slots), (hf, pr.flags)):
+                out = C.c_void_p()
+                rc = lib.halo_cuda_ipc_open(ctx, handle, C.byref(out))
+                if rc != 0:
+                    raise hb.HaloError(rc, capi.last_error())
+                arr[p] = out.value
+                self._peer_maps.append(out.value)
+        pr.epoch, pr.done = words.ptr, words.ptr + 16
+        self.peers = pr
+        dist.barrier()  # nobody pushes before every rank has mapped its peers
+
+    def close(self) -> None:
+        if self.peers is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()  # no peer may still be writing into a buffer that is about to go
+            for ptr in self._peer_maps:
+                self.be.lib.halo_cuda_ipc_close(self.be.ctx, C.c_void_p(ptr))
+            self.peers, self._peer_maps = None, []
 
     def stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
@@ -38,10 +91,13 @@ class CudaTp:
             buf, variant = packed, capi.GEMV_MMA_R
         self._weights[id(shard)] = buf
         shard.weights = np.empty((0, 0), np.uint8)  # the host copy is not needed any more
+        if mode == "row" and self.peers is not None and variant_pushes(wtype, variant):
+            # the matmul kernel pushes its rows to the peers and a small kernel adds them: no separate collective
+            return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v, reduce=True), None, fused=True)
         return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v),
                                self.all_reduce if mode == "row" else None)
 
-    def matmul(self, s: tp.Shard, wbuf: hb.Buffer, x: torch.Tensor, variant: int = 0) -> torch.Tensor:
+    def matmul(self, s: tp.Shard, wbuf: hb.Buffer, x: torch.Tensor, variant: int = 0, reduce: bool = False) -> torch.Tensor:
         x = x.contiguous()
         n_vec = x.shape[0]
         y = torch.empty((n_vec, s.rows), dtype=torch.float32, device=self.device)
@@ -51,7 +107,10 @@ class CudaTp:
         g.x, g.x_stride = x.data_ptr(), x.stride(0) * 4
         g.y, g.y_stride = y.data_ptr(), 0
         g.rows, g.cols, g.n_vec, g.flags = s.rows, s.cols, n_vec, 0
-        rc = self.be.lib.halo_cuda_gemv(self.be.ctx, C.byref(g), self.stream())
+        if reduce:
+            rc = self.be.lib.halo_cuda_gemv_reduce(self.be.ctx, C.byref(g), C.byref(self.peers), self.stream())
+        else:
+            rc = self.be.lib.halo_cuda_gemv(self.be.ctx, C.byref(g), self.stream())
         if rc != 0:
             raise hb.HaloError(rc, capi.last_error())
         return y

@@ -36,6 +36,27 @@ for wtype, rows, cols, m in [(synth.Q4_K, 1024, 5120, 1), (synth.Q6_K, 512, 4352
     assert err <= 1e-5, f"row split + all-reduce off by {err}"
     ref = yr.clone(); dist.broadcast(ref, 0)
     assert torch.equal(ref.view(torch.int32), yr.view(torch.int32)), "every rank must hold the same reduced y"
+# the same row splits with the peer-memory epilogue: the matmul kernel pushes its rows to the peers, a small kernel adds them
+rt.enable_peer_reduce(16 * 1024)
+for wtype, rows, cols, m in [(synth.Q4_K, 1024, 5120, 1), (synth.Q6_K, 512, 4352, 4), (synth.Q4_K, 640, 6144, 3), (synth.Q4_K, 37, 1024, 16)]:
+    w = synth.quant_weights(wtype, rows, cols, 33, 1)
+    x = torch.from_numpy(synth.activations(m, cols, 33, 2)).cuda()
+    full = one.load(wtype, w, rows, cols, "column")(x)
+    rt.peers, keep = None, rt.peers
+    nccl = rt.load(wtype, w, rows, cols, "row")(x)       # partial products + NCCL all-reduce
+    rt.peers = keep
+    fused = rt.load(wtype, w, rows, cols, "row")
+    assert fused.fused and fused.all_reduce is None, "the fused projection must not call a collective"
+    for it in range(5):                                     # both ping-pong slot sets, several times over
+        yf = fused(x)
+        err = (yf - full).abs().max().item() / full.abs().max().item()
+        assert err <= 1e-5, f"peer-reduced row split off by {err} (iteration {it})"
+        if world == 2:                                      # two addends: the order cannot matter
+            assert torch.equal(yf.view(torch.int32), nccl.view(torch.int32)), "peer reduction differs from the NCCL all-reduce"
+        ref = yf.clone(); dist.broadcast(ref, 0)
+        assert torch.equal(ref.view(torch.int32), yf.view(torch.int32)), "every rank must hold the same reduced y"
+st = rt.be.create_stream(); st.wait()                      # raises if a flag wait expired on the device
+rt.close()
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
 print("TP_OK", rank)
 '''
