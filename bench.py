@@ -170,82 +170,96 @@ def sweep_layers():
     return gdn, gqa
 
 
-def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
-    """Per-token decode weight sweep over an 8-layer slice (6 Gated-DeltaNet + 2 GQA layers) of the 64-layer stack of
-    BASELINE config 3, tensor-parallel over `world` GPUs: column split for qkv / gate / up, row split + NCCL all-reduce
-    for out / o / down.  Aggregate weight GB/s includes the collectives."""
+def time_token_slice(layers, m: int, steps: int, world: int):
+    """One x row set through every projection of `layers`, `steps` times: ms per pass (max over ranks) and whether the pass
+    ran as a CUDA graph."""
     import torch
     import torch.distributed as dist
+    xs = {}
+    for projs in layers:
+        for _, p in projs:
+            if p.shard.cols not in xs:
+                xs[p.shard.cols] = torch.randn((m, p.shard.cols), device="cuda", dtype=torch.float32)
 
+    def one_token():
+        for projs in layers:
+            for _, p in projs:
+                p(xs[p.shard.cols])
+
+    for _ in range(3):
+        one_token()
+    torch.cuda.synchronize()
+    # The token pass is launch-bound when issued from Python: capture it once as a CUDA graph and replay it.
+    replay, graphed = one_token, False
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            one_token()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                one_token()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        replay, graphed = graph.replay, True
+    except Exception as exc:  # noqa: BLE001 - fall back to eager launches and say so
+        sys.stderr.write(f"tp_sweep: CUDA graph capture failed ({exc!r}); timing eager launches\n")
+        torch.cuda.synchronize()
+    for _ in range(2):
+        replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, graphed
+
+
+def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
+    """Per-token decode weight sweep over an 8-layer slice (6 Gated-DeltaNet + 2 GQA layers) of the 64-layer stack of
+    BASELINE config 3, tensor-parallel over `world` GPUs: column split for qkv / gate / up, row split for out / o / down.
+    With more than one GPU the row splits are timed twice: partial products + NCCL all-reduce, and the matmul kernel's
+    peer-memory epilogue (rows pushed to the peers over NVLink, added by a small kernel).  Aggregate weight GB/s
+    includes the reductions."""
     from halo_b200 import synth, tp_cuda
     rt = tp_cuda.CudaTp(local_rank, rank, world)
     gdn, gqa = sweep_layers()
-    host = {}
-    layers, total_bytes = [], 0
-    for li in range(8):
-        projs = []
-        for name, wtype, n, k, mode in (gqa if li % 4 == 3 else gdn):
-            key = (wtype, n, k)
-            if key not in host:
-                host[key] = synth.quant_weights(wtype, n, k, 7, len(host) + 1)
-            projs.append((name, rt.load(wtype, host[key], n, k, mode)))
-            total_bytes += n * synth.row_bytes(wtype, k)
-        layers.append(projs)
-    out = {}
-    for m in (1, 4):
-        xs = {}
+    host, out, total_bytes = {}, {}, 0
+    for how in (("nccl", "peer_epilogue") if world > 1 else ("none",)):
+        if how == "peer_epilogue":
+            rt.enable_peer_reduce(4 * 5120)  # the widest row-split result: 4 x rows of 5120
+        layers, total_bytes = [], 0
+        for li in range(8):
+            projs = []
+            for name, wtype, n, k, mode in (gqa if li % 4 == 3 else gdn):
+                key = (wtype, n, k)
+                if key not in host:
+                    host[key] = synth.quant_weights(wtype, n, k, 7, len(host) + 1)
+                projs.append((name, rt.load(wtype, host[key], n, k, mode)))
+                total_bytes += n * synth.row_bytes(wtype, k)
+            layers.append(projs)
+        for m in (1, 4):
+            ms, graphed = time_token_slice(layers, m, steps, world)
+            out[f"m{m}" if how != "peer_epilogue" else f"m{m}_peer_epilogue"] = {
+                "ms_per_token_slice": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9,
+                "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if how == "nccl" else 0,
+                "row_split_reduction": how, "cuda_graph": graphed}
         for projs in layers:
             for _, p in projs:
-                kk = p.shard.cols
-                if kk not in xs:
-                    xs[kk] = torch.randn((m, kk), device="cuda", dtype=torch.float32)
-
-        def one_token():
-            for projs in layers:
-                for _, p in projs:
-                    p(xs[p.shard.cols])
-
-        for _ in range(3):
-            one_token()
-        torch.cuda.synchronize()
-        # The token pass is launch-bound when issued from Python: capture it once as a CUDA graph and replay it.
-        replay, graphed = one_token, False
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                one_token()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    one_token()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            replay, graphed = graph.replay, True
-        except Exception as exc:  # noqa: BLE001 - fall back to eager launches and say so
-            sys.stderr.write(f"tp_sweep: CUDA graph capture failed ({exc!r}); timing eager launches\n")
-            torch.cuda.synchronize()
-        for _ in range(2):
-            replay()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            replay()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        if world > 1:
-            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        out[f"m{m}"] = {"ms_per_token_slice": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9,
-                        "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if world > 1 else 0,
-                        "cuda_graph": graphed}
+                rt._weights.pop(id(p.shard)).free()
     out["workload"] = (f"cfg3 slice: 8 of 64 layers (6 GDN + 2 GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K weights in total, "
-                       f"tp={world}: column split qkv/gate/up, row split + all-reduce out/o/down")
+                       f"tp={world}: column split qkv/gate/up, row split + reduction out/o/down")
     out["scaling"] = "strong"
+    rt.close()
     return out
 
 

@@ -40,7 +40,7 @@ class Gemv(C.Structure):
 
 class PeerReduce(C.Structure):
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("capacity", C.c_uint32), ("reserved", C.c_uint32),
-                ("slots", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("done", C.c_void_p)]
+                ("slots", C.c_void_p * 8), ("epoch", C.c_void_p), ("done", C.c_void_p)]
 
 
 class LmHead(C.Structure):

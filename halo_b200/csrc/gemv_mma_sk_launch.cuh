@@ -51,9 +51,8 @@ inline PeerPush peer_push(const GemvCall& c) {
     PeerPush pp{};
     if (c.peer == nullptr) return pp;
     pp.world = c.peer->world, pp.rank = c.peer->rank, pp.capacity = c.peer->capacity;
-    pp.n_rb = (c.rows + 15u) / 16u;
-    for (uint32_t i = 0; i < c.peer->world && i < kMaxPeers; ++i) pp.slots[i] = c.peer->slots[i], pp.flags[i] = c.peer->flags[i];
-    pp.epoch = c.peer->epoch, pp.done = c.peer->done;
+    for (uint32_t i = 0; i < c.peer->world && i < kMaxPeers; ++i) pp.slots[i] = static_cast<unsigned long long*>(c.peer->slots[i]);
+    pp.epoch = c.peer->epoch;
     return pp;
 }
 

@@ -223,24 +223,20 @@ struct SkTable {
 };
 
 /// Row-split tensor parallelism: instead of storing a finished row block to y, push it into slot `rank` of every
-/// peer's receive buffer (peer-mapped memory, plain stores over NVLink), count the row blocks done, and let the last
-/// one raise this rank's arrival flag on every peer.  world == 0: not in use.
-/// Receive buffer of a rank: [2 ping-pong sets][world slots][capacity floats]; flags: [2 sets][world] words holding the
-/// number of the reduction they belong to; *epoch counts the reductions this rank has finished.
+/// peer's receive buffer (peer-mapped memory, plain stores over NVLink).  Every element travels as one 8-byte word
+/// {value bits, number of the reduction}: the word is written and read atomically, so the receiver needs no flag
+/// and the sender no fence — an element is valid as soon as its tag is the reduction the receiver is waiting for.
+/// world == 0: not in use.  Receive buffer of a rank: [2 ping-pong sets][world slots][capacity] words; *epoch counts
+/// the reductions this rank has finished (the sender tags with *epoch + 1).
 constexpr uint32_t kMaxPeers = 8;
 struct PeerPush {
-    uint32_t world, rank, capacity, n_rb;
-    float* slots[kMaxPeers];
-    uint32_t* flags[kMaxPeers];
+    uint32_t world, rank, capacity, reserved;
+    unsigned long long* slots[kMaxPeers];
     const uint32_t* epoch;
-    uint32_t* done;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ unsigned long long peer_word(float v, uint32_t tag) {
+    return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
 }
 
 /// Sums of one row block (this lane: rows g and g + 8 for its G token columns) -> y: directly when this CTA covered
@@ -309,18 +305,12 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
                 const float inv = s_inv[tk];
                 const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
                 const uint64_t at = slot + uint64_t{tk} * rows;  // the pushed rows are dense: [x row][W row]
+                const unsigned long long w0 = peer_word(sum[gi][0] * inv, next), w1 = peer_word(sum[gi][1] * inv, next);
                 for (uint32_t p = 0; p < peer.world; ++p) {
-                    if (n0 < rows) peer.slots[p][at + n0] = sum[gi][0] * inv;
-                    if (n1 < rows) peer.slots[p][at + n1] = sum[gi][1] * inv;
+                    if (n0 < rows) peer.slots[p][at + n0] = w0;
+                    if (n1 < rows) peer.slots[p][at + n1] = w1;
                 }
             }
-        }
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0 && atomicAdd(peer.done, 1u) == peer.n_rb - 1u) {  // every row block of this rank is on every peer
-            *peer.done = 0;
-            __threadfence_system();
-            for (uint32_t p = 0; p < peer.world; ++p) st_release_sys(peer.flags[p] + set * peer.world + peer.rank, next);
         }
         return;
     }

@@ -1,5 +1,7 @@
-// The second half of halo_cuda_gemv_reduce: wait for every rank's arrival flag, add the pushed slots in rank order.
-// The first half is the push epilogue of the balanced skinny kernels (mma_common.cuh, sk_flush).
+// The second half of halo_cuda_gemv_reduce: add the slots the ranks pushed, in rank order.
+// The first half is the push epilogue of the balanced skinny kernels (mma_common.cuh, sk_flush): every element
+// arrives as one 8-byte word {value bits, number of the reduction}, so waiting for an element is reading it until
+// its tag matches.  Every wait is bounded; on expiry the context's error word is raised and nothing is stored.
 #include <cuda_runtime.h>
 
 #include "internal.h"
@@ -8,39 +10,43 @@
 namespace halo_cuda {
 namespace {
 
-constexpr uint32_t kFlagPolls = 1u << 20;  // x ~1 us of sleep each: about a second before a peer is declared lost
+constexpr uint32_t kPolls = 1u << 22;  // reads of one word (~0.25 us apart once sleeping) before its sender is declared lost
+
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t n_vec,
-                                                          const float* __restrict__ slots, const uint32_t* __restrict__ flags, uint32_t* epoch,
-                                                          uint32_t* blocks_done, uint32_t world, uint32_t capacity, uint32_t* error_word) {
+                                                          const unsigned long long* __restrict__ slots, uint32_t* epoch, uint32_t* blocks_done,
+                                                          uint32_t world, uint32_t capacity, uint32_t* error_word) {
     const uint32_t next = *epoch + 1u, set = next & 1u;
-    __shared__ uint32_t ok;
-    if (threadIdx.x == 0) {
-        uint32_t good = 1;
-        for (uint32_t p = 0; p < world && good; ++p) {
-            uint32_t n = 0;
-            while (mma::ld_acquire_sys(flags + set * world + p) != next) {
-                if (++n == kFlagPolls) {
-                    good = 0;
+    const uint64_t count = uint64_t{rows} * n_vec;
+    const unsigned long long* base = slots + uint64_t{set} * world * capacity;
+    bool lost = false;
+    for (uint64_t i = uint64_t{blockIdx.x} * blockDim.x + threadIdx.x; i < count && !lost; i += uint64_t{gridDim.x} * blockDim.x) {
+        float sum = 0.0f;
+        for (uint32_t p = 0; p < world; ++p) {
+            const unsigned long long* src = base + uint64_t{p} * capacity + i;
+            unsigned long long w = ld_relaxed_sys(src);
+            for (uint32_t n = 0; static_cast<uint32_t>(w >> 32) != next; ++n) {
+                if (n == kPolls) {
+                    lost = true;
                     break;
                 }
-                __nanosleep(1000);
+                if (n > 64) __nanosleep(200);
+                w = ld_relaxed_sys(src);
             }
+            if (lost) break;
+            const float v = __uint_as_float(static_cast<uint32_t>(w));
+            sum = p == 0 ? v : sum + v;
         }
-        if (!good && error_word != nullptr) atomicOr(error_word, 1u);
-        ok = good;
+        if (lost) break;
+        const uint32_t tk = static_cast<uint32_t>(i / rows), n = static_cast<uint32_t>(i - uint64_t{tk} * rows);
+        reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{tk} * y_stride)[n] = sum;
     }
-    __syncthreads();
-    if (ok) {
-        const uint64_t count = uint64_t{rows} * n_vec;
-        const float* base = slots + uint64_t{set} * world * capacity;
-        for (uint64_t i = uint64_t{blockIdx.x} * blockDim.x + threadIdx.x; i < count; i += uint64_t{gridDim.x} * blockDim.x) {
-            float sum = __ldcg(base + i);  // the slots were written by other GPUs: read them from L2, not a stale L1 line
-            for (uint32_t p = 1; p < world; ++p) sum += __ldcg(base + uint64_t{p} * capacity + i);
-            const uint32_t tk = static_cast<uint32_t>(i / rows), n = static_cast<uint32_t>(i - uint64_t{tk} * rows);
-            reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{tk} * y_stride)[n] = sum;
-        }
-    }
+    if (lost && error_word != nullptr) atomicOr(error_word, 1u);
     // the last block to finish closes the reduction: the next one uses the other slot set
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -56,10 +62,9 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
 
 int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, cudaStream_t s) {
     const uint64_t count = uint64_t{rows} * n_vec;
-    const uint32_t grid = static_cast<uint32_t>(count / 2048 < 1 ? 1 : count / 2048 > 64 ? 64 : count / 2048);
-    // `done` is free again once the matmul's last row block has raised the flags: it doubles as the block counter here
-    peer_finish_kernel<<<grid, 256, 0, s>>>(y, y_stride, rows, n_vec, p.slots[p.rank], p.flags[p.rank], p.epoch, p.done, p.world, p.capacity,
-                                            ctx->error_word_dev);
+    const uint32_t grid = static_cast<uint32_t>(count / 1024 < 1 ? 1 : count / 1024 > 64 ? 64 : count / 1024);
+    peer_finish_kernel<<<grid, 256, 0, s>>>(y, y_stride, rows, n_vec, static_cast<const unsigned long long*>(p.slots[p.rank]), p.epoch, p.done,
+                                            p.world, p.capacity, ctx->error_word_dev);
     HC_CUDA(cudaGetLastError());
     return 0;
 }

@@ -32,37 +32,33 @@ class CudaTp:
 
     def enable_peer_reduce(self, capacity: int) -> None:
         """Sets up the peer-memory all-reduce epilogue of the row-split projections: a receive buffer of 2 x world slots of
-        `capacity` floats and 2 x world arrival flags per rank, exchanged as IPC handles over torch.distributed."""
+        `capacity` 8-byte words per rank, exchanged as IPC handles over torch.distributed."""
         if self.world == 1 or self.peers is not None:
             return
         lib, ctx = self.be.lib, self.be.ctx
-        slots = self.be.allocate(2 * self.world * capacity * 4)
-        flags = self.be.allocate(2 * self.world * 4 + 64)
+        slots = self.be.allocate(2 * self.world * capacity * 8)
         words = self.be.allocate(64)
-        self._peer_bufs = [slots, flags, words]
+        self._peer_bufs = [slots, words]
         torch.cuda.synchronize(self.device)
-        mine = []
-        for b in (slots, flags):
-            h = C.create_string_buffer(64)
-            rc = lib.halo_cuda_ipc_export(ctx, C.c_void_p(b.ptr), h)
-            if rc != 0:
-                raise hb.HaloError(rc, capi.last_error())
-            mine.append(bytes(h.raw))
+        h = C.create_string_buffer(64)
+        rc = lib.halo_cuda_ipc_export(ctx, C.c_void_p(slots.ptr), h)
+        if rc != 0:
+            raise hb.HaloError(rc, capi.last_error())
+        mine = bytes(h.raw)
         everyone: list = [None] * self.world
         dist.all_gather_object(everyone, mine)
         pr = capi.PeerReduce()
         pr.world, pr.rank, pr.capacity = self.world, self.rank, capacity
-        for p, (hs, hf) in enumerate(everyone):
+        for p, handle in enumerate(everyone):
             if p == self.rank:
-                pr.slots[p], pr.flags[p] = slots.ptr, flags.ptr
+                pr.slots[p] = slots.ptr
                 continue
-            for handle, arr in ((hs, pr.slots), (hf, pr.flags)):
-                out = C.c_void_p()
-                rc = lib.halo_cuda_ipc_open(ctx, handle, C.byref(out))
-                if rc != 0:
-                    raise hb.HaloError(rc, capi.last_error())
-                arr[p] = out.value
-                self._peer_maps.append(out.value)
+            out = C.c_void_p()
+            rc = lib.halo_cuda_ipc_open(ctx, handle, C.byref(out))
+            if rc != 0:
+                raise hb.HaloError(rc, capi.last_error())
+            pr.slots[p] = out.value
+            self._peer_maps.append(out.value)
         pr.epoch, pr.done = words.ptr, words.ptr + 16
         self.peers = pr
         dist.barrier()  # nobody pushes before every rank has mapped its peers

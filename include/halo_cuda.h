@@ -194,23 +194,24 @@ int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStre
 int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaStream stream);
 
 /* ---- row-split tensor parallelism: matmul with a peer-memory all-reduce epilogue ------------------------------------
- * One process per GPU.  Each rank allocates a receive buffer and a flag array with halo_cuda_malloc (zeroed), exports
- * them (halo_cuda_ipc_export), hands the 64-byte handles to its peers over its own channel, and maps the peers'
+ * One process per GPU.  Each rank allocates a receive buffer with halo_cuda_malloc (zeroed), exports it
+ * (halo_cuda_ipc_export), hands the 64-byte handle to its peers over its own channel, and maps the peers'
  * (halo_cuda_ipc_open).  halo_cuda_gemv_reduce then computes this rank's partial product (a row-split projection: the
  * rank holds some columns of every W row, the call's `cols` and x are the rank's share) and, instead of storing it,
  * its matmul kernel pushes every finished row block into slot `rank` of every peer's receive buffer with plain stores
- * over NVLink and finally raises the rank's arrival flag on every peer; a second small kernel waits (bounded; on
- * expiry the context's error word is raised and the next stream wait reports E_BACKEND) for all `world` flags and adds
- * the slots in rank order into y, so every rank gets the same bits.  No counterpart in the reference (its backends
- * are single-device); the single-GPU product of the unsplit projection is the oracle.
- *   slots[p]: rank p's receive buffer as mapped on this rank (own: the local pointer), 2 * world * capacity floats
- *   flags[p]: rank p's flags, 2 * world words;  epoch, done: two zeroed words of this rank's own memory
- * rows * n_vec must not exceed capacity.  Only the tensor-core skinny variants (3, 7) push; others: E_UNSUPPORTED. */
+ * over NVLink, each element as one 8-byte word {value, number of the reduction}; a second small kernel reads the
+ * `world` slots until every word carries the current number (bounded; on expiry the context's error word is raised and
+ * the next stream wait reports E_BACKEND) and adds them in rank order into y, so every rank gets the same bits.  No
+ * counterpart in the reference (its backends are single-device); the single-GPU product of the unsplit projection is
+ * the oracle.
+ *   slots[p]: rank p's receive buffer as mapped on this rank (own: the local pointer), 2 * world * capacity * 8 bytes
+ *   epoch, done: two zeroed words of this rank's own memory
+ * rows * n_vec must not exceed capacity; the ranks must issue the same sequence of reductions.  Only the tensor-core
+ * skinny variants (3, 7) push; others: E_UNSUPPORTED. */
 #define HALO_CUDA_MAX_PEERS 8
 typedef struct HaloCudaPeerReduce {
     uint32_t world, rank, capacity, reserved;
-    float* slots[HALO_CUDA_MAX_PEERS];
-    uint32_t* flags[HALO_CUDA_MAX_PEERS];
+    void* slots[HALO_CUDA_MAX_PEERS];
     uint32_t* epoch;
     uint32_t* done;
 } HaloCudaPeerReduce;
