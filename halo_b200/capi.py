@@ -38,6 +38,11 @@ class Gemv(C.Structure):
                 ("n_vec", C.c_uint32), ("flags", C.c_uint32)]
 
 
+class GemvPlan(C.Structure):
+    _fields_ = [("slices", C.c_uint32), ("ctas", C.c_uint32), ("cols_per_unit", C.c_uint32), ("reserved", C.c_uint32),
+                ("start", C.c_uint32 * 161)]
+
+
 class PeerReduce(C.Structure):
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("capacity", C.c_uint32), ("reserved", C.c_uint32),
                 ("slots", C.c_void_p * 8), ("epoch", C.c_void_p), ("done", C.c_void_p)]
@@ -88,6 +93,7 @@ SYMBOLS = {
     "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_repacked_row_bytes": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
     "halo_cuda_repack_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P]),
+    "halo_cuda_gemv_plan": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvPlan)]),
     "halo_cuda_ipc_export": (C.c_int, [_P, _P, C.c_char_p]),
     "halo_cuda_ipc_open": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
     "halo_cuda_ipc_close": (C.c_int, [_P, _P]),

@@ -6,6 +6,7 @@
 #include <thread>
 
 #include "internal.h"
+#include "mma_common.cuh"
 
 namespace halo_cuda {
 
@@ -530,6 +531,22 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
         return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
     if (c.rows == 0 || c.n_vec == 0) return 0;
     return run_gemv(ctx, c, args->variant_id, static_cast<cudaStream_t>(stream));
+}
+
+int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan) {
+    if (plan == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    const bool grouped = repacked_row_bytes(wtype, 256) != 0;
+    if (wtype != HALO_CUDA_T_Q4_K && !grouped) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: no tensor-core skinny kernel for weight type id %u", wtype);
+    if (cols == 0 || cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "MATMUL: %u elements is not a multiple of 256", cols);
+    if (rows == 0 || sm_count == 0) return fail(HALO_CUDA_E_KERNEL, "MATMUL: empty matrix or device");
+    static_assert(HALO_CUDA_PLAN_MAX_CTAS == mma::kSkMaxCtas, "plan table size of the C ABI");
+    mma::SkTable t{};
+    std::memset(plan, 0, sizeof *plan);
+    plan->slices = mma::plan_partition(rows, cols / 256u, sm_count, mma::format_allows_slices(wtype), &t);
+    plan->ctas = t.parts;
+    plan->cols_per_unit = t.cols_per_unit;
+    for (uint32_t c = 0; c <= t.parts; ++c) plan->start[c] = t.start[c];
+    return 0;
 }
 
 int halo_cuda_gemv_reduce(HaloCudaCtx* ctx, const HaloCudaGemv* args, const HaloCudaPeerReduce* peers, HaloCudaStream stream) {

@@ -63,38 +63,13 @@ struct Geometry {
     void *counters, *partials;
 };
 
-/// Columns one CTA walks at most under `ks` slices with whole units per CTA (0: not possible) and with an even split.
-/// The choice is a function of (rows, cols, SM count) alone, so every batch size of a shape gets the same partition.
-inline void plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool allow_slices, Geometry* g) {
-    const uint64_t n_rb = (uint64_t{rows} + 15) / 16;
-    sms = std::min(sms, kSkMaxCtas);
-    // candidate A: 2 slices, whole units per CTA.  candidate B: 1 slice, even split of the columns, where a CTA pays
-    // roughly three columns' time for the cross-CTA reduction of the units its range cuts.
-    const uint64_t units_a = (n_rb + 7) / 8, cpu_a = (nb + 1) / 2, parts_a = std::min<uint64_t>(sms, units_a);
-    const uint64_t time_a = (units_a + parts_a - 1) / parts_a * cpu_a;
-    const uint64_t units_b = (n_rb + 15) / 16, cols_b = units_b * nb, parts_b = std::min<uint64_t>(sms, cols_b);
-    const uint64_t time_b = (cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : 3);
-    SkTable& t = g->table;
-    if (allow_slices && nb >= 2 && time_a <= time_b) {
-        g->ks = 2;
-        t.parts = static_cast<uint32_t>(parts_a);
-        t.cols_per_unit = static_cast<uint32_t>(cpu_a);
-        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * units_a / parts_a * cpu_a);
-    } else {
-        g->ks = 1;
-        t.parts = static_cast<uint32_t>(parts_b);
-        t.cols_per_unit = nb;
-        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * cols_b / parts_b);
-    }
-}
-
 template <class F, int NTOK>
 int geometry(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s, Geometry* g) {
     constexpr int G = (NTOK + 3) / 4;
     g->nb = c.cols / 256u;
     const uint64_t n_rb = (uint64_t{c.rows} + 15) / 16;
     if (n_rb * g->nb >= (1ull << 30)) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: more than 2^30 (16-row, 256-column) tiles");
-    plan_partition(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), F::kAllowSlices, g);
+    g->ks = plan_partition(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), F::kAllowSlices, &g->table);
     if (int rc = workspace(ctx, 2, n_rb * 4, s, &g->counters, /*zeroed=*/true)) return rc;
     return workspace(ctx, 3, uint64_t{g->table.parts} * 2 * kSkWarps * 32 * 2 * G * 4, s, &g->partials);
 }

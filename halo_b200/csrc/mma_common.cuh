@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cstdint>
 
 namespace halo_cuda {
@@ -221,6 +222,35 @@ struct SkTable {
     uint32_t cols_per_unit;           // ceil(nb / KS)
     uint32_t start[kSkMaxCtas + 1];   // CTA c owns columns [start[c], start[c + 1])
 };
+
+/// Whether the kernels of a weight type may cut K into two in-CTA slices: two columns of x records must fit in shared
+/// memory next to the weight ring at every batch size, which the 5 KB ring slots of repacked Q8_0 do not allow.
+constexpr bool format_allows_slices(uint32_t wtype) { return wtype != 8u /* Q8_0 */; }
+
+/// Host side of the partition: returns the number of K slices (1 or 2) and fills the table.
+/// Columns one CTA walks at most under `ks` slices with whole units per CTA (0: not possible) and with an even split.
+/// The choice is a function of (rows, cols, SM count) alone, so every batch size of a shape gets the same partition.
+inline uint32_t plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool allow_slices, SkTable* table) {
+    const uint64_t n_rb = (uint64_t{rows} + 15) / 16;
+    sms = std::min(sms, kSkMaxCtas);
+    // candidate A: 2 slices, whole units per CTA.  candidate B: 1 slice, even split of the columns, where a CTA pays
+    // roughly three columns' time for the cross-CTA reduction of the units its range cuts.
+    const uint64_t units_a = (n_rb + 7) / 8, cpu_a = (nb + 1) / 2, parts_a = std::min<uint64_t>(sms, units_a);
+    const uint64_t time_a = (units_a + parts_a - 1) / parts_a * cpu_a;
+    const uint64_t units_b = (n_rb + 15) / 16, cols_b = units_b * nb, parts_b = std::min<uint64_t>(sms, cols_b);
+    const uint64_t time_b = (cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : 3);
+    SkTable& t = *table;
+    if (allow_slices && nb >= 2 && time_a <= time_b) {
+        t.parts = static_cast<uint32_t>(parts_a);
+        t.cols_per_unit = static_cast<uint32_t>(cpu_a);
+        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * units_a / parts_a * cpu_a);
+        return 2;
+    }
+    t.parts = static_cast<uint32_t>(parts_b);
+    t.cols_per_unit = nb;
+    for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * cols_b / parts_b);
+    return 1;
+}
 
 /// Row-split tensor parallelism: instead of storing a finished row block to y, push it into slot `rank` of every
 /// peer's receive buffer (peer-mapped memory, plain stores over NVLink).  Every element travels as one 8-byte word

@@ -122,7 +122,7 @@ static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __
 // lane t of a row finishes sub-blocks t and 4 + t; two shuffles build T.  Adding exact zeros leaves S_s bit-identical.
 struct Q4Kf {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1, kXLaneBytes = 16;
-    static constexpr bool kAllowSlices = true;  // two K slices per row block fit in shared memory at every batch size
+    static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr uint32_t kZeroBytes = 1024;  // zeros a single-row call reads for the B columns that carry nothing
 
     /// int byte `idx` of `word` as float (times 1/16 with `sixteenth`) through a 2^23 (2^19) + code bit pattern: exact.
@@ -358,7 +358,7 @@ struct GroupedItem {
 struct Q40r : GroupedItem<Q40r> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kGroupBytes = 144, kPitch = 192, kScaleGroups = 8, kStepsPerGroup = 2;
     static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
-    static constexpr bool kAllowSlices = true;
+    static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr float kZero = 8.0f;
     struct Frag {
         uint4 q[2];  // chunk c: words of blocks 4c..4c+3
@@ -392,7 +392,7 @@ struct Q40r : GroupedItem<Q40r> {
 struct Q80r : GroupedItem<Q80r> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kGroupBytes = 272, kPitch = 320, kScaleGroups = 8, kStepsPerGroup = 2;
     static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
-    static constexpr bool kAllowSlices = false;  // the 5 KB slots leave no room for two columns of x
+    static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr float kZero = 128.0f;
     struct Frag {
         uint4 q[4];  // chunk c: (block 2c, step 0), (block 2c, step 1), (block 2c+1, step 0), (block 2c+1, step 1)
@@ -418,7 +418,7 @@ struct Q80r : GroupedItem<Q80r> {
 struct Q6Kr : GroupedItem<Q6Kr> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kGroupBytes = 224, kPitch = 224, kScaleGroups = 16, kStepsPerGroup = 1;
     static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
-    static constexpr bool kAllowSlices = true;
+    static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr float kZero = 32.0f;
     struct Frag {
         uint4 ql[2];  // half n: words (b, lh) = (0,0), (0,1), (1,0), (1,1)

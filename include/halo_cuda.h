@@ -188,6 +188,18 @@ int halo_cuda_repacked_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes)
 int halo_cuda_repack_rows(HaloCudaCtx* ctx, uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride,
                           uint32_t rows, uint32_t cols, HaloCudaStream stream);
 
+/* ---- the partition of the balanced skinny kernels (variants 3 and 7), for inspection and tests ----------------------
+ * Pure host arithmetic, no device needed: how a rows x cols matmul of `wtype` is cut over a GPU with `sm_count` SMs.
+ * A CTA is (16 / slices) row blocks of 16 W rows x `slices` interleaved K slices; a unit is that many row blocks, a
+ * column one step of 256 * slices elements of K; CTA c walks columns [start[c], start[c + 1]) of the unit-major
+ * sequence (unit u = column / cols_per_unit).  The plan depends on nothing else, in particular not on n_vec. */
+#define HALO_CUDA_PLAN_MAX_CTAS 160
+typedef struct HaloCudaGemvPlan {
+    uint32_t slices, ctas, cols_per_unit, reserved;
+    uint32_t start[HALO_CUDA_PLAN_MAX_CTAS + 1];
+} HaloCudaGemvPlan;
+int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan);
+
 /* ---- the operators ------------------------------------------------------------------------------ */
 int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);
 int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);

@@ -1,0 +1,81 @@
+"""The host-side partition of the balanced skinny kernels (halo_cuda_gemv_plan): every (row block, super-block) tile is
+owned exactly once, ranges are contiguous and non-empty, and the CTAs that share a unit are the ones the kernel's
+last-arriver reduction will count.  Pure host arithmetic: runs without a GPU."""
+from __future__ import annotations
+
+import ctypes as C
+import random
+
+import pytest
+
+from halo_b200 import capi, synth
+
+
+def plan(wtype: int, rows: int, cols: int, sms: int = 148):
+    lib = capi.load()
+    p = capi.GemvPlan()
+    rc = lib.halo_cuda_gemv_plan(wtype, rows, cols, sms, C.byref(p))
+    assert rc == 0, capi.last_error()
+    return p.slices, p.ctas, p.cols_per_unit, list(p.start[: p.ctas + 1])
+
+
+def check(wtype: int, rows: int, cols: int, sms: int = 148):
+    ks, ctas, cpu, start = plan(wtype, rows, cols, sms)
+    nb, n_rb, r_blocks = cols // 256, (rows + 15) // 16, 16 // ks
+    assert ks in (1, 2) and 1 <= ctas <= min(sms, 160) and cpu == (nb + ks - 1) // ks
+    assert start[0] == 0 and all(a < b for a, b in zip(start, start[1:])), "ranges must be contiguous and non-empty"
+    units = (n_rb + r_blocks - 1) // r_blocks
+    assert start[-1] == units * cpu, "the ranges must cover every column of every unit"
+    seen = set()
+    for c in range(ctas):
+        for col in range(start[c], start[c + 1]):
+            unit, k = divmod(col, cpu)
+            for r in range(r_blocks):
+                for s in range(ks):
+                    rb, sb = unit * r_blocks + r, k * ks + s
+                    if rb < n_rb and sb < nb:
+                        assert (rb, sb) not in seen
+                        seen.add((rb, sb))
+    assert len(seen) == n_rb * nb, "every tile exactly once"
+    # a CTA's range touches at most two units partially (its first and its last): two partial records per CTA suffice
+    for c in range(ctas):
+        partial = {col // cpu for col in (start[c], start[c + 1] - 1) if not (start[c] <= (col // cpu) * cpu and (col // cpu + 1) * cpu <= start[c + 1])}
+        assert len(partial) <= 2
+    return ks, ctas
+
+
+def test_plan_of_the_benchmark_shapes():
+    # config 0: whole units per CTA, two K slices, no row block shared between CTAs
+    assert check(synth.Q4_K, 17408, 5120) == (2, 136)
+    ks, ctas, cpu, start = plan(synth.Q4_K, 17408, 5120)
+    assert all(s % cpu == 0 for s in start)
+    # config 1: too few row blocks for that; an even split of the columns over all SMs
+    assert check(synth.Q6_K, 5120, 17408) == (1, 148)
+    assert check(synth.Q8_0, 5120, 17408) == (1, 148)
+    # config 4 head and a tensor-parallel shard of it
+    assert check(synth.Q4_0, 151936, 5120) == (1, 148)
+    assert check(synth.Q4_0, 18992, 5120)[1] == 148
+    # Q8_0 never takes two slices
+    assert check(synth.Q8_0, 17408, 5120)[0] == 1
+
+
+def test_plan_does_not_depend_on_anything_but_shape_and_sm_count():
+    a = plan(synth.Q4_K, 4096, 4096)
+    assert a == plan(synth.Q4_K, 4096, 4096)
+    assert plan(synth.Q4_K, 4096, 4096, 132) != a or a[1] <= 132
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_plan_covers_random_shapes(seed):
+    rng = random.Random(seed)
+    for _ in range(60):
+        wtype = rng.choice([synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q4_0])
+        check(wtype, rng.randint(1, 40000), 256 * rng.randint(1, 70), rng.choice([148, 132, 8, 1, 160, 400]))
+
+
+def test_plan_rejects_what_the_kernels_do_not_take():
+    lib = capi.load()
+    p = capi.GemvPlan()
+    assert lib.halo_cuda_gemv_plan(synth.Q4_K, 16, 1000, 148, C.byref(p)) == capi.E_MODEL
+    assert lib.halo_cuda_gemv_plan(0, 16, 1024, 148, C.byref(p)) == capi.E_UNSUPPORTED
+    assert lib.halo_cuda_gemv_plan(synth.Q4_K, 0, 1024, 148, C.byref(p)) == capi.E_KERNEL
