@@ -83,17 +83,36 @@ __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, 
 /// Bytes of global scratch stage_x_rec_kernel fills: the records of all super-blocks, then 16 reciprocal scales.
 inline uint64_t stage_rec_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * xrec_bytes(n_tok) + 64; }
 
-/// One block per x row: the row's power-of-two scale, then its records.
+/// One block per x row: the row's power-of-two scale, then its records.  Rows of up to kKeep quads per thread are read
+/// once and converted from registers; longer ones are read again after the scale is known.
 static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
                                                                  uint32_t nb, uint32_t n_tok) {
     __shared__ float red[16];
     __shared__ float sc[2];
+    constexpr uint32_t kKeep = 10, kThreads = 512;
+    // Programmatic dependent launch on both sides: the matmul behind this kernel may start filling its weight ring
+    // now; x and the scratch records belong to the kernels before this one until they have completed.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    const float4* xr = reinterpret_cast<const float4*>(xrow);
+    const uint32_t n_quads = nb * 64u;
+    const bool keep = n_quads <= kKeep * kThreads;
+    float4 v[kKeep];
     float m = 0.0f;
-    for (uint32_t i = tid; i < nb * 64u; i += 512) {
-        const float4 v = reinterpret_cast<const float4*>(xrow)[i];
-        m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    if (keep) {
+#pragma unroll
+        for (uint32_t i = 0; i < kKeep; ++i) {
+            const uint32_t qd = tid + i * kThreads;
+            v[i] = qd < n_quads ? xr[qd] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            m = fmaxf(fmaxf(m, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+        }
+    } else {
+        for (uint32_t i = tid; i < n_quads; i += kThreads) {
+            const float4 u = xr[i];
+            m = fmaxf(fmaxf(m, fmaxf(fabsf(u.x), fabsf(u.y))), fmaxf(fabsf(u.z), fabsf(u.w)));
+        }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
@@ -105,7 +124,15 @@ static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __
         row_scale(a, sc[0], sc[1]);
     }
     __syncthreads();
-    stage_row_rec(scratch, xrow, sc[0], nb, n_tok, tk, tid, 512);
+    if (keep) {
+#pragma unroll
+        for (uint32_t i = 0; i < kKeep; ++i) {
+            const uint32_t qd = tid + i * kThreads;  // whole warps are inside or outside the row: n_quads is a multiple of 64
+            if (qd < n_quads) stage_quad(scratch, v[i], sc[0], qd, n_tok, tk);
+        }
+    } else {
+        stage_row_rec(scratch, xrow, sc[0], nb, n_tok, tk, tid, kThreads);
+    }
     if (tid == 0) reinterpret_cast<float*>(scratch + uint64_t{nb} * xrec_bytes(n_tok))[tk] = sc[1];
 }
 
