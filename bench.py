@@ -503,6 +503,28 @@ def run_ours(args) -> None:
                                 "traffic": None, "peak_source": pkk["source"], "flops_per_launch": flops},
                    "l2": "operands larger than L2: W 50 MB + x 42 MB + y 143 MB per call", "gpu_launches": 2 * psteps}
 
+        # the other two batch sizes of config 2, same weights (timed with fewer repetitions)
+        by_m = [{"m": pm, "ms_per_call": pms, "tflops_per_gpu": flops / (pms * 1e-3) / 1e12}]
+        if not args.profile:
+            for om in (512, 4096):
+                xo = be.import_host_readonly(synth.activations(om, K_COLS, rank, 4))
+                yo = be.allocate(om * N_ROWS * 4, zero=False)
+                ostruct = be._gemv_struct(hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[0]), hb.TensorRef.of(xo), hb.TensorRef.of(yo), N_ROWS,
+                                                       K_COLS, om, 0, allow_gemm=True), "MATMUL", False)
+
+                def other_pass(g=ostruct):
+                    rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+                    if rc != 0:
+                        raise hb.HaloError(rc, capi.last_error())
+
+                for _ in range(3):
+                    other_pass()
+                osteps = max(1, psteps // 2)
+                oms = timed(other_pass, osteps) / osteps
+                by_m.append({"m": om, "ms_per_call": oms, "tflops_per_gpu": 2.0 * om * N_ROWS * K_COLS / (oms * 1e-3) / 1e12})
+                xo.free()
+                yo.free()
+        prefill["by_m"] = sorted(by_m, key=lambda r: r["m"])
         if world > 1:  # the same GEMM with N column-split over the ranks (strong scaling; no collective: each rank keeps its columns)
             n_split = N_ROWS // world
             sargs = hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[0]), hb.TensorRef.of(xpb), hb.TensorRef.of(ypb), n_split, K_COLS, pm, 0,
