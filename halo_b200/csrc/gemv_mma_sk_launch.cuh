@@ -6,6 +6,12 @@
 namespace halo_cuda {
 namespace sk {
 
+constexpr int kResidentMaxTok = 4;  // larger batches always stream x
+// Stages of a warp's weight ring.  Two (one tile being read, one in flight) measured faster than three or four on every
+// shape: the per-warp streams already keep far more bytes in flight than the memory system needs, and deeper rings
+// only spread the DRAM accesses over more rows at a time.
+constexpr int kRingStages = 2;
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -117,8 +123,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
 
 template <class F, int NTOK, int KS>
 int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
-    // the deepest ring that leaves room for two columns of x at the widest batch
-    constexpr int NS = SkLayout<F, 16, 3, KS>::kOffData + 2 * KS * XRec<16>::kBytes <= kSmemBudget ? 3 : 2;
+    constexpr int NS = kRingStages;
     using L = SkLayout<F, NTOK, NS, KS>;
     constexpr uint32_t kXSlot = KS * L::kRec;
     static_assert(L::kOffData + 2 * kXSlot <= kSmemBudget, "two columns of x must fit next to the ring");
@@ -145,15 +150,12 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     return 0;
 }
 
-constexpr int kResidentMaxTok = 4;  // larger batches always stream x
-
-/// n rows starting at tok0: the resident kernel with the deepest ring that leaves room for x, else the streamed one.
+/// n rows starting at tok0: the resident kernel when all of x fits next to the ring, else the streamed one.
 template <class F, int NTOK, int KS>
 int launch_sliced(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
     if constexpr (NTOK <= kResidentMaxTok) {
         const uint64_t x_bytes = uint64_t{g.nb} * XRec<NTOK>::kBytes;
-        if (SkLayout<F, NTOK, 3, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, 3, KS>(ctx, c, g, tok0, s);
-        if (SkLayout<F, NTOK, 2, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, 2, KS>(ctx, c, g, tok0, s);
+        if (SkLayout<F, NTOK, kRingStages, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, kRingStages, KS>(ctx, c, g, tok0, s);
     }
     return launch_streamed<F, NTOK, KS>(ctx, c, g, tok0, s);
 }
