@@ -268,6 +268,19 @@ public:
     void argmax(Stream&, const ArgmaxArgs&) override { unsupported(OpId::Argmax); }
     void top_k(Stream&, const TopKArgs&) override { unsupported(OpId::TopK); }
 
+    std::unique_ptr<Buffer> repack(Stream& s, DType wtype, const TensorRef& src, std::uint32_t rows, std::uint32_t cols) {
+        CudaStream& cs = stream_of(s, "repack");
+        std::uint64_t raw = 0, packed = 0;
+        check(halo_cuda_row_bytes(static_cast<std::uint32_t>(wtype), cols, &raw));
+        check(halo_cuda_repacked_row_bytes(static_cast<std::uint32_t>(wtype), cols, &packed));
+        const std::byte* from = resolve(src, extent(rows, raw, src.row_stride, "repack", "src"), Access::Read, "repack", "src");
+        void* p = nullptr;
+        check(halo_cuda_malloc(ctx_, std::max<std::uint64_t>(mul_u64(rows, packed, "repack", "dst"), 16), 0, &p));
+        auto buf = std::make_unique<CudaBuffer>(this, ctx_, p, mul_u64(rows, packed, "repack", "dst"), false);
+        check(halo_cuda_repack_rows(ctx_, static_cast<std::uint32_t>(wtype), from, src.row_stride, p, 0, rows, cols, cs.handle()));
+        return buf;
+    }
+
     void set_plan(std::span<const CudaPlanEntry> plan) {
         check(halo_cuda_plan_clear(ctx_));
         for (const CudaPlanEntry& p : plan)
@@ -326,11 +339,12 @@ private:
     HaloCudaGemv gemv_struct(const GemvArgs& a, const char* op, bool y_optional) const {
         HALO_CHECK(a.norm_w.empty(), ErrorCode::Unsupported, "{}: a fused norm (GemvArgs::norm_w) is Vulkan-only", op);
         HALO_CHECK(a.gates.n_v == 0, ErrorCode::Unsupported, "{}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only", op);
-        std::uint64_t rb = 0;
-        check(halo_cuda_row_bytes(static_cast<std::uint32_t>(a.wtype), a.cols, &rb));
         HaloCudaGemv g{};
         g.wtype = static_cast<std::uint32_t>(a.wtype);
         g.variant_id = a.kernel.variant_id != 0 ? a.kernel.variant_id : options_.default_gemv_variant;
+        std::uint64_t rb = 0;
+        if (g.variant_id == HALO_CUDA_GEMV_MMA_R) check(halo_cuda_repacked_row_bytes(g.wtype, a.cols, &rb));  // W is in the variant's layout
+        else check(halo_cuda_row_bytes(g.wtype, a.cols, &rb));
         g.w = resolve(a.w, extent(a.rows, rb, a.w.row_stride, op, "w"), Access::Read, op, "w");
         g.w_stride = a.w.row_stride;
         g.x = reinterpret_cast<const float*>(resolve(a.x, extent(a.n_vec, mul_u64(a.cols, 4, op, "x"), a.x.row_stride, op, "x"), Access::Read, op, "x"));
@@ -356,6 +370,13 @@ const Backend* CudaBuffer::backend() const noexcept { return owner_; }
 }  // namespace
 
 std::unique_ptr<Backend> make_cuda_backend(const CudaBackendOptions& options) { return std::make_unique<CudaBackend>(options); }
+
+std::unique_ptr<Buffer> cuda_backend_repack(Backend& backend, Stream& stream, DType wtype, const TensorRef& src, std::uint32_t rows,
+                                            std::uint32_t cols) {
+    auto* cb = dynamic_cast<CudaBackend*>(&backend);
+    HALO_CHECK(cb != nullptr, ErrorCode::Api, "cuda_backend_repack: not a cuda backend");
+    return cb->repack(stream, wtype, src, rows, cols);
+}
 
 void cuda_backend_set_plan(Backend& backend, std::span<const CudaPlanEntry> plan) {
     auto* cb = dynamic_cast<CudaBackend*>(&backend);

@@ -39,6 +39,13 @@ struct CudaPlanEntry {
 /// Throws Error(Device) when no sm_100 device is usable, Error(Config) for an unknown default variant.
 [[nodiscard]] std::unique_ptr<Backend> make_cuda_backend(const CudaBackendOptions& options = {});
 
+/// The load-time weight repack of the gemv_mma_r variant (id 7), the counterpart of tensor::gemv_repack for the
+/// reference's repacked Vulkan matvecs (include/halo/tensor/repack.h:11-36): `rows` raw GGUF rows of Q6_K / Q8_0 /
+/// Q4_0 (cols a multiple of 256) -> a new read-only device buffer in the repacked row layout, to be passed as
+/// GemvArgs::w together with KernelChoice{7}.  Error(Unsupported) for other types, Error(Api) for another backend.
+[[nodiscard]] std::unique_ptr<Buffer> cuda_backend_repack(Backend& backend, Stream& stream, DType wtype, const TensorRef& src, std::uint32_t rows,
+                                                          std::uint32_t cols);
+
 /// Installs tuner decisions on a backend made by make_cuda_backend (Error(Api) for any other backend).
 void cuda_backend_set_plan(Backend& backend, std::span<const CudaPlanEntry> plan);
 

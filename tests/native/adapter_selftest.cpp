@@ -155,6 +155,53 @@ void test_gemv_bitwise(Pair& p, Report& r) {
     }
 }
 
+/// The repacked-layout tensor-core variant through the adapter: repack once, KernelChoice{7}, rows of any batch size.
+void test_gemv_repacked(Pair& p, Report& r) {
+    struct Case {
+        DType t;
+        std::uint32_t n, k, m;
+    };
+    const Case cases[] = {{DType::Q6_K, 37, 2560, 1}, {DType::Q8_0, 130, 512, 5}, {DType::Q4_0, 50, 5120, 16}};
+    for (const Case& c : cases) {
+        const auto w = random_weights(c.t, c.n, c.k, 20 + c.n);
+        const auto x = random_floats(std::size_t{c.m} * c.k, 21);
+        std::vector<float> yc, yg;
+        run_gemv_both(p, c.t, w, x, c.n, c.k, c.m, 1 /*gemv_exact8*/, yc, yg);  // yc: the CPU backend
+        const auto raw = p.gpu->import_host_readonly(w);
+        const auto packed = hb::cuda_backend_repack(*p.gpu, *p.gst, c.t, hb::TensorRef::of(*raw), c.n, c.k);
+        const auto xb = p.gpu->import_host_readonly(cbytes(x.data(), x.size() * 4));
+        const auto yb = p.gpu->allocate(yg.size() * 4, hb::Tier::Vram);
+        p.gpu->gemv(*p.gst, {c.t, hb::TensorRef::of(*packed), hb::TensorRef::of(*xb), hb::TensorRef::of(*yb), c.n, c.k, c.m, {7}});
+        p.gpu->download(*p.gst, hb::TensorRef::of(*yb), wbytes(yg.data(), yg.size() * 4));
+        p.gst->wait();
+        float maxref = 0, maxerr = 0;
+        for (std::size_t i = 0; i < yc.size(); ++i) {
+            maxref = std::max(maxref, std::fabs(yc[i]));
+            maxerr = std::max(maxerr, std::fabs(yc[i] - yg[i]));
+        }
+        r.expect(maxerr <= 1e-3f * maxref, std::format("gemv_mma_r over repacked rows within 1e-3 of the CPU backend (type {}): {} vs {}", static_cast<int>(c.t), maxerr, maxref));
+        // a raw-sized operand must not pass as a repacked one where the layouts differ in size
+        if (c.t == DType::Q6_K) {
+            bool thrown = false;
+            try {
+                p.gpu->gemv(*p.gst, {c.t, hb::TensorRef::of(*raw), hb::TensorRef::of(*xb), hb::TensorRef::of(*yb), c.n, c.k, c.m, {7}});
+            } catch (const halo::Error& e) {
+                thrown = e.code() == halo::ErrorCode::Kernel;
+            }
+            r.expect(thrown, "raw Q6_K rows are too short for the repacked variant: Error(Kernel)");
+        }
+    }
+    bool refused = false;
+    try {
+        const auto w = random_weights(DType::Q4_K, 16, 256, 5);
+        const auto raw = p.gpu->import_host_readonly(w);
+        (void)hb::cuda_backend_repack(*p.gpu, *p.gst, DType::Q4_K, hb::TensorRef::of(*raw), 16, 256);
+    } catch (const halo::Error& e) {
+        refused = e.code() == halo::ErrorCode::Unsupported;
+    }
+    r.expect(refused, "Q4_K has no repacked layout: Error(Unsupported)");
+}
+
 void test_validation_parity(Pair& p, Report& r) {
     const std::uint32_t N = 8, K = 64, T = 2;
     const auto w = random_weights(DType::Q8_0, N, K, 3);
@@ -330,6 +377,7 @@ extern "C" int halo_adapter_selftest(char* report, std::size_t len) {
     try {
         Pair p;
         test_registry(p, r);
+        test_gemv_repacked(p, r);
         test_gemv_bitwise(p, r);
         test_validation_parity(p, r);
         test_lm_head(p, r);
