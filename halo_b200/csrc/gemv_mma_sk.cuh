@@ -61,7 +61,7 @@ __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) { a
 template <int G, int NTOK, int KS>
 __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit, uint32_t r, uint32_t ks, float* red, const SkTable& tb, uint32_t cta,
                                              float* part, uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows,
-                                             uint32_t lane, const PeerPush& peer) {
+                                             uint32_t lane, uint32_t row, const PeerPush& peer) {
     constexpr int R = kSkWarps / KS;
     if constexpr (KS > 1) {
         if (ks != 0) {
@@ -79,7 +79,7 @@ __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit,
         }
         named_barrier(1 + r, KS * 32);  // the slices may overwrite `red` at their next block only after slice 0 has read it
     }
-    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, s_inv, y, y_stride, rows, lane, peer);
+    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, s_inv, y, y_stride, rows, lane, row, peer);
 #pragma unroll
     for (int gi = 0; gi < G; ++gi) yacc[gi][0] = yacc[gi][1] = 0.0f;
 }
@@ -212,7 +212,9 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
     }
 
     const XLane<G> xl = make_xlane<NTOK, F::kXLaneBytes>(g, t);
-    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + g * F::kPitch;
+    // fragment row g of the MMA reads slot row F::slot_row(g) (a format may permute the rows of a tile against bank conflicts)
+    const uint32_t row = F::slot_row(g);
+    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + row * F::kPitch;
     float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
     float yacc[G][2];
 #pragma unroll
@@ -241,7 +243,7 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                 refill();  // keeps the producer in step
             }
             if (cons.k + 1 == cpu || cons.col + 1 == cons.end)  // the row block, or this CTA's share of it, is done
-                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, peer);
+                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, row, peer);
         } else {
             refill();
         }
@@ -314,7 +316,9 @@ gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
         for (uint32_t c = col_lo; c < col_lo + x_slots && c < col_hi; ++c) fetch_x(c);
 
     const XLane<G> xl = make_xlane<NTOK, F::kXLaneBytes>(g, t);
-    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + g * F::kPitch;
+    // fragment row g of the MMA reads slot row F::slot_row(g) (a format may permute the rows of a tile against bank conflicts)
+    const uint32_t row = F::slot_row(g);
+    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + row * F::kPitch;
     float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
     float yacc[G][2];
 #pragma unroll
@@ -346,7 +350,7 @@ gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                     refill();
                 }
                 if (cons.k + 1 == cpu || c + 1 == col_hi)
-                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, peer);
+                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, row, peer);
             } else {
                 refill();
             }

@@ -276,8 +276,8 @@ __device__ __forceinline__ unsigned long long peer_word(float v, uint32_t tag) {
 template <int G, int NTOK, int R>
 __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
                                          uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
-                                         const PeerPush& peer) {
-    const uint32_t g = lane >> 2, t = lane & 3u, rb = unit * R + r;
+                                         uint32_t g /* the W row of the block (0..7, and + 8) this lane's sums belong to */, const PeerPush& peer) {
+    const uint32_t t = lane & 3u, rb = unit * R + r;
     const uint32_t u_lo = unit * tb.cols_per_unit, u_hi = u_lo + tb.cols_per_unit;  // the unit's columns
     uint32_t c_lo = cta, c_hi = cta;
     while (c_lo > 0 && tb.start[c_lo] > u_lo) --c_lo;

@@ -151,6 +151,7 @@ struct Q4Kf {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1, kXLaneBytes = 16;
     static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr uint32_t kZeroBytes = 1024;  // zeros a single-row call reads for the B columns that carry nothing
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
     /// int byte `idx` of `word` as float (times 1/16 with `sixteenth`) through a 2^23 (2^19) + code bit pattern: exact.
     __device__ static __forceinline__ float code_to_float(uint32_t word, uint32_t idx, bool sixteenth) {
@@ -283,6 +284,7 @@ struct Q4Kf {
 template <class T>
 struct GroupedItem {
     static constexpr uint32_t kZeroBytes = 1024;
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
     template <int G, int NTOK, class Release>
     __device__ static __forceinline__ void item(const uint8_t* r0, uint32_t t, const uint8_t* rec, const XLane<G>& xl, const uint8_t* zeros,
@@ -447,6 +449,9 @@ struct Q6Kr : GroupedItem<Q6Kr> {
     static constexpr uint32_t kItemCoord = kGroupBytes / 4, kBoxInner = kPitch / 4, kMapElemBytes = 4, kXLaneBytes = 8;
     static constexpr bool kAllowSlices = format_allows_slices(kType);
     static constexpr float kZero = 32.0f;
+    /// The 224-byte slot rows put rows g and g + 1 on overlapping banks; fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7
+    /// instead (rows two apart are 64 bytes apart modulo the 128-byte bank span), and y is stored accordingly.
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return ((2u * g) & 7u) | (g >> 2); }
     struct Frag {
         uint4 ql[2];  // half n: words (b, lh) = (0,0), (0,1), (1,0), (1,1)
         uint4 qh;     // words (n, lh) = (0,0), (0,1), (1,0), (1,1)
