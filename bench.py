@@ -425,19 +425,26 @@ def run_ours(args) -> None:
         sampler.start()
     ms = timed(one_pass, args.steps)
 
-    # ---- e2e: the same pass through the public call with host buffers (pinned x up, y down, one wait per step)
+    # ---- e2e: the same pass through the public calls with host buffers: the step's COPIES x rows go up from pinned memory in
+    # one copy, every matmul reads its own row and writes its own y, the step's COPIES y rows come down in one copy, one wait
     hx, hy = C.c_void_p(), C.c_void_p()
-    lib.halo_cuda_host_alloc(ctx, K_COLS * 4, C.byref(hx))
+    lib.halo_cuda_host_alloc(ctx, COPIES * K_COLS * 4, C.byref(hx))
     lib.halo_cuda_host_alloc(ctx, COPIES * N_ROWS * 4, C.byref(hy))
-    C.memmove(hx.value, x.ctypes.data, K_COLS * 4)
+    for i in range(COPIES):
+        C.memmove(hx.value + i * K_COLS * 4, x.ctypes.data, K_COLS * 4)
+    x_all = be.allocate(COPIES * K_COLS * 4)
+    y_all = be.allocate(COPIES * N_ROWS * 4)
+    e2e_structs = [be._gemv_struct(hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef(x_all, i * K_COLS * 4, K_COLS * 4),
+                                               hb.TensorRef(y_all, i * N_ROWS * 4, N_ROWS * 4), N_ROWS, K_COLS, 1, args.variant), "MATMUL", False)
+                   for i in range(COPIES)]
 
     def e2e_pass():
-        for i, g in enumerate(structs):
-            lib.halo_cuda_memcpy_h2d_async(ctx, g.x, hx, K_COLS * 4, st.handle)
+        lib.halo_cuda_memcpy_h2d_async(ctx, C.c_void_p(x_all.ptr), hx, COPIES * K_COLS * 4, st.handle)
+        for g in e2e_structs:
             rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
             if rc != 0:
                 raise hb.HaloError(rc, capi.last_error())
-            lib.halo_cuda_memcpy_d2h_async(ctx, hy.value + i * N_ROWS * 4, g.y, N_ROWS * 4, st.handle)
+        lib.halo_cuda_memcpy_d2h_async(ctx, hy, C.c_void_p(y_all.ptr), COPIES * N_ROWS * 4, st.handle)
         st.wait()
 
     for _ in range(0 if args.profile else 3):
