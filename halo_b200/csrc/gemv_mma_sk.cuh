@@ -60,7 +60,7 @@ __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) { a
 /// memory (`red`: [r][ks - 1][lane][2G] floats), then slice 0 hands the sums over.
 template <int G, int NTOK, int KS>
 __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit, uint32_t r, uint32_t ks, float* red, const SkTable& tb, uint32_t cta,
-                                             float* part, uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows,
+                                             float* part, uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows,
                                              uint32_t lane, uint32_t row, const PeerPush& peer) {
     constexpr int R = kSkWarps / KS;
     if constexpr (KS > 1) {
@@ -79,7 +79,7 @@ __device__ __forceinline__ void finish_block(float (&yacc)[G][2], uint32_t unit,
         }
         named_barrier(1 + r, KS * 32);  // the slices may overwrite `red` at their next block only after slice 0 has read it
     }
-    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, s_inv, y, y_stride, rows, lane, row, peer);
+    if (ks == 0) sk_flush<G, NTOK, R>(yacc, unit, r, tb, cta, part, counters, y, y_stride, rows, lane, row, peer);
 #pragma unroll
     for (int gi = 0; gi < G; ++gi) yacc[gi][0] = yacc[gi][1] = 0.0f;
 }
@@ -144,9 +144,6 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
     // The weights never depend on the kernel before this one, so the ring is filled first; only now wait for it.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    float* s_scale = reinterpret_cast<float*>(smem + kOffScale);
-    float* s_inv = reinterpret_cast<float*>(smem + kOffInv);
-    float* s_red = reinterpret_cast<float*>(smem + kOffRed);
     const uint32_t xbar = smem_base + kOffXBar;
     bool lost = false;
     for (uint32_t i = tid; i < L::kZeroBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffZero)[i] = 0u;  // before the barriers below
@@ -158,56 +155,16 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
             for (uint32_t off = 0; off < nb * kRec; off += 32768u)  // records are multiples of 16 bytes
                 bulk_g2s(smem_base + kOffData + off, xstage + off, min(32768u, nb * kRec - off), xbar);
         }
-        if (tid < NTOK) s_inv[tid] = reinterpret_cast<const float*>(xstage + uint64_t{nb} * kRec)[tid];
         __syncthreads();
         if (!mbar_wait(xbar, 0)) {
             if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
             lost = true;
         }
     } else {
-        // One row at a time: its largest magnitude gives the power-of-two scale.  Rows of up to kKeep quads per thread
-        // are read once and converted from registers; longer ones are read again after the scale is known.
-        constexpr uint32_t kKeep = 10;
-        const uint32_t n_quads = nb * 64u;
-        for (uint32_t tk = 0; tk < NTOK; ++tk) {
-            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-            const bool keep = n_quads <= kKeep * kThreads;
-            float4 v[kKeep];
-            float m = 0.0f;
-            if (keep) {
-#pragma unroll
-                for (uint32_t i = 0; i < kKeep; ++i) {
-                    const uint32_t qd = tid + i * kThreads;
-                    v[i] = qd < n_quads ? xr[qd] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    m = fmaxf(fmaxf(m, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
-                }
-            } else {
-                for (uint32_t i = tid; i < n_quads; i += kThreads) {
-                    const float4 u = xr[i];
-                    m = fmaxf(fmaxf(m, fmaxf(fabsf(u.x), fabsf(u.y))), fmaxf(fabsf(u.z), fabsf(u.w)));
-                }
-            }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-            if (lane == 0) s_red[warp] = m;
-            __syncthreads();
-            if (tid == 0) {
-                float a = 0.0f;
-                for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
-                row_scale(a, s_scale[tk], s_inv[tk]);
-            }
-            __syncthreads();
-            const float sc = s_scale[tk];
-            if (keep) {
-#pragma unroll
-                for (uint32_t i = 0; i < kKeep; ++i) {
-                    const uint32_t qd = tid + i * kThreads;  // whole warps are inside or outside the row: n_quads is a multiple of 64
-                    if (qd < n_quads) stage_quad(smem + kOffData, v[i], sc, qd, NTOK, tk);
-                }
-            } else {
-                stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(xr), sc, nb, NTOK, tk, tid, kThreads);
-            }
-        }
+        // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
+        for (uint32_t tk = 0; tk < NTOK; ++tk)
+            stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), nb, NTOK, tk,
+                          warp, kWarps, lane);
         __syncthreads();
     }
 
@@ -243,7 +200,7 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                 refill();  // keeps the producer in step
             }
             if (cons.k + 1 == cpu || cons.col + 1 == cons.end)  // the row block, or this CTA's share of it, is done
-                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, row, peer);
+                finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, row, peer);
         } else {
             refill();
         }
@@ -302,10 +259,8 @@ gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
     for (int it = 0; it < NS; ++it) refill();
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    float* s_inv = reinterpret_cast<float*>(smem + kOffInv);
-    if (tid < NTOK) s_inv[tid] = reinterpret_cast<const float*>(xstage + uint64_t{nb} * kRec)[tid];
     for (uint32_t i = tid; i < L::kZeroBytes / 4; i += kSkWarps * 32) reinterpret_cast<uint32_t*>(smem + L::kOffZero)[i] = 0u;
-    __syncthreads();  // barriers initialised, reciprocal scales and zeros in place
+    __syncthreads();  // barriers initialised, zeros in place
     // x ring: column c of this CTA (super-blocks k * KS .. k * KS + KS - 1 of x) goes to slot (c - col_lo) % x_slots
     auto fetch_x = [&](uint32_t c) {  // called by thread 0
         const uint32_t xs = (c - col_lo) % x_slots, sb0 = (c % cpu) * KS, bytes = min(static_cast<uint32_t>(KS), nb - sb0) * kRec;
@@ -350,7 +305,7 @@ gemv_sk_streamed_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                     refill();
                 }
                 if (cons.k + 1 == cpu || c + 1 == col_hi)
-                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, s_inv, y, y_stride, rows, lane, row, peer);
+                    finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, row, peer);
             } else {
                 refill();
             }

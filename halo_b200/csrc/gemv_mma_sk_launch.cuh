@@ -52,10 +52,11 @@ inline cudaLaunchConfig_t pdl_config(uint32_t grid, uint32_t smem, cudaStream_t 
     return cfg;
 }
 
-/// The x conversion of a batched call: one block per x row, launched so that it overlaps the tail of the kernel before it.
+/// The x conversion of a batched call: one warp per super-block, launched so that it overlaps the tail of the kernel before it.
 inline int launch_stage(const float* x, uint64_t x_stride, uint8_t* scratch, uint32_t nb, uint32_t n_tok, cudaStream_t s) {
     cudaLaunchAttribute attr[1];
-    const cudaLaunchConfig_t cfg = pdl_config(n_tok, 0, s, attr);
+    cudaLaunchConfig_t cfg = pdl_config(n_tok, 0, s, attr);
+    cfg.gridDim = dim3(n_tok, (nb + 15u) / 16u);
     HC_CUDA(cudaLaunchKernelEx(&cfg, stage_x_rec_kernel, x, x_stride, scratch, nb, n_tok));
     return 0;
 }

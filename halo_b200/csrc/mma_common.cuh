@@ -275,7 +275,7 @@ __device__ __forceinline__ unsigned long long peer_word(float v, uint32_t tag) {
 /// 32 lanes x 2G floats; `counters` one zeroed word per row block, left zeroed.
 template <int G, int NTOK, int R>
 __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
-                                         uint32_t* counters, const float* s_inv, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
+                                         uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
                                          uint32_t g /* the W row of the block (0..7, and + 8) this lane's sums belong to */, const PeerPush& peer) {
     const uint32_t t = lane & 3u, rb = unit * R + r;
     const uint32_t u_lo = unit * tb.cols_per_unit, u_hi = u_lo + tb.cols_per_unit;  // the unit's columns
@@ -332,10 +332,9 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
         for (int gi = 0; gi < G; ++gi) {
             const uint32_t tk = 4u * gi + t;
             if (tk < NTOK) {
-                const float inv = s_inv[tk];
                 const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
                 const uint64_t at = slot + uint64_t{tk} * rows;  // the pushed rows are dense: [x row][W row]
-                const unsigned long long w0 = peer_word(sum[gi][0] * inv, next), w1 = peer_word(sum[gi][1] * inv, next);
+                const unsigned long long w0 = peer_word(sum[gi][0], next), w1 = peer_word(sum[gi][1], next);
                 for (uint32_t p = 0; p < peer.world; ++p) {
                     if (n0 < rows) peer.slots[p][at + n0] = w0;
                     if (n1 < rows) peer.slots[p][at + n1] = w1;
@@ -348,11 +347,10 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
     for (int gi = 0; gi < G; ++gi) {
         const uint32_t tk = 4u * gi + t;
         if (tk < NTOK) {
-            const float inv = s_inv[tk];
             float* yr = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{tk} * y_stride);
             const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
-            if (n0 < rows) yr[n0] = sum[gi][0] * inv;
-            if (n1 < rows) yr[n1] = sum[gi][1] * inv;
+            if (n0 < rows) yr[n0] = sum[gi][0];
+            if (n1 < rows) yr[n1] = sum[gi][1];
         }
     }
 }

@@ -6,10 +6,14 @@
 // columns, fp32 accumulation in mma.sync m16n8k16; a lane (g = lane / 4, t = lane % 4) owns rows g and g + 8 of the
 // tile and the B columns 2t, 2t + 1 of every 8-column group.
 //
-// x record of one super-block for NTOK rows (what stage_row_rec writes and an item reads), kRec = 1120 * NTOK bytes:
+// x is scaled per super-block (256 elements, what one warp converts at a time): s = the power of two that puts the
+// super-block's largest magnitude near 2^13, so the conversion needs no pass over the whole row and no block-wide
+// reduction, and an item folds 1 / s into its final multiply.
+// x record of one super-block for NTOK rows (what stage_superblock writes and an item reads):
 //   [sub-block 0..7][column 0..2*NTOK-1][64 B]   fp16 hi (even column) / lo (odd column) of x * s, in quads of 8 bytes
 //   [column][16 B]                               sum of each 32-element sub-block / 32 as fp16 hi / lo (Q4_K min term)
 //   [16-element group 0..15][row] fp32           sums of x * s over 16 elements (zero points of the other formats)
+//   [row] fp32                                   1 / s (padded to 16 bytes)
 #pragma once
 #include "halo_cuda.h"
 #include "mma_common.cuh"
@@ -20,9 +24,10 @@ namespace mma {
 template <int NTOK>
 struct XRec {
     static constexpr uint32_t kCols = 2 * NTOK, kSubStride = kCols * 64u, kSbStride = kCols * 16u, kSx16Bytes = 64u * NTOK;
-    static constexpr uint32_t kOffSums = 8u * kSubStride, kOffSx16 = kOffSums + kSbStride, kBytes = kOffSx16 + kSx16Bytes;
+    static constexpr uint32_t kOffSums = 8u * kSubStride, kOffSx16 = kOffSums + kSbStride, kOffInv = kOffSx16 + kSx16Bytes;
+    static constexpr uint32_t kBytes = kOffInv + ((4u * NTOK + 15u) & ~15u);
 };
-inline constexpr uint32_t xrec_bytes(uint32_t n_tok) { return 1120u * n_tok; }
+inline constexpr uint32_t xrec_bytes(uint32_t n_tok) { return 1120u * n_tok + ((4u * n_tok + 15u) & ~15u); }
 
 /// Lane-constant byte offsets into an x record: B fragments and sums of this lane's column in each column group.
 /// A lane whose column carries no row reads the last real column; what it computes is never stored.
@@ -44,96 +49,84 @@ __device__ __forceinline__ XLane<(NTOK + 3) / 4> make_xlane(uint32_t g, uint32_t
     return xl;
 }
 
-/// One quad (4 consecutive elements, index qd within the row) of x * s into the records at `area`: fp16 hi / lo, and its
-/// share of the 16- and 32-element sums.  The eight lanes that hold a sub-block's quads must call it together.
-__device__ __forceinline__ void stage_quad(uint8_t* area, float4 v, float s, uint32_t qd, uint32_t n_tok, uint32_t tok) {
+/// One super-block (index sb) of an x row into its record at `area`, by one warp: lane l holds quads l and l + 32
+/// (elements 4l .. 4l + 3 and 128 + 4l .. ) in v; the scale comes from the largest magnitude among the 64 quads.
+__device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v)[2], uint32_t sb, uint32_t n_tok, uint32_t tok, uint32_t lane) {
     const uint32_t rec = xrec_bytes(n_tok), sub_stride = 128u * n_tok;
-    v.x *= s; v.y *= s; v.z *= s; v.w *= s;
-    uint2 hi, lo;
-    split4(v, hi, lo);
-    const uint32_t sb = qd >> 6, sub = (qd >> 3) & 7u, in = qd & 7u;  // 8 quads per 32-element sub-block
+    float m = 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) m = fmaxf(fmaxf(m, fmaxf(fabsf(v[h].x), fabsf(v[h].y))), fmaxf(fabsf(v[h].z), fabsf(v[h].w)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    float s, inv;
+    row_scale(m, s, inv);
     uint8_t* base = area + sb * rec;
-    uint8_t* dst = base + sub * sub_stride + tok * 128u + in * 8u;
-    *reinterpret_cast<uint2*>(dst) = hi;
-    *reinterpret_cast<uint2*>(dst + 64) = lo;
-    float sum = (v.x + v.y) + (v.z + v.w);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     uint8_t* sums = base + 8u * sub_stride;
-    if ((in & 3u) == 0) reinterpret_cast<float*>(sums + 32u * n_tok)[(sub * 2u + (in >> 2)) * n_tok + tok] = sum;
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-    if (in == 0) {
-        sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
-        const __half h = __float2half_rn(sum);
-        const __half l = __float2half_rn(sum - __half2float(h));
-        uint8_t* sd = sums + tok * 32u + sub * 2u;
-        *reinterpret_cast<__half*>(sd) = h;
-        *reinterpret_cast<__half*>(sd + 16) = l;
+    float* sx16 = reinterpret_cast<float*>(sums + 32u * n_tok);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float4 u = v[h];
+        u.x *= s; u.y *= s; u.z *= s; u.w *= s;
+        uint2 hi, lo;
+        split4(u, hi, lo);
+        const uint32_t qd = 32u * h + lane, sub = qd >> 3, in = qd & 7u;  // 8 quads per 32-element sub-block
+        uint8_t* dst = base + sub * sub_stride + tok * 128u + in * 8u;
+        *reinterpret_cast<uint2*>(dst) = hi;
+        *reinterpret_cast<uint2*>(dst + 64) = lo;
+        float sum = (u.x + u.y) + (u.z + u.w);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if ((in & 3u) == 0) sx16[(sub * 2u + (in >> 2)) * n_tok + tok] = sum;
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+        if (in == 0) {
+            sum *= 0.03125f;  // keeps the fp16 copy in range: |sum| <= 32 * 2^14
+            const __half hh = __float2half_rn(sum);
+            const __half ll = __float2half_rn(sum - __half2float(hh));
+            uint8_t* sd = sums + tok * 32u + sub * 2u;
+            *reinterpret_cast<__half*>(sd) = hh;
+            *reinterpret_cast<__half*>(sd + 16) = ll;
+        }
+    }
+    if (lane == 0) (sx16 + 16u * n_tok)[tok] = inv;
+}
+
+/// Converts super-blocks [0, n_sb) of one x row into records starting at `area`: warp w of `n_warps` takes super-blocks
+/// w, w + n_warps, ..., four at a time so that their loads overlap.  The arithmetic does not depend on who calls it.
+__device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t warp,
+                                              uint32_t n_warps, uint32_t lane) {
+    constexpr uint32_t kAhead = 4;
+    const float4* xr = reinterpret_cast<const float4*>(xrow);
+    for (uint32_t sb0 = warp; sb0 < n_sb; sb0 += kAhead * n_warps) {
+        float4 v[kAhead][2];
+#pragma unroll
+        for (uint32_t j = 0; j < kAhead; ++j) {
+            const uint32_t sb = sb0 + j * n_warps;
+            if (sb < n_sb) v[j][0] = xr[sb * 64u + lane], v[j][1] = xr[sb * 64u + 32u + lane];
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kAhead; ++j) {
+            const uint32_t sb = sb0 + j * n_warps;
+            if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane);
+        }
     }
 }
 
-/// Converts super-blocks [0, n_sb) of one x row into records starting at `area`.  Called by every thread of a block
-/// (`nthreads` a multiple of 32); the arithmetic does not depend on who calls it.
-__device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, float s, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t tid,
-                                              uint32_t nthreads) {
-    const float4* xr = reinterpret_cast<const float4*>(xrow);
-    for (uint32_t qd = tid; qd < n_sb * 64u; qd += nthreads) stage_quad(area, xr[qd], s, qd, n_tok, tok);
-}
+/// Bytes of global scratch stage_x_rec_kernel fills: the records of all super-blocks.
+inline uint64_t stage_rec_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * xrec_bytes(n_tok); }
 
-/// Bytes of global scratch stage_x_rec_kernel fills: the records of all super-blocks, then 16 reciprocal scales.
-inline uint64_t stage_rec_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * xrec_bytes(n_tok) + 64; }
-
-/// One block per x row: the row's power-of-two scale, then its records.  Rows of up to kKeep quads per thread are read
-/// once and converted from registers; longer ones are read again after the scale is known.
+/// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block; nothing is shared between warps.
 static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
                                                                  uint32_t nb, uint32_t n_tok) {
-    __shared__ float red[16];
-    __shared__ float sc[2];
-    constexpr uint32_t kKeep = 10, kThreads = 512;
     // Programmatic dependent launch on both sides: the matmul behind this kernel may start filling its weight ring
     // now; x and the scratch records belong to the kernels before this one until they have completed.
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-    const float4* xr = reinterpret_cast<const float4*>(xrow);
-    const uint32_t n_quads = nb * 64u;
-    const bool keep = n_quads <= kKeep * kThreads;
-    float4 v[kKeep];
-    float m = 0.0f;
-    if (keep) {
-#pragma unroll
-        for (uint32_t i = 0; i < kKeep; ++i) {
-            const uint32_t qd = tid + i * kThreads;
-            v[i] = qd < n_quads ? xr[qd] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            m = fmaxf(fmaxf(m, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
-        }
-    } else {
-        for (uint32_t i = tid; i < n_quads; i += kThreads) {
-            const float4 u = xr[i];
-            m = fmaxf(fmaxf(m, fmaxf(fabsf(u.x), fabsf(u.y))), fmaxf(fabsf(u.z), fabsf(u.w)));
-        }
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    if (tid == 0) {
-        float a = 0.0f;
-        for (int i = 0; i < 16; ++i) a = fmaxf(a, red[i]);
-        row_scale(a, sc[0], sc[1]);
-    }
-    __syncthreads();
-    if (keep) {
-#pragma unroll
-        for (uint32_t i = 0; i < kKeep; ++i) {
-            const uint32_t qd = tid + i * kThreads;  // whole warps are inside or outside the row: n_quads is a multiple of 64
-            if (qd < n_quads) stage_quad(scratch, v[i], sc[0], qd, n_tok, tk);
-        }
-    } else {
-        stage_row_rec(scratch, xrow, sc[0], nb, n_tok, tk, tid, kThreads);
-    }
-    if (tid == 0) reinterpret_cast<float*>(scratch + uint64_t{nb} * xrec_bytes(n_tok))[tk] = sc[1];
+    const uint32_t tk = blockIdx.x, sb = blockIdx.y * 16u + (threadIdx.x >> 5);
+    if (sb >= nb) return;
+    const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    const uint32_t lane = threadIdx.x & 31u;
+    const float4 v[2] = {xr[sb * 64u + lane], xr[sb * 64u + 32u + lane]};
+    stage_superblock(scratch, v, sb, n_tok, tk, lane);
 }
 
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows ----------------------------------------------------
@@ -141,7 +134,7 @@ static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __
 // sub-block s gets a fresh fp32 accumulator S_s (two MMAs), and the 6-bit scales enter in fp32:
 //     a_p = fma(w_{4+p}, S_{4+p}, w_p * S_p)   p = 0..3      (w_s = sc_s, or sc_s / 16 for the high-nibble sub-blocks)
 //     T   = (a_0 + a_1) + (a_2 + a_3)
-//     y  += (d * 2^24) * T  -  (dmin * 2^24 * 32) * M
+//     y  += (d * 2^24 / s) * T  -  (dmin * 2^24 * 32 / s) * M      s = the scale of this super-block of x
 // where M, the min term sum_s m_s * (sum of x over sub-block s) / 32, comes from one extra MMA whose A holds the 6-bit min
 // codes and whose B holds the sub-block sums of x.  That operation order is the same for every batch size; a call
 // with ONE x row gets it with a quarter of the scale work by placing x in the column pair (2p, 2p + 1) of B for the
@@ -190,6 +183,7 @@ struct Q4Kf {
                 aHi[r][0] = qa & 0x00F000F0u, aHi[r][1] = qa8 & 0x00F000F0u, aHi[r][2] = qb & 0x00F000F0u, aHi[r][3] = qb8 & 0x00F000F0u;
             }
         };
+        const float* invp = reinterpret_cast<const float*>(rec + XRec<NTOK>::kOffInv);
         float T[G][2];  // the item's scaled sums per column group: rows g, g + 8
         if constexpr (NTOK == 1) {
             // B base per sub-block phase p: the lane whose column pair is p reads x (hi for even g, lo for odd g), the others zeros
@@ -266,10 +260,11 @@ struct Q4Kf {
             const uint32_t bs = *reinterpret_cast<const uint32_t*>(rec + xl.sums[gi]);
             float cm[4];
             mma16816_first(cm, mpair[0], mpair[1], 0u, 0u, bs, 0u);
-            yacc[gi][0] = fmaf(dq[0], T[gi][0], yacc[gi][0]);
-            yacc[gi][0] = fmaf(-dmn[0], cm[0] + cm[1], yacc[gi][0]);
-            yacc[gi][1] = fmaf(dq[1], T[gi][1], yacc[gi][1]);
-            yacc[gi][1] = fmaf(-dmn[1], cm[2] + cm[3], yacc[gi][1]);
+            const float inv = invp[xl.tok[gi]];  // 1 / s of this super-block of the column group's x row: a power of two
+            yacc[gi][0] = fmaf(dq[0] * inv, T[gi][0], yacc[gi][0]);
+            yacc[gi][0] = fmaf(-dmn[0] * inv, cm[0] + cm[1], yacc[gi][0]);
+            yacc[gi][1] = fmaf(dq[1] * inv, T[gi][1], yacc[gi][1]);
+            yacc[gi][1] = fmaf(-dmn[1] * inv, cm[2] + cm[3], yacc[gi][1]);
         }
     }
 };
@@ -278,7 +273,7 @@ struct Q4Kf {
 // Every scale group sg (a 32-element block, or 16 elements of Q6_K) gets a fresh fp32 accumulator S_sg; the group's
 // scale and zero point are applied in fp32, in this order for every batch size:
 //     P_p = sum over the groups sg = p (mod 4), ascending, of m_sg * (S_sg - zero * 2^-24 * sum_sg(x))     (an fma chain)
-//     y  += (P_0 + P_1) + (P_2 + P_3)                               m_sg = scale_sg * 2^24
+//     y  += ((P_0 + P_1) + (P_2 + P_3)) / s                         m_sg = scale_sg * 2^24, s = the scale of this super-block of x
 // A call with ONE x row places x in the column pair (2p, 2p + 1) of B for the groups sg = p (mod 4) (the other columns
 // read zeros), so one accumulator tile carries four groups and lane t of a row owns P_t; two shuffles build the sum.
 template <class T>
@@ -332,16 +327,17 @@ struct GroupedItem {
                 float sx;
                 if constexpr (kSteps == 2) sx = sx16[2 * (4 * q + t)] + sx16[2 * (4 * q + t) + 1];
                 else sx = sx16[4 * q + t];
-                const float z = sx * kZ;
-                if (q == 0) P0 = m0 * ((c[0] + c[1]) + z), P1 = m1 * ((c[2] + c[3]) + z);
+                const float z = __fmul_rn(sx, kZ);
+                if (q == 0) P0 = __fmul_rn(m0, (c[0] + c[1]) + z), P1 = __fmul_rn(m1, (c[2] + c[3]) + z);
                 else P0 = fmaf(m0, (c[0] + c[1]) + z, P0), P1 = fmaf(m1, (c[2] + c[3]) + z, P1);
             }
             P0 += __shfl_xor_sync(0xFFFFFFFFu, P0, 1);
             P1 += __shfl_xor_sync(0xFFFFFFFFu, P1, 1);
             P0 += __shfl_xor_sync(0xFFFFFFFFu, P0, 2);
             P1 += __shfl_xor_sync(0xFFFFFFFFu, P1, 2);
-            yacc[0][0] += P0;
-            yacc[0][1] += P1;
+            const float inv = reinterpret_cast<const float*>(rec + XRec<NTOK>::kOffInv)[0];  // 1 / s of this super-block of x
+            yacc[0][0] = fmaf(inv, P0, yacc[0][0]);
+            yacc[0][1] = fmaf(inv, P1, yacc[0][1]);
         } else {
             float P[G][2][4];
 #pragma unroll
@@ -365,10 +361,10 @@ struct GroupedItem {
                     float sx;
                     if constexpr (kSteps == 2) sx = sx16[(2 * sg) * NTOK + xl.tok[gi]] + sx16[(2 * sg + 1) * NTOK + xl.tok[gi]];
                     else sx = sx16[sg * NTOK + xl.tok[gi]];
-                    const float z = sx * kZ;
+                    const float z = __fmul_rn(sx, kZ);
                     if (sg < 4) {
-                        P[gi][0][sg & 3] = m0 * ((c[gi][0] + c[gi][1]) + z);
-                        P[gi][1][sg & 3] = m1 * ((c[gi][2] + c[gi][3]) + z);
+                        P[gi][0][sg & 3] = __fmul_rn(m0, (c[gi][0] + c[gi][1]) + z);
+                        P[gi][1][sg & 3] = __fmul_rn(m1, (c[gi][2] + c[gi][3]) + z);
                     } else {
                         P[gi][0][sg & 3] = fmaf(m0, (c[gi][0] + c[gi][1]) + z, P[gi][0][sg & 3]);
                         P[gi][1][sg & 3] = fmaf(m1, (c[gi][2] + c[gi][3]) + z, P[gi][1][sg & 3]);
@@ -377,8 +373,9 @@ struct GroupedItem {
             }
 #pragma unroll
             for (int gi = 0; gi < G; ++gi) {
-                yacc[gi][0] += (P[gi][0][0] + P[gi][0][1]) + (P[gi][0][2] + P[gi][0][3]);
-                yacc[gi][1] += (P[gi][1][0] + P[gi][1][1]) + (P[gi][1][2] + P[gi][1][3]);
+                const float inv = reinterpret_cast<const float*>(rec + XRec<NTOK>::kOffInv)[xl.tok[gi]];
+                yacc[gi][0] = fmaf(inv, (P[gi][0][0] + P[gi][0][1]) + (P[gi][0][2] + P[gi][0][3]), yacc[gi][0]);
+                yacc[gi][1] = fmaf(inv, (P[gi][1][0] + P[gi][1][1]) + (P[gi][1][2] + P[gi][1][3]), yacc[gi][1]);
             }
         }
     }
