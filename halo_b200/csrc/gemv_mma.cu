@@ -1,4 +1,6 @@
-// gemv_mma_f16x2: tensor-core skinny kernel for decode-shaped Q4_K calls (M = 1 ... 16 and beyond in token tiles).
+// The statically partitioned tensor-core skinny kernels for Q4_K: what gemv_mma_f16x2 runs under
+// HALO_CUDA_GEMV_FLAG_NO_SCRATCH (no context scratch: each CTA owns 128 W rows and converts x itself), and the
+// single-row specialist gemv_mma_m1.  Every other call of gemv_mma_f16x2 takes the balanced kernels of gemv_mma_sk.cuh.
 //
 // Why tensor cores for a matrix-vector product: at 0.5625 bytes per weight the B200 streams ~11.6 T weights/s from
 // HBM while the CUDA cores issue ~36 T lane-instructions/s, so a kernel may spend about three instructions per
@@ -43,13 +45,13 @@ using namespace mma;
 // NTOK: x rows of this launch (1..16), i.e. 2 * NTOK B columns in G = ceil(NTOK / 4) MMA column groups.
 // KS: warps sharing one 16-row block; warp ks takes the super-blocks sb = ks (mod KS), a split that depends on
 // nothing but KS, and the KS partial sums are added in ks order.  NS: ring stages per warp.
-// PRE: x was converted once by stage_x_kernel into `xstage`; the CTA fetches each K chunk by bulk copy.  Otherwise the CTA
-// converts its chunks itself (no scratch memory; the path of single-row calls).  Both give the same bits.
-template <int NTOK, int KS, int NS, bool PRE>
+// The CTA converts its chunks of x itself: the kernel needs no scratch memory (the balanced kernels of gemv_mma_sk.cuh
+// serve every call that may use context scratch).
+template <int NTOK, int KS, int NS>
 __global__ void __launch_bounds__(kRowBlocks * KS * 32, kRowBlocks >= 8 ? 1 : 2)
 gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __restrict__ x, uint64_t x_stride,
                     float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t chunk_sb,
-                    uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage) {
+                    uint32_t* __restrict__ error_word) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     constexpr int G = (NTOK + 3) / 4;
@@ -98,33 +100,23 @@ gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __res
     float* s_scale = reinterpret_cast<float*>(smem + kOffScale);
     float* s_inv = reinterpret_cast<float*>(smem + kOffInv);
     float* s_red = reinterpret_cast<float*>(smem + kOffRed);  // kWarps partial maxima
-    const uint32_t xbar = smem_base + kOffXBar;
-    if constexpr (PRE) {
-        if (tid == 0) {
-            mbar_init(xbar, 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (uint32_t tk = 0; tk < NTOK; ++tk) {
+        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+        float m = 0.0f;
+        for (uint32_t i = tid; i < cols / 4; i += kThreads) {
+            const float4 v = xr[i];
+            m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
-        if (tid < NTOK) s_inv[tid] = reinterpret_cast<const float*>(xstage + uint64_t{nb} * (8u * kSubStride + kSbStride))[tid];
-        __syncthreads();
-    } else {
-        for (uint32_t tk = 0; tk < NTOK; ++tk) {
-            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-            float m = 0.0f;
-            for (uint32_t i = tid; i < cols / 4; i += kThreads) {
-                const float4 v = xr[i];
-                m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-            }
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-            if (lane == 0) s_red[warp] = m;
-            __syncthreads();
-            if (tid == 0) {
-                float a = 0.0f;
-                for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
-                row_scale(a, s_scale[tk], s_inv[tk]);
-            }
-            __syncthreads();
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+        if (lane == 0) s_red[warp] = m;
+        __syncthreads();
+        if (tid == 0) {
+            float a = 0.0f;
+            for (uint32_t i = 0; i < kWarps; ++i) a = fmaxf(a, s_red[i]);
+            row_scale(a, s_scale[tk], s_inv[tk]);
         }
+        __syncthreads();
     }
 
     // ---- B fragment pointers.  MMA columns are independent, so a lane whose column carries no token simply reads
@@ -153,25 +145,11 @@ gemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap wmap, const float* __res
     for (uint32_t c0 = 0; c0 < nb; c0 += chunk_sb) {
         const uint32_t n_sb = min(chunk_sb, nb - c0);
         if (c0 != 0) __syncthreads();  // everyone is done reading the previous chunk
-        // ---- x[:, chunk] as fp16 hi / lo in slot order, and the sub-block sums: fetched, or converted here -------------------------
-        if constexpr (PRE) {
-            if (tid == 0) {
-                const uint32_t xs_bytes = n_sb * 8u * kSubStride, sx_bytes = n_sb * kSbStride;
-                mbar_expect_tx(xbar, xs_bytes + sx_bytes);
-                bulk_g2s(smem_base + kOffData, xstage + uint64_t{c0} * 8u * kSubStride, xs_bytes, xbar);
-                bulk_g2s(smem_base + kOffData + chunk_sb * 8u * kSubStride, xstage + uint64_t{nb} * 8u * kSubStride + uint64_t{c0} * kSbStride,
-                         sx_bytes, xbar);
-            }
-            if (!mbar_wait(xbar, (c0 / chunk_sb) & 1u)) {
-                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
-                lost = true;
-            }
-        } else {
-            for (uint32_t tk = 0; tk < NTOK; ++tk)
-                stage_row(smem + kOffData, smem + kOffData + chunk_sb * 8u * kSubStride,
-                          reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), s_scale[tk], c0, n_sb,
-                          kSubStride, kSbStride, 2 * tk * 64u, tid, kThreads);
-        }
+        // ---- x[:, chunk] as fp16 hi / lo in slot order, and the sub-block sums ------------------------------------------------
+        for (uint32_t tk = 0; tk < NTOK; ++tk)
+            stage_row(smem + kOffData, smem + kOffData + chunk_sb * 8u * kSubStride,
+                      reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), s_scale[tk], c0, n_sb,
+                      kSubStride, kSbStride, 2 * tk * 64u, tid, kThreads);
         __syncthreads();
         if (!active || lost) continue;
 
@@ -586,16 +564,14 @@ int weight_map(const GemvCall& c, CUtensorMap* out) {
     return 0;
 }
 
-constexpr uint32_t kInternalNoScratch = HALO_CUDA_GEMV_FLAG_NO_SCRATCH;
-
-template <int NTOK, int KS, int NS, bool PRE>
+template <int NTOK, int KS, int NS>
 int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s) {
     constexpr int G = (NTOK + 3) / 4;
     const uint32_t nb = c.cols / 256u;
     const Plan p = plan_for(nb, NTOK, kOffRing + kRowBlocks * KS * NS * kSlotBytes, (KS - 1) * kRowBlocks * 32 * 2 * G * 4);
     static bool attr_set = false;
     if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_kernel<NTOK, KS, NS, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_kernel<NTOK, KS, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kSmemBudget)));
         attr_set = true;
     }
@@ -604,19 +580,10 @@ int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s)
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
     CUtensorMap wmap;
     if (int rc = weight_map(c, &wmap)) return rc;
-    const uint8_t* xstage = nullptr;
-    if constexpr (PRE) {
-        void* ws = nullptr;
-        const uint64_t bytes = stage_scratch_bytes(nb, NTOK);
-        if (int rc = workspace(ctx, 0, bytes, s, &ws)) return rc;
-        stage_x_kernel<<<NTOK, 512, 0, s>>>(x, c.x_stride, static_cast<uint8_t*>(ws), nb, NTOK);
-        HC_CUDA(cudaGetLastError());
-        xstage = static_cast<const uint8_t*>(ws);
-    }
     cudaLaunchAttribute attr[1];
     const cudaLaunchConfig_t cfg = pdl_config(grid, kRowBlocks * KS * 32, p.smem_bytes, s, attr);
-    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<NTOK, KS, NS, PRE>, wmap, x, c.x_stride, y, c.y_stride, c.rows, nb, p.chunk_sb,
-                               ctx->error_word_dev, xstage));
+    HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<NTOK, KS, NS>, wmap, x, c.x_stride, y, c.y_stride, c.rows, nb, p.chunk_sb,
+                               ctx->error_word_dev));
     return 0;
 }
 
@@ -632,9 +599,7 @@ int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, uint32_t n
 #define HALO_MMA_NS 3
 #endif
         if (n == NTOK) {
-            // batches convert x once into context scratch; single rows (and callers that forbid scratch) convert in the CTA
-            if (NTOK >= 2 && (c.flags & kInternalNoScratch) == 0) return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS, true>(ctx, c, tok0, s);
-            return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS, false>(ctx, c, tok0, s);
+            return launch_n<NTOK, HALO_MMA_KS, HALO_MMA_NS>(ctx, c, tok0, s);
         }
         return launch_tokens<NTOK + 1>(ctx, c, tok0, n, s);
     }

@@ -117,45 +117,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  : "memory");
 }
 
-/// Pre-staging kernel for batches: one CTA per x row converts the whole row once into global scratch laid out exactly
-/// like the in-kernel staging area ([sub-block][column][64 B], then [super-block][column][16 B], then 1/s per row, then
-/// the fp32 sums per 16 elements), so
-/// that the matmul CTAs fetch their K chunks with bulk copies instead of each converting x again.
-/// Bytes of global scratch stage_x_kernel fills for `n_tok` rows of nb super-blocks.
-inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) {
-    return uint64_t{nb} * (8u * 2 * n_tok * 64u + 2 * n_tok * 16u) + 64 + uint64_t{nb} * 16u * n_tok * 4u;
-}
-
-static __global__ void __launch_bounds__(512) stage_x_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
-                                                      uint32_t nb, uint32_t n_tok) {
-    __shared__ float red[16];
-    __shared__ float sc[2];
-    const uint32_t tk = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t cols = nb * 256u, kcols = 2 * n_tok;
-    const float* xrow = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-    float m = 0.0f;
-    for (uint32_t i = tid; i < cols / 4; i += 512) {
-        const float4 v = reinterpret_cast<const float4*>(xrow)[i];
-        m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    if (tid == 0) {
-        float a = 0.0f;
-        for (int i = 0; i < 16; ++i) a = fmaxf(a, red[i]);
-        row_scale(a, sc[0], sc[1]);
-    }
-    __syncthreads();
-    uint8_t* xs = scratch;
-    uint8_t* sx = scratch + uint64_t{nb} * 8u * kcols * 64u;
-    float* inv = reinterpret_cast<float*>(sx + uint64_t{nb} * kcols * 16u);
-    float* sx16 = inv + 16;  // after the 16 reciprocal scales: [16-element group][token]
-    stage_row(xs, sx, xrow, sc[0], 0, nb, kcols * 64u, kcols * 16u, 2 * tk * 64u, tid, 512, sx16, n_tok, tk);
-    if (tid == 0) inv[tk] = sc[1];
-}
-
 // ---- shared-memory weight ring -------------------------------------------------------------------------------------
 // Each warp streams its own rows: per pipeline stage one TMA tile copy (cp.async.bulk.tensor.2d over a tensor map of
 // the weight matrix as rows of bytes) brings the 144-byte super-block of its 16 W rows into a 16 x 160-byte slot and
