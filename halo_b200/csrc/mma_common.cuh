@@ -254,13 +254,14 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
         float2* mine = record(cta);
 #pragma unroll
         for (int gi = 0; gi < G; ++gi) __stcg(mine + gi, make_float2(acc[gi][0], acc[gi][1]));
-        __threadfence();
+        // release this warp's record and acquire the others' in one atomic: the barrier before it makes the other lanes'
+        // stores part of what lane 0 releases, the one after it orders their loads behind what lane 0 acquired
         __syncwarp();
         uint32_t old = 0;
-        if (lane == 0) old = atomicAdd(counters + rb, 1u);
+        if (lane == 0) asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(counters + rb) : "memory");
         old = __shfl_sync(0xFFFFFFFFu, old, 0);
         if (old != c_hi - c_lo) return;  // another CTA will finish this block
-        __threadfence();
+        __syncwarp();
         // the partials are added in CTA order; they are fetched kBatch contributors at a time so that the loads overlap
         constexpr uint32_t kBatch = G <= 1 ? 8 : G == 2 ? 4 : 2;
         for (uint32_t c0 = c_lo; c0 <= c_hi; c0 += kBatch) {
