@@ -62,9 +62,10 @@ inline int launch_stage(const float* x, uint64_t x_stride, uint8_t* scratch, uin
 }
 
 /// The kernel-side view of a call's peer description (none: world = 0).
-inline PeerPush peer_push(const GemvCall& c) {
+inline PeerPush peer_push(const GemvCall& c, uint32_t tok0) {
     PeerPush pp{};
     if (c.peer == nullptr) return pp;
+    pp.tok0 = tok0;
     pp.world = c.peer->world, pp.rank = c.peer->rank, pp.capacity = c.peer->capacity;
     for (uint32_t i = 0; i < c.peer->world && i < kMaxPeers; ++i) pp.slots[i] = static_cast<unsigned long long*>(c.peer->slots[i]);
     pp.epoch = c.peer->epoch;
@@ -117,7 +118,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         cudaLaunchAttribute attr[1];
         const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
         HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb,
-                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, peer_push(c)));
+                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, peer_push(c, tok0)));
         return 0;
     }
 }
@@ -147,7 +148,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
     HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_streamed_kernel<F, NTOK, NS, KS>, wmap, g.table, y, c.y_stride, c.rows, g.nb, xs_cols,
                                static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev,
-                               static_cast<const uint8_t*>(ws), peer_push(c)));
+                               static_cast<const uint8_t*>(ws), peer_push(c, tok0)));
     return 0;
 }
 

@@ -221,7 +221,8 @@ inline uint32_t plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool al
 /// the reductions this rank has finished (the sender tags with *epoch + 1).
 constexpr uint32_t kMaxPeers = 8;
 struct PeerPush {
-    uint32_t world, rank, capacity, reserved;
+    uint32_t world, rank, capacity;
+    uint32_t tok0;  // first x row of this launch within the call (calls of more than 16 rows run in tiles)
     unsigned long long* slots[kMaxPeers];
     const uint32_t* epoch;
 };
@@ -295,7 +296,7 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
             const uint32_t tk = 4u * gi + t;
             if (tk < NTOK) {
                 const uint32_t n0 = rb * 16u + g, n1 = n0 + 8u;
-                const uint64_t at = slot + uint64_t{tk} * rows;  // the pushed rows are dense: [x row][W row]
+                const uint64_t at = slot + uint64_t{peer.tok0 + tk} * rows;  // the pushed rows are dense: [x row][W row]
                 const unsigned long long w0 = peer_word(sum[gi][0], next), w1 = peer_word(sum[gi][1], next);
                 for (uint32_t p = 0; p < peer.world; ++p) {
                     if (n0 < rows) peer.slots[p][at + n0] = w0;

@@ -38,7 +38,7 @@ for wtype, rows, cols, m in [(synth.Q4_K, 1024, 5120, 1), (synth.Q6_K, 512, 4352
     assert torch.equal(ref.view(torch.int32), yr.view(torch.int32)), "every rank must hold the same reduced y"
 # the same row splits with the peer-memory epilogue: the matmul kernel pushes its rows to the peers, a small kernel adds them
 rt.enable_peer_reduce(16 * 1024)
-for wtype, rows, cols, m in [(synth.Q4_K, 1024, 5120, 1), (synth.Q6_K, 512, 4352, 4), (synth.Q4_K, 640, 6144, 3), (synth.Q4_K, 37, 1024, 16)]:
+for wtype, rows, cols, m in [(synth.Q4_K, 1024, 5120, 1), (synth.Q6_K, 512, 4352, 4), (synth.Q4_K, 640, 6144, 3), (synth.Q4_K, 37, 1024, 16), (synth.Q4_K, 200, 2048, 21)]:
     w = synth.quant_weights(wtype, rows, cols, 33, 1)
     x = torch.from_numpy(synth.activations(m, cols, 33, 2)).cuda()
     full = one.load(wtype, w, rows, cols, "column")(x)
