@@ -470,6 +470,9 @@ int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t
     if (variant_id == 0 || variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
         return fail(HALO_CUDA_E_CONFIG, "plan: unknown kernel variant id %u", variant_id);
     if (n_vec_lo > n_vec_hi) return fail(HALO_CUDA_E_API, "plan: empty n_vec range");
+    if (variant_id == HALO_CUDA_GEMV_MMA_R)
+        return fail(HALO_CUDA_E_CONFIG, "plan: gemv_mma_r reads another weight layout: the loader that repacks a tensor passes variant id %u with it",
+                    variant_id);
     for (PlanEntry& p : ctx->plan) {
         if (p.wtype == wtype && p.rows == rows && p.cols == cols && p.n_vec_lo == n_vec_lo && p.n_vec_hi == n_vec_hi) {
             p.variant_id = variant_id;

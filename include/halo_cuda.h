@@ -174,7 +174,8 @@ int halo_cuda_variants(uint32_t op, HaloCudaVariant* out, uint32_t cap, uint32_t
 /* The variant id 0 resolves to for this call (what the shape heuristic, or an installed plan, picks). */
 int halo_cuda_gemv_resolve(HaloCudaCtx* ctx, const HaloCudaGemv* args, uint32_t* variant_id);
 /* Installs the autotuner's choice for one shape bucket: calls with variant_id 0, this wtype, rows, cols and
- * n_vec in [n_vec_lo, n_vec_hi] run `variant_id` (the "KernelPlan" join of ADR-001 5.6). */
+ * n_vec in [n_vec_lo, n_vec_hi] run `variant_id` (the "KernelPlan" join of ADR-001 5.6).  Variant 7 is refused (E_CONFIG): it
+ * reads another weight layout, so it travels with the tensor a loader has repacked, not with a shape. */
 int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec_lo, uint32_t n_vec_hi,
                        uint32_t variant_id);
 int halo_cuda_plan_clear(HaloCudaCtx* ctx);

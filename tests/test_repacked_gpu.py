@@ -118,3 +118,25 @@ def test_repacked_kernel_rows_do_not_depend_on_batch_size(be, t):
     for m in (1, 3, 4, 7, 16):
         ym, _ = run(be, st, t, w, x[:m], n, k)
         assert np.array_equal(bits(ym), bits(y20[:m])), f"batch of {m}"
+
+
+def test_lm_head_over_repacked_rows_and_plan_refusal(be):
+    t, n, k, m = synth.Q4_0, 9000, 512, 3   # more than one 8192-row argmax chunk
+    w = synth.quant_weights(t, n, k, 8, 1)
+    x = synth.activations(m, k, 8, 2)
+    st = be.create_stream()
+    y, _ = run(be, st, t, w, x, n, k)
+    raw = be.import_host_readonly(w.reshape(-1))
+    pk = be.repack(st, t, hb.TensorRef.of(raw), n, k)
+    xb = be.import_host_readonly(x)
+    lb, rb, ib = be.allocate(m * n * 4), be.allocate(m * 12), be.allocate(m * 4)
+    g = hb.GemvArgs(t, hb.TensorRef.of(pk), hb.TensorRef.of(xb), hb.TensorRef.of(lb), n, k, m, capi.GEMV_MMA_R)
+    be.lm_head(st, hb.LmHeadArgs(g, hb.TensorRef.of(rb), 0, hb.TensorRef.of(ib)))
+    logits, ids = np.empty((m, n), np.float32), np.empty(m, np.int32)
+    be.download(st, hb.TensorRef.of(lb), logits)
+    be.download(st, hb.TensorRef.of(ib), ids)
+    st.wait()
+    assert np.array_equal(bits(logits), bits(y)), "the head runs the same matmul"
+    assert np.array_equal(ids, np.argmax(y, axis=1))
+    with pytest.raises(hb.HaloError):   # the repacked variant belongs to a tensor, not to a shape bucket
+        be.plan_set(t, n, k, 1, 4, capi.GEMV_MMA_R)
