@@ -164,7 +164,7 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
         // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
         for (uint32_t tk = 0; tk < NTOK; ++tk)
             stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), nb, NTOK, tk,
-                          warp, kWarps, lane);
+                          warp, kWarps, lane, F::kXLaneBytes == 8);
         __syncthreads();
     }
 

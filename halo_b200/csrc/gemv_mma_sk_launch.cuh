@@ -53,11 +53,11 @@ inline cudaLaunchConfig_t pdl_config(uint32_t grid, uint32_t smem, cudaStream_t 
 }
 
 /// The x conversion of a batched call: one warp per super-block, launched so that it overlaps the tail of the kernel before it.
-inline int launch_stage(const float* x, uint64_t x_stride, uint8_t* scratch, uint32_t nb, uint32_t n_tok, cudaStream_t s) {
+inline int launch_stage(const float* x, uint64_t x_stride, uint8_t* scratch, uint32_t nb, uint32_t n_tok, bool split_halves, cudaStream_t s) {
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(n_tok, 0, s, attr);
     cfg.gridDim = dim3(n_tok, (nb + 15u) / 16u);
-    HC_CUDA(cudaLaunchKernelEx(&cfg, stage_x_rec_kernel, x, x_stride, scratch, nb, n_tok));
+    HC_CUDA(cudaLaunchKernelEx(&cfg, stage_x_rec_kernel, x, x_stride, scratch, nb, n_tok, split_halves ? 1u : 0u));
     return 0;
 }
 
@@ -112,7 +112,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         if constexpr (PRE) {
             void* ws = nullptr;
             if (int rc = workspace(ctx, 0, stage_rec_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
-            if (int rc = launch_stage(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK, s)) return rc;
+            if (int rc = launch_stage(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK, F::kXLaneBytes == 8, s)) return rc;
             xstage = static_cast<const uint8_t*>(ws);
         }
         cudaLaunchAttribute attr[1];
@@ -143,7 +143,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     if (int rc = weight_map<F>(c, &wmap)) return rc;
     void* ws = nullptr;
     if (int rc = workspace(ctx, 0, stage_rec_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
-    if (int rc = launch_stage(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK, s)) return rc;
+    if (int rc = launch_stage(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK, F::kXLaneBytes == 8, s)) return rc;
     cudaLaunchAttribute attr[1];
     const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
     HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_streamed_kernel<F, NTOK, NS, KS>, wmap, g.table, y, c.y_stride, c.rows, g.nb, xs_cols,

@@ -10,7 +10,10 @@
 // super-block's largest magnitude near 2^13, so the conversion needs no pass over the whole row and no block-wide
 // reduction, and an item folds 1 / s into its final multiply.
 // x record of one super-block for NTOK rows (what stage_superblock writes and an item reads):
-//   [sub-block 0..7][column 0..2*NTOK-1][64 B]   fp16 hi (even column) / lo (odd column) of x * s, in quads of 8 bytes
+//   [sub-block 0..7][column 0..2*NTOK-1][64 B]   fp16 hi (even column) / lo (odd column) of x * s, in quads of 8 bytes; for
+//                                                the formats that read 8 bytes per lane and k-step the two 16-element halves
+//                                                of a sub-block are kept apart instead: [half][column][32 B], so that the
+//                                                four columns a half warp reads together fall on different banks
 //   [column][16 B]                               sum of each 32-element sub-block / 32 as fp16 hi / lo (Q4_K min term)
 //   [16-element group 0..15][row] fp32           sums of x * s over 16 elements (zero points of the other formats)
 //   [row] fp32                                   1 / s (padded to 16 bytes)
@@ -42,7 +45,7 @@ __device__ __forceinline__ XLane<(NTOK + 3) / 4> make_xlane(uint32_t g, uint32_t
 #pragma unroll
     for (int gi = 0; gi < (NTOK + 3) / 4; ++gi) {
         const uint32_t col = min(8u * gi + g, XRec<NTOK>::kCols - 1);
-        xl.xs[gi] = col * 64u + t * LaneBytes;
+        xl.xs[gi] = LaneBytes == 8 ? col * 32u + t * 8u : col * 64u + t * 16u;
         xl.sums[gi] = XRec<NTOK>::kOffSums + col * 16u + t * 4u;
         xl.tok[gi] = min(4u * gi + t, static_cast<uint32_t>(NTOK - 1));
     }
@@ -51,7 +54,8 @@ __device__ __forceinline__ XLane<(NTOK + 3) / 4> make_xlane(uint32_t g, uint32_t
 
 /// One super-block (index sb) of an x row into its record at `area`, by one warp: lane l holds quads l and l + 32
 /// (elements 4l .. 4l + 3 and 128 + 4l .. ) in v; the scale comes from the largest magnitude among the 64 quads.
-__device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v)[2], uint32_t sb, uint32_t n_tok, uint32_t tok, uint32_t lane) {
+__device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v)[2], uint32_t sb, uint32_t n_tok, uint32_t tok, uint32_t lane,
+                                                 bool split_halves) {
     const uint32_t rec = xrec_bytes(n_tok), sub_stride = 128u * n_tok;
     float m = 0.0f;
 #pragma unroll
@@ -70,9 +74,15 @@ __device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v
         uint2 hi, lo;
         split4(u, hi, lo);
         const uint32_t qd = 32u * h + lane, sub = qd >> 3, in = qd & 7u;  // 8 quads per 32-element sub-block
-        uint8_t* dst = base + sub * sub_stride + tok * 128u + in * 8u;
-        *reinterpret_cast<uint2*>(dst) = hi;
-        *reinterpret_cast<uint2*>(dst + 64) = lo;
+        if (split_halves) {
+            uint8_t* dst = base + sub * sub_stride + (in >> 2) * (64u * n_tok) + tok * 64u + (in & 3u) * 8u;
+            *reinterpret_cast<uint2*>(dst) = hi;
+            *reinterpret_cast<uint2*>(dst + 32) = lo;
+        } else {
+            uint8_t* dst = base + sub * sub_stride + tok * 128u + in * 8u;
+            *reinterpret_cast<uint2*>(dst) = hi;
+            *reinterpret_cast<uint2*>(dst + 64) = lo;
+        }
         float sum = (u.x + u.y) + (u.z + u.w);
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
@@ -93,7 +103,7 @@ __device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v
 /// Converts super-blocks [0, n_sb) of one x row into records starting at `area`: warp w of `n_warps` takes super-blocks
 /// w, w + n_warps, ..., four at a time so that their loads overlap.  The arithmetic does not depend on who calls it.
 __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t warp,
-                                              uint32_t n_warps, uint32_t lane) {
+                                              uint32_t n_warps, uint32_t lane, bool split_halves) {
     constexpr uint32_t kAhead = 4;
     const float4* xr = reinterpret_cast<const float4*>(xrow);
     for (uint32_t sb0 = warp; sb0 < n_sb; sb0 += kAhead * n_warps) {
@@ -106,7 +116,7 @@ __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, 
 #pragma unroll
         for (uint32_t j = 0; j < kAhead; ++j) {
             const uint32_t sb = sb0 + j * n_warps;
-            if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane);
+            if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane, split_halves);
         }
     }
 }
@@ -116,7 +126,7 @@ inline uint64_t stage_rec_scratch_bytes(uint32_t nb, uint32_t n_tok) { return ui
 
 /// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block; nothing is shared between warps.
 static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch,
-                                                                 uint32_t nb, uint32_t n_tok) {
+                                                                 uint32_t nb, uint32_t n_tok, uint32_t split_halves) {
     // Programmatic dependent launch on both sides: the matmul behind this kernel may start filling its weight ring
     // now; x and the scratch records belong to the kernels before this one until they have completed.
     asm volatile("griddepcontrol.launch_dependents;");
@@ -126,7 +136,7 @@ static __global__ void __launch_bounds__(512) stage_x_rec_kernel(const float* __
     const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
     const uint32_t lane = threadIdx.x & 31u;
     const float4 v[2] = {xr[sb * 64u + lane], xr[sb * 64u + 32u + lane]};
-    stage_superblock(scratch, v, sb, n_tok, tk, lane);
+    stage_superblock(scratch, v, sb, n_tok, tk, lane, split_halves != 0);
 }
 
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows ----------------------------------------------------
@@ -287,6 +297,7 @@ struct GroupedItem {
         constexpr uint32_t kSubStride = XRec<NTOK>::kSubStride;
         constexpr int kGroups = static_cast<int>(T::kScaleGroups), kSteps = static_cast<int>(T::kStepsPerGroup);
         constexpr float kZ = -T::kZero / 16777216.0f;
+        constexpr uint32_t kHalfStride = XRec<NTOK>::kCols * 32u;  // the two 16-element halves of a sub-block are [half][column][32 B]
         const uint8_t* r1 = r0 + 8 * T::kPitch;
         typename T::Frag f0, f1;
         T::load(f0, r0, t);
@@ -300,7 +311,7 @@ struct GroupedItem {
         auto sub_of = [](int sg, int s) { return kSteps == 2 ? sg : sg >> 1; };
         auto lh_of = [](int sg, int s) { return kSteps == 2 ? s : sg & 1; };
         if constexpr (NTOK == 1) {
-            const uint8_t* real = rec + (xl.g & 1u) * 64u + t * 8u;
+            const uint8_t* real = rec + (xl.g & 1u) * 32u + t * 8u;
             const uint8_t* zb = zeros + t * 8u;
             const uint8_t* bp[4];
 #pragma unroll
@@ -317,7 +328,7 @@ struct GroupedItem {
                         uint32_t a0, a1, a2, a3;
                         T::pairs(f0, sg, s, a0, a2);
                         T::pairs(f1, sg, s, a1, a3);
-                        const uint2 b = *reinterpret_cast<const uint2*>(bp[p] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * 32);
+                        const uint2 b = *reinterpret_cast<const uint2*>(bp[p] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * kHalfStride);
                         if (p == 0 && s == 0) mma16816_first(c, a0, a1, a2, a3, b.x, b.y);
                         else mma16816(c, a0, a1, a2, a3, b.x, b.y);
                     }
@@ -350,7 +361,7 @@ struct GroupedItem {
                     T::pairs(f1, sg, s, a1, a3);
 #pragma unroll
                     for (int gi = 0; gi < G; ++gi) {
-                        const uint2 b = *reinterpret_cast<const uint2*>(rec + xl.xs[gi] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * 32);
+                        const uint2 b = *reinterpret_cast<const uint2*>(rec + xl.xs[gi] + sub_of(sg, s) * kSubStride + lh_of(sg, s) * kHalfStride);
                         if (s == 0) mma16816_first(c[gi], a0, a1, a2, a3, b.x, b.y);
                         else mma16816(c[gi], a0, a1, a2, a3, b.x, b.y);
                     }
