@@ -484,12 +484,13 @@ struct Q6Kr : GroupedItem<Q6Kr> {
         const int wi = b * 2 + lh, hi = n * 2 + lh;
         const uint32_t w = wi == 0 ? c.x : wi == 1 ? c.y : wi == 2 ? c.z : c.w;
         const uint32_t h = hi == 0 ? f.qh.x : hi == 1 ? f.qh.y : hi == 2 ? f.qh.z : f.qh.w;
-        // 6-bit code = nibble | two high bits << 4, both halves of a pair at once
-        const int sh02 = 2 * quarter - 4, sh13 = 8 + 2 * quarter - 4;
-        const uint32_t h02 = sh02 >= 0 ? h >> sh02 : h << -sh02;
-        const uint32_t h13 = h >> sh13;
-        p02 = ((w >> (4 * nib)) & 0x000F000Fu) | (h02 & 0x00300030u);
-        p13 = ((w >> (8 + 4 * nib)) & 0x000F000Fu) | (h13 & 0x00300030u);
+        // the four 6-bit codes of this lane as bytes: nibble | two high bits << 4 (byte j of h holds element j's high bits
+        // of all four quarters, two bits each), then the byte pairs (0, 2) and (1, 3) as 16-bit lanes
+        const uint32_t wn = nib ? w >> 4 : w;
+        const uint32_t hs = quarter == 0 ? h << 4 : quarter == 1 ? h << 2 : quarter == 2 ? h : h >> 2;
+        const uint32_t codes = (wn & 0x0F0F0F0Fu) | (hs & 0x30303030u);
+        p02 = prmt(codes, 0u, 0x4240u);
+        p13 = prmt(codes, 0u, 0x4341u);
     }
     /// d * 2^24 * sc_g; the int8 goes to float through the 2^23 + 128 + sc bit pattern (exact, no conversion instruction)
     __device__ static float scale(const Scales& s, int g) {
