@@ -1,4 +1,4 @@
-"""ctypes binding of libhalo_cuda.so (the C ABI declared in include/halo_cuda.h).
+"""ctypes binding of libhalo_cuda.so (the C ABI declared in include/halo_cuda.h and include/halo_cuda_gguf.h).
 
 The library is the product; this module only loads it and mirrors its structs.  There is no CPU
 fallback: if the library is missing, or no sm_100 device is present, the calls fail loudly.
@@ -12,9 +12,10 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libhalo_cuda.so"
 
 OK = 0
-E_MODEL, E_MEMORY, E_BACKEND, E_KERNEL, E_CONFIG, E_API, E_DEVICE, E_UNSUPPORTED = -1, -2, -3, -4, -5, -6, -7, -8
+E_MODEL, E_MEMORY, E_BACKEND, E_KERNEL, E_CONFIG, E_API, E_DEVICE, E_UNSUPPORTED, E_IO = -1, -2, -3, -4, -5, -6, -7, -8, -9
 ERROR_NAMES = {E_MODEL: "Model", E_MEMORY: "Memory", E_BACKEND: "Backend", E_KERNEL: "Kernel", E_CONFIG: "Config", E_API: "Api",
-               E_DEVICE: "Device", E_UNSUPPORTED: "Unsupported"}
+               E_DEVICE: "Device", E_UNSUPPORTED: "Unsupported", E_IO: "Io"}
+SPLIT_NONE, SPLIT_COLUMN, SPLIT_ROW = 0, 1, 2
 
 OP_GET_ROWS, OP_GEMV, OP_LM_HEAD = 0, 3, 14
 GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16, GEMV_MMA_M1, GEMV_MMA_R = 0, 1, 2, 3, 4, 5, 6, 7
@@ -58,7 +59,26 @@ class GetRows(C.Structure):
                 ("n_ids", C.c_uint32), ("status", C.c_void_p)]
 
 
-# Every symbol include/halo_cuda.h declares: name -> (restype, argtypes)
+class GgufInfo(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("alignment", C.c_uint32), ("n_kv", C.c_uint64), ("n_tensors", C.c_uint64),
+                ("header_size", C.c_uint64), ("data_offset", C.c_uint64), ("file_size", C.c_uint64)]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("n_dims", C.c_uint32), ("type", C.c_uint32), ("ne", C.c_int64 * 4), ("offset", C.c_uint64),
+                ("n_elements", C.c_uint64), ("n_bytes", C.c_uint64), ("supported", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class Upload(C.Structure):
+    _fields_ = [("split", C.c_uint32), ("rank", C.c_uint32), ("world", C.c_uint32), ("repack", C.c_uint32), ("staging_bytes", C.c_uint64)]
+
+
+class Matrix(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("w_stride", C.c_uint64), ("bytes", C.c_uint64), ("wtype", C.c_uint32), ("variant_id", C.c_uint32),
+                ("rows", C.c_uint32), ("cols", C.c_uint32), ("row0", C.c_uint32), ("k0", C.c_uint32)]
+
+
+# Every symbol the two headers declare: name -> (restype, argtypes)
 _P = C.c_void_p
 SYMBOLS = {
     "halo_cuda_device_count": (C.c_int, [C.POINTER(C.c_int)]),
@@ -98,6 +118,19 @@ SYMBOLS = {
     "halo_cuda_ipc_open": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
     "halo_cuda_ipc_close": (C.c_int, [_P, _P]),
     "halo_cuda_gemv_reduce": (C.c_int, [_P, C.POINTER(Gemv), C.POINTER(PeerReduce), _P]),
+    "halo_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
+    "halo_gguf_parse": (C.c_int, [_P, C.c_uint64, C.POINTER(_P)]),
+    "halo_gguf_close": (C.c_int, [_P]),
+    "halo_gguf_info": (C.c_int, [_P, C.POINTER(GgufInfo)]),
+    "halo_gguf_kv_u64": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
+    "halo_gguf_kv_i64": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_int)]),
+    "halo_gguf_kv_f64": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
+    "halo_gguf_kv_string": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
+    "halo_gguf_tensor": (C.c_int, [_P, C.c_uint64, C.POINTER(GgufTensor)]),
+    "halo_gguf_find": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
+    "halo_gguf_tensor_data": (C.c_int, [_P, C.c_uint64, C.POINTER(_P), C.POINTER(C.c_uint64)]),
+    "halo_cuda_matrix_share": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(Upload), C.POINTER(Matrix)]),
+    "halo_cuda_upload_matrix": (C.c_int, [_P, _P, C.c_uint64, C.POINTER(Upload), _P, C.POINTER(Matrix)]),
 }
 
 _lib = None

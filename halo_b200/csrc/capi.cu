@@ -250,6 +250,10 @@ int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
         for (void* p : ctx->workspace)
             if (p != nullptr) cudaFree(p);
         if (ctx->error_word_host != nullptr) cudaFreeHost(ctx->error_word_host);
+        for (int i = 0; i < 2; ++i) {
+            if (ctx->staging[i] != nullptr) cudaFreeHost(ctx->staging[i]);
+            if (ctx->staging_done[i] != nullptr) cudaEventDestroy(ctx->staging_done[i]);
+        }
     }
     delete ctx;
     return 0;

@@ -51,6 +51,10 @@ struct HaloCudaCtx {
     // expired).  The host reads it after every stream wait; a set bit marks the context lost.
     uint32_t* error_word_host = nullptr;
     uint32_t* error_word_dev = nullptr;
+    // Two pinned host buffers the weight loader fills in turn, and the event behind each one's last device copy.
+    void* staging[2] = {nullptr, nullptr};
+    uint64_t staging_bytes = 0;
+    cudaEvent_t staging_done[2] = {nullptr, nullptr};
 };
 
 namespace halo_cuda {

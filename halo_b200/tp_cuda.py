@@ -12,7 +12,7 @@ import torch
 import torch.distributed as dist
 
 from . import backend as hb
-from . import capi, synth, tp
+from . import capi, gguf, synth, tp
 
 
 def variant_pushes(wtype: int, variant: int) -> bool:
@@ -85,8 +85,21 @@ class CudaTp:
             torch.cuda.current_stream(self.device).synchronize()
             buf.free()
             buf, variant = packed, capi.GEMV_MMA_R
-        self._weights[id(shard)] = buf
         shard.weights = np.empty((0, 0), np.uint8)  # the host copy is not needed any more
+        return self._projection(shard, buf, variant)
+
+    def load_file(self, f: gguf.GgufFile, info: gguf.TensorInfo, mode: str) -> tp.TpProjection:
+        """The same projection straight from a GGUF file: the loader cuts this rank's share out of the mapping, stages it through
+        pinned memory and repacks it on the device where the kernels have a repacked layout."""
+        split = {"column": capi.SPLIT_COLUMN, "row": capi.SPLIT_ROW}[mode]
+        m = gguf.upload_matrix(self.be, hb.Stream(self.be, self.stream()), f, info, split, self.rank, self.world, repack=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        shard = tp.Shard(mode, self.rank, self.world, m.wtype, m.rows, m.cols, m.row0, m.k0, np.empty((0, 0), np.uint8))
+        return self._projection(shard, m.buf if m.buf is not None else self.be.allocate(16), m.variant_id)
+
+    def _projection(self, shard: tp.Shard, buf: hb.Buffer, variant: int) -> tp.TpProjection:
+        mode, wtype = shard.mode, shard.wtype
+        self._weights[id(shard)] = buf
         if mode == "row" and self.peers is not None and variant_pushes(wtype, variant):
             # the matmul kernel pushes its rows to the peers and a small kernel adds them: no separate collective
             return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v, reduce=True), None, fused=True)

@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/halo_cuda.h declares.  CPU only: no compute calls."""
+"""The C-ABI library loads and exports every symbol the headers under include/ declare.  CPU only: no compute calls."""
 from __future__ import annotations
 
 import ctypes as C
@@ -9,13 +9,13 @@ import pytest
 
 from halo_b200 import capi
 
-HEADER = Path(__file__).resolve().parents[1] / "include" / "halo_cuda.h"
+HEADERS = sorted((Path(__file__).resolve().parents[1] / "include").glob("*.h"))
 
 
 def declared_functions() -> list[str]:
-    text = HEADER.read_text()
+    text = "\n".join(h.read_text() for h in HEADERS)
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(halo_cuda_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(halo_(?:cuda|gguf)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_is_built_in_tree():
@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported_and_bound():
     names = declared_functions()
     assert len(names) >= 25
     for n in names:
-        assert hasattr(lib, n), f"{n} is declared in halo_cuda.h but not exported"
+        assert hasattr(lib, n), f"{n} is declared under include/ but not exported"
         assert n in capi.SYMBOLS, f"{n} has no ctypes prototype"
     assert sorted(capi.SYMBOLS) == names
 
