@@ -281,6 +281,33 @@ public:
         return buf;
     }
 
+    CudaMat load_mat(Stream& s, const HaloGguf* file, std::string_view name, const CudaSplit& split) {
+        CudaStream& cs = stream_of(s, "load_mat");
+        HALO_CHECK(file != nullptr, ErrorCode::Api, "load_mat: null container");
+        const std::string key(name);
+        std::uint64_t index = 0;
+        int found = 0;
+        check(halo_gguf_find(file, key.c_str(), &index, &found));
+        HALO_CHECK(found != 0, ErrorCode::Model, "missing weight matrix {}", name);
+        HaloCudaUpload how{};
+        how.split = static_cast<std::uint32_t>(split.mode);
+        how.rank = split.rank;
+        how.world = split.world;
+        how.repack = split.repack ? 1 : 0;
+        HaloCudaMatrix m{};
+        check(halo_cuda_upload_matrix(ctx_, file, index, &how, cs.handle(), &m));
+        CudaMat out;
+        if (m.w != nullptr) out.buf = std::make_unique<CudaBuffer>(this, ctx_, m.w, m.bytes, false);
+        out.type = static_cast<DType>(m.wtype);
+        out.rows = m.rows;
+        out.cols = m.cols;
+        out.row0 = m.row0;
+        out.k0 = m.k0;
+        out.row_stride = m.w_stride;
+        out.kernel = KernelChoice{m.variant_id};
+        return out;
+    }
+
     void set_plan(std::span<const CudaPlanEntry> plan) {
         check(halo_cuda_plan_clear(ctx_));
         for (const CudaPlanEntry& p : plan)
@@ -376,6 +403,12 @@ std::unique_ptr<Buffer> cuda_backend_repack(Backend& backend, Stream& stream, DT
     auto* cb = dynamic_cast<CudaBackend*>(&backend);
     HALO_CHECK(cb != nullptr, ErrorCode::Api, "cuda_backend_repack: not a cuda backend");
     return cb->repack(stream, wtype, src, rows, cols);
+}
+
+CudaMat cuda_backend_load_mat(Backend& backend, Stream& stream, const HaloGguf* file, std::string_view name, const CudaSplit& split) {
+    auto* cb = dynamic_cast<CudaBackend*>(&backend);
+    HALO_CHECK(cb != nullptr, ErrorCode::Api, "cuda_backend_load_mat: not a cuda backend");
+    return cb->load_mat(stream, file, name, split);
 }
 
 void cuda_backend_set_plan(Backend& backend, std::span<const CudaPlanEntry> plan) {

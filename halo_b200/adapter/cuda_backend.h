@@ -17,7 +17,10 @@
 #include <cstdint>
 #include <memory>
 
+#include <string_view>
+
 #include "halo/backend/backend.h"
+#include "halo_cuda_gguf.h"
 
 namespace halo::backend {
 
@@ -45,6 +48,32 @@ struct CudaPlanEntry {
 /// GemvArgs::w together with KernelChoice{7}.  Error(Unsupported) for other types, Error(Api) for another backend.
 [[nodiscard]] std::unique_ptr<Buffer> cuda_backend_repack(Backend& backend, Stream& stream, DType wtype, const TensorRef& src, std::uint32_t rows,
                                                           std::uint32_t cols);
+
+/// How a matrix is shared out over a tensor-parallel group: Column keeps whole W rows of each rank, Row keeps a K range cut at
+/// whole quantization blocks (ranges dealt like ThreadPool::partition_range, include/halo/backends/cpu/thread_pool.h:64-72).
+struct CudaSplit {
+    enum class Mode : std::uint32_t { None = 0, Column = 1, Row = 2 } mode = Mode::None;
+    std::uint32_t rank = 0, world = 1;
+    bool repack = false;  ///< store Q6_K / Q8_0 / Q4_0 rows in the gemv_mma_r layout when the local K is a multiple of 256
+};
+
+/// A device-resident matmul operand with what GemvArgs needs beside it: the counterpart of the model's Mat
+/// (src/models/qwen35.cpp:52-67).  `kernel` is KernelChoice{7} for repacked rows, else KernelChoice{}.
+struct CudaMat {
+    std::unique_ptr<Buffer> buf;  ///< null for an empty share
+    DType type = DType::F32;
+    std::uint32_t rows = 0, cols = 0;  ///< local extents
+    std::uint32_t row0 = 0, k0 = 0;    ///< first global row / K element of the share
+    std::uint64_t row_stride = 0;
+    KernelChoice kernel{};
+    [[nodiscard]] TensorRef ref() const { return TensorRef::of(*buf).with_stride(row_stride); }
+};
+
+/// Loads tensor `name` of an opened GGUF container (halo_gguf_open / halo_gguf_parse), or one rank's share of it, into device
+/// memory of `backend`: what Impl::make_mat + import_host_readonly + try_repack do for the reference's backends
+/// (src/models/qwen35.cpp:301-346), with the file read through pinned staging while the previous piece is in flight.
+/// Error(Model) for a missing tensor, a tensor that is not a matrix of dense rows; Error(Unsupported) for a type without a kernel.
+[[nodiscard]] CudaMat cuda_backend_load_mat(Backend& backend, Stream& stream, const HaloGguf* file, std::string_view name, const CudaSplit& split = {});
 
 /// Installs tuner decisions on a backend made by make_cuda_backend (Error(Api) for any other backend).
 void cuda_backend_set_plan(Backend& backend, std::span<const CudaPlanEntry> plan);

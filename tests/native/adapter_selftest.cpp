@@ -202,6 +202,107 @@ void test_gemv_repacked(Pair& p, Report& r) {
     r.expect(refused, "Q4_K has no repacked layout: Error(Unsupported)");
 }
 
+/// Appends the little-endian bytes of a trivially copyable value.
+template <class T>
+void put(std::vector<std::byte>& out, T v) {
+    const auto* p = reinterpret_cast<const std::byte*>(&v);
+    out.insert(out.end(), p, p + sizeof v);
+}
+void put_string(std::vector<std::byte>& out, std::string_view s) {
+    put<std::uint64_t>(out, s.size());
+    out.insert(out.end(), reinterpret_cast<const std::byte*>(s.data()), reinterpret_cast<const std::byte*>(s.data()) + s.size());
+}
+
+/// Weights loaded from a GGUF image through the adapter: the product over a loaded operand is bitwise the product over the same
+/// bytes imported directly, for the whole matrix and for the shares of a tensor-parallel group.
+void test_load_mat(Pair& p, Report& r) {
+    struct Entry {
+        const char* name;
+        DType t;
+        std::uint32_t n, k;
+        std::vector<std::byte> w;
+        std::uint64_t offset = 0;
+    };
+    std::vector<Entry> entries;
+    entries.push_back({"blk.0.ffn_up.weight", DType::Q4_K, 45, 1024, {}});
+    entries.push_back({"blk.0.ffn_down.weight", DType::Q6_K, 33, 1536, {}});
+    entries.push_back({"output.weight", DType::Q4_0, 70, 512, {}});
+    std::vector<std::byte> data;
+    for (Entry& e : entries) {
+        e.w = random_weights(e.t, e.n, e.k, 40 + e.n);
+        data.resize((data.size() + 31) / 32 * 32);
+        e.offset = data.size();
+        data.insert(data.end(), e.w.begin(), e.w.end());
+    }
+    std::vector<std::byte> img;
+    put<std::uint32_t>(img, 0x46554747u);
+    put<std::uint32_t>(img, 3);
+    put<std::uint64_t>(img, entries.size());
+    put<std::uint64_t>(img, 1);
+    put_string(img, "general.architecture");
+    put<std::uint32_t>(img, 8);
+    put_string(img, "qwen35");
+    for (const Entry& e : entries) {
+        put_string(img, e.name);
+        put<std::uint32_t>(img, 2);
+        put<std::uint64_t>(img, e.k);
+        put<std::uint64_t>(img, e.n);
+        put<std::uint32_t>(img, static_cast<std::uint32_t>(e.t));
+        put<std::uint64_t>(img, e.offset);
+    }
+    img.resize((img.size() + 31) / 32 * 32);
+    img.insert(img.end(), data.begin(), data.end());
+
+    HaloGguf* file = nullptr;
+    r.expect(halo_gguf_parse(img.data(), img.size(), &file) == 0 && file != nullptr, "the GGUF image parses");
+    if (file == nullptr) return;
+    const std::uint32_t m = 3;
+    for (const Entry& e : entries) {
+        const auto x = random_floats(std::size_t{m} * e.k, 50);
+        std::vector<float> yc, yg;
+        run_gemv_both(p, e.t, e.w, x, e.n, e.k, m, 1 /*gemv_exact8*/, yc, yg);
+        const auto xb = p.gpu->import_host_readonly(cbytes(x.data(), x.size() * 4));
+        const auto run = [&](const hb::CudaMat& mat, const hb::TensorRef& xr, hb::KernelChoice kernel) {
+            std::vector<float> y(std::size_t{m} * mat.rows);
+            const auto yb = p.gpu->allocate(std::max<std::size_t>(y.size() * 4, 4), hb::Tier::Vram);
+            p.gpu->gemv(*p.gst, {mat.type, mat.ref(), xr, hb::TensorRef::of(*yb), mat.rows, mat.cols, m, kernel});
+            p.gpu->download(*p.gst, hb::TensorRef::of(*yb), wbytes(y.data(), y.size() * 4));
+            p.gst->wait();
+            return y;
+        };
+        const hb::CudaMat whole = hb::cuda_backend_load_mat(*p.gpu, *p.gst, file, e.name);
+        r.expect(whole.rows == e.n && whole.cols == e.k && whole.type == e.t && whole.kernel.variant_id == 0, std::format("{}: extents of the loaded operand", e.name));
+        r.expect(run(whole, hb::TensorRef::of(*xb), {1}) == yc, std::format("{}: exact-order product over the loaded operand is bitwise the CPU backend's", e.name));
+        // column shares: whole rows, bitwise the rows of the CPU backend's product in the exact-order variant
+        bool cols_ok = true;
+        for (std::uint32_t rank = 0; rank < 3; ++rank) {
+            const hb::CudaMat part = hb::cuda_backend_load_mat(*p.gpu, *p.gst, file, e.name, {hb::CudaSplit::Mode::Column, rank, 3, false});
+            const auto y = run(part, hb::TensorRef::of(*xb), {1});
+            for (std::uint32_t t = 0; t < m; ++t)
+                for (std::uint32_t n = 0; n < part.rows; ++n) cols_ok = cols_ok && y[std::size_t{t} * part.rows + n] == yc[std::size_t{t} * e.n + part.row0 + n];
+        }
+        r.expect(cols_ok, std::format("{}: three column shares give the rows of the whole product bit for bit", e.name));
+        // row shares (repacked where the type has the layout): partial products over each rank's K range add up to the whole
+        std::vector<double> sum(yc.size(), 0.0);
+        for (std::uint32_t rank = 0; rank < 2; ++rank) {
+            const hb::CudaMat part = hb::cuda_backend_load_mat(*p.gpu, *p.gst, file, e.name, {hb::CudaSplit::Mode::Row, rank, 2, true});
+            r.expect((part.kernel.variant_id == 7) == (e.t != DType::Q4_K), std::format("{}: row share {} repacked iff the type has the layout", e.name, rank));
+            const auto xr = hb::TensorRef::of(*xb).shifted(std::uint64_t{part.k0} * 4).with_stride(std::uint64_t{e.k} * 4);
+            const auto y = run(part, xr, part.kernel);
+            for (std::size_t i = 0; i < y.size(); ++i) sum[i] += y[i];
+        }
+        float maxref = 0, maxerr = 0;
+        for (std::size_t i = 0; i < yc.size(); ++i) {
+            maxref = std::max(maxref, std::fabs(yc[i]));
+            maxerr = std::max(maxerr, std::fabs(yc[i] - static_cast<float>(sum[i])));
+        }
+        r.expect(maxerr <= 1e-3f * maxref, std::format("{}: two row shares add up to the CPU backend's product: {} vs {}", e.name, maxerr, maxref));
+    }
+    r.expect(code_of([&] { (void)hb::cuda_backend_load_mat(*p.gpu, *p.gst, file, "blk.7.missing.weight"); }) == static_cast<int>(halo::ErrorCode::Model),
+             "a missing tensor: Error(Model)");
+    halo_gguf_close(file);
+}
+
 void test_validation_parity(Pair& p, Report& r) {
     const std::uint32_t N = 8, K = 64, T = 2;
     const auto w = random_weights(DType::Q8_0, N, K, 3);
@@ -378,6 +479,7 @@ extern "C" int halo_adapter_selftest(char* report, std::size_t len) {
         Pair p;
         test_registry(p, r);
         test_gemv_repacked(p, r);
+        test_load_mat(p, r);
         test_gemv_bitwise(p, r);
         test_validation_parity(p, r);
         test_lm_head(p, r);
