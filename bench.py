@@ -348,6 +348,49 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
     return out
 
 
+def loader_leg(be, st, rank: int, world: int, reps: int = 3):
+    """File -> device: this rank's column share of the config-4 LM head (Q4_0, 151936 x 5120, 437.6 MB in all) brought from a GGUF
+    file in the page cache into HBM by the loader (pinned double-buffered staging, repack on the device), beside the plain
+    import of the same bytes from pageable memory.  Wall clock around call + stream wait; best of `reps`."""
+    import tempfile
+
+    import numpy as np
+
+    from halo_b200 import capi, gguf, synth
+
+    rows, cols, t = 151936, 5120, synth.Q4_0
+    rb = synth.row_bytes(t, cols)
+    raw = np.random.default_rng(rank).integers(0, 256, rows * rb, dtype=np.uint8)
+    out = {"tensor": f"Q4_0 {rows} x {cols}", "file_mb": raw.size / 1e6, "split": f"column x{world}"}
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "head.gguf")
+        gguf.write_gguf(path, [("output.weight", t, rows, cols, raw)], {"general.architecture": "qwen35"})
+        with gguf.GgufFile.open(path) as f:
+            info = f.find_tensor("output.weight")
+            share = gguf.matrix_share(t, rows, cols, capi.SPLIT_COLUMN, rank, world)
+            nbytes = share.rows * rb
+            for name, repack in (("upload_gbs", False), ("upload_repacked_gbs", True)):
+                best = float("inf")
+                for _ in range(reps + 1):
+                    t0 = time.perf_counter()
+                    m = gguf.upload_matrix(be, st, f, info, capi.SPLIT_COLUMN, rank, world, repack=repack)
+                    st.wait()
+                    best = min(best, time.perf_counter() - t0)
+                    m.buf.free()
+                out[name] = nbytes / best / 1e9
+    lo = share.row0 * rb
+    best = float("inf")
+    for _ in range(reps + 1):
+        t0 = time.perf_counter()
+        b = be.import_host_readonly(raw[lo:lo + nbytes])
+        st.wait()
+        best = min(best, time.perf_counter() - t0)
+        b.free()
+    out["import_pageable_gbs"] = nbytes / best / 1e9
+    out["share_mb"] = nbytes / 1e6
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -548,12 +591,13 @@ def run_ours(args) -> None:
             sms = timed(split_pass, psteps) / psteps
             prefill["column_split"] = {"rows_per_gpu": n_split, "ms_per_call": sms, "tflops": flops / (sms * 1e-3) / 1e12, "scaling": "strong"}
 
-    sweep = shapes = None
+    sweep = shapes = loader = None
     if not args.profile:
         for b in wbufs[1:] + ybufs[1:]:
             b.free()
         shapes = decode_shapes(be, st, rank, world, max(3, min(args.steps, 20)))
         sweep = tp_sweep(local_rank, rank, world, max(3, min(args.steps, 20)))
+        loader = loader_leg(be, st, rank, world)
     clocks = sampler.stop() if rank == 0 else None
 
     launches_per_step = COPIES
@@ -587,6 +631,7 @@ def run_ours(args) -> None:
         "prefill": prefill,
         "decode_shapes": shapes,
         "tp_sweep": sweep,
+        "loader": loader,
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

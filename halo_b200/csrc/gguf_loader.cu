@@ -523,7 +523,7 @@ int plan_share(uint32_t wtype, uint64_t rows, uint64_t cols, const HaloCudaUploa
         s->byte0 = b * ti.block_bytes;
     }
     s->row_bytes = s->cols / ti.block_elems * ti.block_bytes;
-    s->repack = how != nullptr && how->repack != 0 && s->rows != 0 && s->cols != 0 && repacked_row_bytes(wtype, s->cols) != 0;
+    s->repack = how != nullptr && how->repack != 0 && s->rows != 0 && s->cols != 0 && s->cols % 256 == 0 && repacked_row_bytes(wtype, s->cols) != 0;
     return 0;
 }
 

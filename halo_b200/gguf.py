@@ -167,3 +167,41 @@ def upload_matrix(be: hb.CudaBackend, s: hb.Stream, f: GgufFile, t: TensorInfo, 
                                           C.byref(m)))
     buf = hb.Buffer(be, m.w, m.bytes, writable=False) if m.w else None
     return DeviceMatrix(buf, m.wtype, m.variant_id, m.rows, m.cols, m.w_stride, m.row0, m.k0)
+
+
+def write_gguf(path: str | Path, tensors: list[tuple[str, int, int, int, np.ndarray]], metadata: dict[str, int | float | str] | None = None,
+               alignment: int = 32) -> None:
+    """Writes a GGUF v3 container of 2-D tensors (name, ggml type, rows, cols, raw row bytes) and scalar / string metadata:
+    enough to produce synthetic model files for the loader (the published layout; integers as UINT32, floats as FLOAT32)."""
+    import struct
+
+    def s(b: str) -> bytes:
+        e = b.encode()
+        return struct.pack("<Q", len(e)) + e
+
+    meta = dict(metadata or {})
+    if alignment != 32:
+        meta["general.alignment"] = alignment
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(meta))
+    for k, v in meta.items():
+        if isinstance(v, str):
+            head += s(k) + struct.pack("<I", 8) + s(v)
+        elif isinstance(v, float):
+            head += s(k) + struct.pack("<If", 6, v)
+        else:
+            head += s(k) + struct.pack("<II", 4, v)
+    offset, offsets = 0, []
+    for name, t, rows, cols, raw in tensors:
+        offset = (offset + alignment - 1) // alignment * alignment
+        offsets.append(offset)
+        head += s(name) + struct.pack("<IQQIQ", 2, cols, rows, t, offset)
+        offset += int(np.asarray(raw).nbytes)
+    with open(path, "wb") as out:
+        out.write(head)
+        out.write(b"\0" * ((-len(head)) % alignment))
+        pos = 0
+        for (name, t, rows, cols, raw), off in zip(tensors, offsets):
+            out.write(b"\0" * (off - pos))
+            a = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+            out.write(a.data)
+            pos = off + a.size

@@ -263,6 +263,8 @@ def test_share_extents_match_the_tensor_parallel_split():
     assert whole.variant_id == capi.GEMV_MMA_R and whole.row_stride == 17408 // 256 * 224
     assert matrix_share(Q4_K, 64, 512, repack=True).variant_id == capi.GEMV_DEFAULT  # Q4_K has no repacked layout
     assert matrix_share(Q8_0, 64, 96, repack=True).variant_id == capi.GEMV_DEFAULT   # K is not a whole number of 256-element groups
+    assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 4, repack=True).variant_id == capi.GEMV_DEFAULT  # 384 local columns: one and a half groups
+    assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 2, repack=True).variant_id == capi.GEMV_MMA_R
     for bad, status in (((Q5_K, 4, 256), capi.E_UNSUPPORTED), ((Q4_K, 4, 100), capi.E_MODEL)):
         with pytest.raises(HaloError) as e:
             matrix_share(*bad)
@@ -270,3 +272,21 @@ def test_share_extents_match_the_tensor_parallel_split():
     with pytest.raises(HaloError) as e:
         matrix_share(Q4_K, 4, 256, capi.SPLIT_ROW, 2, 2)
     assert code_of(e) == capi.E_API
+
+
+def test_writer_round_trip(tmp_path):
+    """halo_b200.gguf.write_gguf produces a container both this index and gguf-py read back."""
+    from halo_b200.gguf import write_gguf
+    w = synth.quant_weights(Q6_K, 5, 512, seed=1)
+    v = synth.quant_weights(Q4_K, 3, 256, seed=2)
+    path = tmp_path / "s.gguf"
+    write_gguf(path, [("a.weight", Q6_K, 5, 512, w), ("b.weight", Q4_K, 3, 256, v)], {"general.architecture": "qwen35", "n": 3, "eps": 1.5}, alignment=64)
+    f = GgufFile.open(path)
+    assert f.alignment == 64 and f.get_uint("n") == 3 and f.get_float("eps") == 1.5 and f.get_string("general.architecture") == "qwen35"
+    a, b = f.find_tensor("a.weight"), f.find_tensor("b.weight")
+    assert (a.ne[0], a.ne[1], b.ne[0], b.ne[1]) == (512, 5, 256, 3) and a.offset % 64 == 0 and b.offset % 64 == 0
+    assert f.tensor_data(a).tobytes() == np.ascontiguousarray(w).tobytes() and f.tensor_data(b).tobytes() == np.ascontiguousarray(v).tobytes()
+    gguf = pytest.importorskip("gguf")
+    theirs = {t.name: t for t in gguf.GGUFReader(str(path)).tensors}
+    assert np.ascontiguousarray(theirs["a.weight"].data).tobytes() == np.ascontiguousarray(w).tobytes()
+    assert int(theirs["b.weight"].tensor_type) == Q4_K and theirs["b.weight"].data_offset == f.data_offset + b.offset
