@@ -252,7 +252,8 @@ int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
         if (ctx->error_word_host != nullptr) cudaFreeHost(ctx->error_word_host);
         for (int i = 0; i < 2; ++i) {
             if (ctx->staging[i] != nullptr) cudaFreeHost(ctx->staging[i]);
-            if (ctx->staging_done[i] != nullptr) cudaEventDestroy(ctx->staging_done[i]);
+            for (cudaEvent_t e : ctx->staging_done[i])
+                if (e != nullptr) cudaEventDestroy(e);
         }
     }
     delete ctx;

@@ -17,6 +17,7 @@
 #include <cstring>
 #include <string>
 #include <string_view>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -539,16 +540,23 @@ void fill_matrix(uint32_t wtype, const Share& s, HaloCudaMatrix* out) {
     out->bytes = s.rows * out->w_stride;
 }
 
-/// The context's two pinned staging buffers of at least `bytes` each (grown on demand) and their events.
+constexpr uint32_t kMaxLanes = 8;  // HaloCudaCtx::staging_done holds two events per lane
+
+/// The context's two pinned staging buffers of at least `bytes` each (grown on demand) and the events of their lanes.
 int staging(HaloCudaCtx* ctx, uint64_t bytes) {
+    for (int i = 0; i < 2; ++i)
+        for (uint32_t l = 0; l < kMaxLanes; ++l)
+            if (ctx->staging_done[i][l] == nullptr) HC_CUDA(cudaEventCreateWithFlags(&ctx->staging_done[i][l], cudaEventDisableTiming));
+    // The last copies of an earlier upload may still be reading the buffers, cut into lanes of another size: let them drain
+    // (a fraction of a millisecond) before this upload's lanes write there.
+    for (int i = 0; i < 2; ++i)
+        for (uint32_t l = 0; l < kMaxLanes; ++l) HC_CUDA(cudaEventSynchronize(ctx->staging_done[i][l]));
     if (ctx->staging_bytes >= bytes) return 0;
     for (int i = 0; i < 2; ++i) {
         if (ctx->staging[i] != nullptr) {
-            HC_CUDA(cudaEventSynchronize(ctx->staging_done[i]));  // an earlier upload may still be reading it
             HC_CUDA(cudaFreeHost(ctx->staging[i]));
             ctx->staging[i] = nullptr;
         }
-        if (ctx->staging_done[i] == nullptr) HC_CUDA(cudaEventCreateWithFlags(&ctx->staging_done[i], cudaEventDisableTiming));
     }
     ctx->staging_bytes = 0;
     for (int i = 0; i < 2; ++i) {
@@ -561,6 +569,38 @@ int staging(HaloCudaCtx* ctx, uint64_t bytes) {
     ctx->staging_bytes = bytes;
     return 0;
 }
+
+/// One lane of the upload: rows [row_begin, row_end) of the share go, `lane_rows` at a time, from the mapping into this lane's
+/// part of the two staging buffers in turn and from there to the device.  Lanes run on host threads of their own -- one core's
+/// memcpy out of the page cache carries a fraction of what the link to the device does -- and share nothing but the stream.
+struct Lane {
+    HaloCudaCtx* ctx;
+    cudaStream_t stream;
+    uint32_t index;
+    const uint8_t* src;  // first byte of the share's row 0
+    uint8_t* dst;        // device, dense rows
+    uint64_t row_begin, row_end, lane_rows, row_bytes, src_row_bytes;
+    cudaError_t status = cudaSuccess;
+
+    void run() {
+        status = cudaSetDevice(ctx->device);
+        uint32_t turn = 0;
+        for (uint64_t r0 = row_begin; r0 < row_end && status == cudaSuccess; r0 += lane_rows, turn ^= 1) {
+            const uint64_t n = std::min(lane_rows, row_end - r0);
+            uint8_t* stage = static_cast<uint8_t*>(ctx->staging[turn]) + uint64_t{index} * lane_rows * row_bytes;
+            // the copy that last read this part of the buffer must have drained before the host overwrites it
+            status = cudaEventSynchronize(ctx->staging_done[turn][index]);
+            if (status != cudaSuccess) break;
+            if (row_bytes == src_row_bytes) {
+                std::memcpy(stage, src + r0 * src_row_bytes, n * row_bytes);
+            } else {
+                for (uint64_t r = 0; r < n; ++r) std::memcpy(stage + r * row_bytes, src + (r0 + r) * src_row_bytes, row_bytes);
+            }
+            status = cudaMemcpyAsync(dst + r0 * row_bytes, stage, n * row_bytes, cudaMemcpyHostToDevice, stream);
+            if (status == cudaSuccess) status = cudaEventRecord(ctx->staging_done[turn][index], stream);
+        }
+    }
+};
 
 }  // namespace
 
@@ -591,32 +631,30 @@ int halo_cuda_upload_matrix(HaloCudaCtx* ctx, const HaloGguf* g, uint64_t index,
 
     const cudaStream_t cs = static_cast<cudaStream_t>(stream);
     const uint64_t want = how != nullptr && how->staging_bytes != 0 ? how->staging_bytes : (32ull << 20);
-    // a staging buffer holds whole rows of the share, at least one
-    const uint64_t rows_per_chunk = std::max<uint64_t>(1, want / s.row_bytes);
-    if (int rc = staging(ctx, std::min(rows_per_chunk, s.rows) * s.row_bytes)) return rc;
+    // one lane per 8 MiB of the share, each with room for whole rows (at least one) in both staging buffers
+    const uint32_t lanes = uint32_t(std::min<uint64_t>({kMaxLanes, std::max(1u, std::thread::hardware_concurrency()), std::max<uint64_t>(1, raw_bytes >> 23), s.rows}));
+    const uint64_t lane_rows = std::min(std::max<uint64_t>(1, want / lanes / s.row_bytes), (s.rows + lanes - 1) / lanes);
+    if (int rc = staging(ctx, lanes * lane_rows * s.row_bytes)) return rc;
 
     void* raw = nullptr;
     if (int rc = halo_cuda_malloc(ctx, raw_bytes, 0, &raw)) return rc;
     const uint8_t* src = g->bytes + g->info.data_offset + t.offset + s.row0 * s.src_row_bytes + s.byte0;
-    const bool contiguous = s.row_bytes == s.src_row_bytes;
-    int rc = 0;
-    uint32_t turn = 0;
-    for (uint64_t r0 = 0; r0 < s.rows && rc == 0; r0 += rows_per_chunk, turn ^= 1) {
-        const uint64_t n = std::min(rows_per_chunk, s.rows - r0);
-        uint8_t* stage = static_cast<uint8_t*>(ctx->staging[turn]);
-        // the copy that last read this buffer must have drained before the host overwrites it
-        cudaError_t e = cudaEventSynchronize(ctx->staging_done[turn]);
-        if (e == cudaSuccess) {
-            if (contiguous) {
-                std::memcpy(stage, src + r0 * s.src_row_bytes, n * s.row_bytes);
-            } else {
-                for (uint64_t r = 0; r < n; ++r) std::memcpy(stage + r * s.row_bytes, src + (r0 + r) * s.src_row_bytes, s.row_bytes);
-            }
-            e = cudaMemcpyAsync(static_cast<uint8_t*>(raw) + r0 * s.row_bytes, stage, n * s.row_bytes, cudaMemcpyHostToDevice, cs);
-        }
-        if (e == cudaSuccess) e = cudaEventRecord(ctx->staging_done[turn], cs);
-        if (e != cudaSuccess) rc = fail(HALO_CUDA_E_BACKEND, "upload of '%s': %s", t.name, cudaGetErrorString(e));
+    std::vector<Lane> work(lanes);
+    for (uint32_t l = 0; l < lanes; ++l) {
+        uint64_t b, e;
+        even_part(s.rows, lanes, l, &b, &e);
+        work[l] = Lane{ctx, cs, l, src, static_cast<uint8_t*>(raw), b, e, lane_rows, s.row_bytes, s.src_row_bytes};
     }
+    {
+        std::vector<std::thread> helpers;
+        helpers.reserve(lanes - 1);
+        for (uint32_t l = 1; l < lanes; ++l) helpers.emplace_back(&Lane::run, &work[l]);
+        work[0].run();
+        for (std::thread& th : helpers) th.join();
+    }
+    int rc = 0;
+    for (const Lane& l : work)
+        if (l.status != cudaSuccess && rc == 0) rc = fail(HALO_CUDA_E_BACKEND, "upload of '%s': %s", t.name, cudaGetErrorString(l.status));
     void* packed = nullptr;
     if (rc == 0 && s.repack) {
         rc = halo_cuda_malloc(ctx, out->bytes, 0, &packed);

@@ -51,10 +51,11 @@ struct HaloCudaCtx {
     // expired).  The host reads it after every stream wait; a set bit marks the context lost.
     uint32_t* error_word_host = nullptr;
     uint32_t* error_word_dev = nullptr;
-    // Two pinned host buffers the weight loader fills in turn, and the event behind each one's last device copy.
+    // Two pinned host buffers the weight loader fills in turn, each cut into up to eight lanes (one per host thread), and the
+    // event behind the last device copy out of each lane.
     void* staging[2] = {nullptr, nullptr};
     uint64_t staging_bytes = 0;
-    cudaEvent_t staging_done[2] = {nullptr, nullptr};
+    cudaEvent_t staging_done[2][8] = {};
 };
 
 namespace halo_cuda {
