@@ -205,9 +205,11 @@ class CudaBackend:
         return [(arr[i].id, arr[i].name.decode(), arr[i].family) for i in range(n.value)]
 
     # ---- memory ----------------------------------------------------------------------------------
-    def allocate(self, nbytes: int, zero: bool = True) -> Buffer:
+    def allocate(self, nbytes: int, zero: bool = True, shareable: bool = False) -> Buffer:
+        """Zero-filled device memory from the context's pool (Backend::allocate, backend.h:523); `shareable` takes it from the
+        driver instead, which exporting it to another process needs."""
         p = C.c_void_p()
-        _check(self.lib.halo_cuda_malloc(self.ctx, nbytes, 1 if zero else 0, C.byref(p)))
+        _check(self.lib.halo_cuda_malloc(self.ctx, nbytes, (1 if zero else 0) | (2 if shareable else 0), C.byref(p)))
         return Buffer(self, p.value or 0, nbytes, True)
 
     def _free(self, ptr: int) -> None:

@@ -240,6 +240,21 @@ int halo_cuda_ctx_create(int device, HaloCudaCtx** out) {
         if (cudaHostGetDevicePointer(&dev_word, host_word, 0) == cudaSuccess) ctx->error_word_dev = static_cast<uint32_t*>(dev_word);
     }
     cudaGetLastError();
+    cudaMemPoolProps props{};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
+    e = cudaMemPoolCreate(&ctx->pool, &props);
+    if (e == cudaSuccess) {
+        uint64_t keep = UINT64_MAX;  // freed blocks stay with the pool
+        e = cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->pool_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        halo_cuda_ctx_destroy(ctx);
+        return fail(HALO_CUDA_E_BACKEND, "device %d: cannot set up the allocation pool: %s", device, cudaGetErrorString(e));
+    }
     *out = ctx;
     return 0;
 }
@@ -247,6 +262,15 @@ int halo_cuda_ctx_create(int device, HaloCudaCtx** out) {
 int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
     if (ctx == nullptr) return 0;
     if (cudaSetDevice(ctx->device) == cudaSuccess) {
+        if (ctx->pool != nullptr) {
+            cudaDeviceSynchronize();
+            for (void* p : ctx->pooled) cudaFreeAsync(p, ctx->pool_stream);
+            if (ctx->pool_stream != nullptr) {
+                cudaStreamSynchronize(ctx->pool_stream);
+                cudaStreamDestroy(ctx->pool_stream);
+            }
+            cudaMemPoolDestroy(ctx->pool);
+        }
         for (void* p : ctx->workspace)
             if (p != nullptr) cudaFree(p);
         if (ctx->error_word_host != nullptr) cudaFreeHost(ctx->error_word_host);
@@ -281,22 +305,31 @@ int halo_cuda_device_info(HaloCudaCtx* ctx, HaloCudaDeviceInfo* info) {
     return 0;
 }
 
-int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int zero, void** ptr) {
+int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int flags, void** ptr) {
     if (ptr == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
     *ptr = nullptr;
     if (int rc = enter(ctx)) return rc;
-    const cudaError_t e = cudaMalloc(ptr, bytes == 0 ? 1 : bytes);
+    const bool zero = (flags & HALO_CUDA_MALLOC_ZERO) != 0, shareable = (flags & HALO_CUDA_MALLOC_SHAREABLE) != 0;
+    const uint64_t size = bytes == 0 ? 1 : bytes;
+    const cudaError_t e = shareable ? cudaMalloc(ptr, size) : cudaMallocFromPoolAsync(ptr, size, ctx->pool, ctx->pool_stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
+        *ptr = nullptr;
         return fail(HALO_CUDA_E_MEMORY, "cannot allocate %llu bytes on device %d: %s", (unsigned long long)bytes, ctx->device,
                     cudaGetErrorString(e));
     }
-    if (zero != 0 && bytes != 0) {
-        // The clear runs on the legacy default stream, which the non-blocking streams of this library do not wait
-        // for: finish it here so that no later upload can be overtaken by it.
-        HC_CUDA(cudaMemset(*ptr, 0, bytes));
-        HC_CUDA(cudaStreamSynchronize(nullptr));
+    // The block belongs to the pool's stream until that stream has passed the allocation (and the clear): finish both here,
+    // so that the pointer is good on every stream and no later upload can be overtaken by the clear.
+    cudaError_t f = cudaSuccess;
+    if (zero && bytes != 0) f = cudaMemsetAsync(*ptr, 0, bytes, ctx->pool_stream);
+    if (f == cudaSuccess && (!shareable || zero)) f = cudaStreamSynchronize(ctx->pool_stream);
+    if (f != cudaSuccess) {
+        if (shareable) cudaFree(*ptr);
+        else cudaFreeAsync(*ptr, ctx->pool_stream);
+        *ptr = nullptr;
+        return fail(HALO_CUDA_E_BACKEND, "clearing %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(f));
     }
+    if (!shareable) ctx->pooled.insert(*ptr);
     return 0;
 }
 
@@ -304,7 +337,16 @@ int halo_cuda_free(HaloCudaCtx* ctx, void* ptr) {
     if (ptr == nullptr) return 0;
     if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
     HC_CUDA(cudaSetDevice(ctx->device));
-    HC_CUDA(cudaFree(ptr));
+    const auto it = ctx->pooled.find(ptr);
+    if (it == ctx->pooled.end()) {
+        HC_CUDA(cudaFree(ptr));  // waits for the device, like the pool path below
+        return 0;
+    }
+    // Work that still reads or writes the block may be queued on any stream: wait for the device (a no-op for a caller
+    // that frees after its stream wait), then hand the block back to the pool, where the next allocation finds it.
+    HC_CUDA(cudaDeviceSynchronize());
+    ctx->pooled.erase(it);
+    HC_CUDA(cudaFreeAsync(ptr, ctx->pool_stream));
     return 0;
 }
 
@@ -586,6 +628,8 @@ int halo_cuda_ipc_export(HaloCudaCtx* ctx, void* ptr, uint8_t handle[64]) {
     if (int rc = enter(ctx)) return rc;
     if (ptr == nullptr || handle == nullptr) return fail(HALO_CUDA_E_API, "null argument");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size of the C ABI");
+    if (ctx->pooled.count(ptr) != 0)
+        return fail(HALO_CUDA_E_KERNEL, "ipc_export: the block comes from the allocation pool; allocate it with HALO_CUDA_MALLOC_SHAREABLE");
     cudaIpcMemHandle_t h;
     HC_CUDA(cudaIpcGetMemHandle(&h, ptr));
     std::memcpy(handle, &h, 64);

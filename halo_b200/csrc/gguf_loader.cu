@@ -667,13 +667,13 @@ int halo_cuda_upload_matrix(HaloCudaCtx* ctx, const HaloGguf* g, uint64_t index,
     }
     if (rc != 0) {
         cudaStreamSynchronize(cs);
-        cudaFree(raw);
-        if (packed != nullptr) cudaFree(packed);
+        halo_cuda_free(ctx, raw);
+        if (packed != nullptr) halo_cuda_free(ctx, packed);
         std::memset(out, 0, sizeof *out);
         return rc;
     }
     if (s.repack) {
-        cudaFree(raw);
+        halo_cuda_free(ctx, raw);
         out->w = packed;
     } else {
         out->w = raw;

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
+#include <unordered_set>
 #include <vector>
 
 #include "halo_cuda.h"
@@ -51,6 +52,12 @@ struct HaloCudaCtx {
     // expired).  The host reads it after every stream wait; a set bit marks the context lost.
     uint32_t* error_word_host = nullptr;
     uint32_t* error_word_dev = nullptr;
+    // halo_cuda_malloc serves from a memory pool that never gives memory back to the driver while the context lives, on a
+    // stream of its own: an allocation costs microseconds, not a driver call.  `pooled` holds what came from the pool
+    // (shareable allocations come from cudaMalloc, which inter-process handles need).
+    cudaMemPool_t pool = nullptr;
+    cudaStream_t pool_stream = nullptr;
+    std::unordered_set<void*> pooled;
     // Two pinned host buffers the weight loader fills in turn, each cut into up to eight lanes (one per host thread), and the
     // event behind the last device copy out of each lane.
     void* staging[2] = {nullptr, nullptr};

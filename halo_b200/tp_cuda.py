@@ -36,7 +36,7 @@ class CudaTp:
         if self.world == 1 or self.peers is not None:
             return
         lib, ctx = self.be.lib, self.be.ctx
-        slots = self.be.allocate(2 * self.world * capacity * 8)
+        slots = self.be.allocate(2 * self.world * capacity * 8, shareable=True)
         words = self.be.allocate(64)
         self._peer_bufs = [slots, words]
         torch.cuda.synchronize(self.device)

@@ -143,8 +143,15 @@ int halo_cuda_device_count(int* count);
 int halo_cuda_ctx_create(int device, HaloCudaCtx** ctx);
 int halo_cuda_ctx_destroy(HaloCudaCtx* ctx);
 int halo_cuda_device_info(HaloCudaCtx* ctx, HaloCudaDeviceInfo* info);
-/* Device memory; zero != 0 clears it (Backend::allocate is zero-filled, backend.h:523). */
-int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int zero, void** ptr);
+/* Device memory.  The model allocates every activation buffer of a forward through Backend::allocate
+ * (src/models/qwen35.cpp:462-465, 542-579), so this is a sub-allocator: blocks come from a per-context pool that keeps
+ * freed memory, and cost microseconds.  flags: HALO_CUDA_MALLOC_ZERO clears the block (Backend::allocate is
+ * zero-filled, backend.h:523); HALO_CUDA_MALLOC_SHAREABLE takes the block from the driver instead, which
+ * halo_cuda_ipc_export needs.  The pointer is usable on every stream when the call returns.  halo_cuda_free waits
+ * for the device first, so a block that queued work still uses is never handed out again early. */
+#define HALO_CUDA_MALLOC_ZERO 1
+#define HALO_CUDA_MALLOC_SHAREABLE 2
+int halo_cuda_malloc(HaloCudaCtx* ctx, uint64_t bytes, int flags, void** ptr);
 int halo_cuda_free(HaloCudaCtx* ctx, void* ptr);
 int halo_cuda_stream_create(HaloCudaCtx* ctx, HaloCudaStream* stream);
 int halo_cuda_stream_destroy(HaloCudaCtx* ctx, HaloCudaStream stream);
