@@ -348,6 +348,57 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
     return out
 
 
+def fused_norm_leg(be, st, reps: int = 20, copies: int = 8):
+    """The matmul with the fused input norm (GemvArgs::norm_w) beside the plain matmul of the same shape: config 0 and the Q6_K
+    shape of config 1, one x row, `copies` distinct weight copies cycled (> L2), CUDA events on the launching stream."""
+    import numpy as np
+
+    from halo_b200 import backend as hb
+    from halo_b200 import capi, synth
+
+    lib, ctx = be.lib, be.ctx
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.halo_cuda_event_create(ctx, C.byref(e0))
+    lib.halo_cuda_event_create(ctx, C.byref(e1))
+    out = []
+    for name, t, n, k, variant in (("cfg0 q4_k", synth.Q4_K, N_ROWS, K_COLS, 0), ("cfg1 q6_k down", synth.Q6_K, 5120, 17408, capi.GEMV_MMA_R)):
+        w = synth.quant_weights(t, n, k, 0, 1)
+        bufs = []
+        for _ in range(copies):
+            b = be.import_host_readonly(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
+            if variant == capi.GEMV_MMA_R:
+                p = be.repack(st, t, hb.TensorRef.of(b), n, k)
+                st.wait()
+                b.free()
+                b = p
+            bufs.append(b)
+        xb = be.import_host_readonly(synth.activations(1, k, 0, 2))
+        nw = be.import_host_readonly(np.full(k, 1.25, np.float32))
+        yb = be.allocate(n * 4)
+        row = {"shape": name, "rows": n, "cols": k, "m": 1}
+        for key, fused in (("us_plain", False), ("us_fused_norm", True)):
+            args = [hb.GemvArgs(t, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, 1, variant) for b in bufs]
+            if fused:
+                for a in args:
+                    a.norm_w = hb.TensorRef.of(nw)
+            for a in args:
+                be.gemv(st, a)
+            st.wait()
+            lib.halo_cuda_event_record(ctx, e0, st.handle)
+            for _ in range(reps):
+                for a in args:
+                    be.gemv(st, a)
+            lib.halo_cuda_event_record(ctx, e1, st.handle)
+            st.wait()
+            ns = C.c_uint64()
+            lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+            row[key] = ns.value / 1e3 / (reps * copies)
+        out.append(row)
+        for b in bufs + [xb, nw, yb]:
+            b.free()
+    return out
+
+
 def loader_leg(be, st, rank: int, world: int, reps: int = 3):
     """File -> device: this rank's column share of the config-4 LM head (Q4_0, 151936 x 5120, 437.6 MB in all) brought from a GGUF
     file in the page cache into HBM by the loader (pinned double-buffered staging, repack on the device), beside the plain
@@ -591,13 +642,14 @@ def run_ours(args) -> None:
             sms = timed(split_pass, psteps) / psteps
             prefill["column_split"] = {"rows_per_gpu": n_split, "ms_per_call": sms, "tflops": flops / (sms * 1e-3) / 1e12, "scaling": "strong"}
 
-    sweep = shapes = loader = None
+    sweep = shapes = loader = fused_norm = None
     if not args.profile:
         for b in wbufs[1:] + ybufs[1:]:
             b.free()
         shapes = decode_shapes(be, st, rank, world, max(3, min(args.steps, 20)))
         sweep = tp_sweep(local_rank, rank, world, max(3, min(args.steps, 20)))
         loader = loader_leg(be, st, rank, world)
+        fused_norm = fused_norm_leg(be, st) if rank == 0 else None
     clocks = sampler.stop() if rank == 0 else None
 
     launches_per_step = COPIES
@@ -632,6 +684,7 @@ def run_ours(args) -> None:
         "decode_shapes": shapes,
         "tp_sweep": sweep,
         "loader": loader,
+        "fused_norm": fused_norm,
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -6,6 +6,7 @@
 #include <format>
 #include <limits>
 #include <string>
+#include <string_view>
 #include <vector>
 
 #include "halo/core/error.h"
@@ -224,6 +225,12 @@ public:
     void gemv(Stream& s, const GemvArgs& a) override {
         CudaStream& cs = stream_of(s, "MATMUL");
         const HaloCudaGemv g = gemv_struct(a, "MATMUL", false);
+        if (!a.norm_w.empty()) {
+            // the fused input norm: the library has it for one x row on the tensor-core skinny kernels and refuses the rest
+            const auto* nw = reinterpret_cast<const float*>(resolve(a.norm_w, mul_u64(a.cols, 4, "MATMUL", "norm_w"), Access::Read, "MATMUL", "norm_w"));
+            check(halo_cuda_gemv_normed(ctx_, &g, nw, a.norm_eps, cs.handle()));
+            return;
+        }
         check(halo_cuda_gemv(ctx_, &g, cs.handle()));
     }
 
@@ -364,7 +371,7 @@ private:
     }
 
     HaloCudaGemv gemv_struct(const GemvArgs& a, const char* op, bool y_optional) const {
-        HALO_CHECK(a.norm_w.empty(), ErrorCode::Unsupported, "{}: a fused norm (GemvArgs::norm_w) is Vulkan-only", op);
+        HALO_CHECK(a.norm_w.empty() || std::string_view(op) == "MATMUL", ErrorCode::Unsupported, "{}: a fused norm (GemvArgs::norm_w) is for MATMUL only", op);
         HALO_CHECK(a.gates.n_v == 0, ErrorCode::Unsupported, "{}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only", op);
         HaloCudaGemv g{};
         g.wtype = static_cast<std::uint32_t>(a.wtype);

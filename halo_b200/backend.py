@@ -90,7 +90,8 @@ class TensorRef:
 
 @dataclass
 class GemvArgs:
-    """GemvArgs (backend.h:283-314). norm_w / gates exist only to be rejected, as on the CPU backend."""
+    """GemvArgs (backend.h:283-314).  norm_w / norm_eps: the fused input norm, for one x row on the tensor-core skinny kernels and
+    refused everywhere else; gates exist only to be rejected, as on the CPU backend."""
     wtype: int = F32
     w: TensorRef = field(default_factory=TensorRef)
     x: TensorRef = field(default_factory=TensorRef)
@@ -100,6 +101,7 @@ class GemvArgs:
     n_vec: int = 1
     variant_id: int = 0
     norm_w: TensorRef = field(default_factory=TensorRef)
+    norm_eps: float = 1e-6
     allow_gemm: bool = False
     gates_n_v: int = 0
     #: cuda extension: the call may not touch context scratch (the statically partitioned kernels; what
@@ -281,8 +283,8 @@ class CudaBackend:
 
     # ---- ops ---------------------------------------------------------------------------------------
     def _gemv_struct(self, a: GemvArgs, op: str, y_optional: bool) -> capi.Gemv:
-        if not a.norm_w.empty():
-            raise HaloError(capi.E_UNSUPPORTED, f"{op}: a fused norm (GemvArgs::norm_w) is Vulkan-only")
+        if not a.norm_w.empty() and op != "MATMUL":
+            raise HaloError(capi.E_UNSUPPORTED, f"{op}: a fused norm (GemvArgs::norm_w) is for MATMUL only")
         if a.gates_n_v != 0:
             raise HaloError(capi.E_UNSUPPORTED, f"{op}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only")
         rb = C.c_uint64()
@@ -304,6 +306,10 @@ class CudaBackend:
 
     def gemv(self, s: Stream, a: GemvArgs) -> None:
         g = self._gemv_struct(a, "MATMUL", False)
+        if not a.norm_w.empty():
+            nw = self._resolve(a.norm_w, a.cols * 4, "norm_w", "MATMUL")
+            _check(self.lib.halo_cuda_gemv_normed(self.ctx, C.byref(g), nw, a.norm_eps, s.handle))
+            return
         _check(self.lib.halo_cuda_gemv(self.ctx, C.byref(g), s.handle))
 
     def resolve_variant(self, a: GemvArgs) -> int:

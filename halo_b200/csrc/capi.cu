@@ -583,6 +583,30 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
     return run_gemv(ctx, c, args->variant_id, static_cast<cudaStream_t>(stream));
 }
 
+int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const float* norm_w, float norm_eps, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    GemvCall c{};
+    if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
+    if (args->variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
+        return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
+    if (norm_w == nullptr) return fail(HALO_CUDA_E_API, "MATMUL: fused input norm without norm_w");
+    if (reinterpret_cast<uintptr_t>(norm_w) % 16 != 0 || reinterpret_cast<uintptr_t>(c.x) % 16 != 0)
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: fused input norm needs 16-byte-aligned x and norm_w");
+    if (!(norm_eps >= 0.0f)) return fail(HALO_CUDA_E_KERNEL, "MATMUL: norm_eps must be a non-negative number");
+    const uint64_t nbytes = uint64_t{c.cols} * 4;
+    if (ranges_overlap(c.y, uint64_t{c.rows} * 4, norm_w, nbytes)) return fail(HALO_CUDA_E_KERNEL, "MATMUL: output y overlaps operand norm_w");
+    // the same restrictions as the reference's fused norm (backend.h:292-298): one x row, and only where the kernel has it
+    if (c.n_vec != 1) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row, not %u", c.n_vec);
+    if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm belongs to the kernels that use context scratch");
+    const uint32_t v = resolve_variant(ctx, c, args->variant_id);
+    const bool has_it = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c));
+    if (!has_it) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7) have the fused input norm");
+    if (c.rows == 0) return 0;
+    c.norm_w = norm_w;
+    c.norm_eps = norm_eps;
+    return run_gemv(ctx, c, v, static_cast<cudaStream_t>(stream));
+}
+
 int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan) {
     if (plan == nullptr) return fail(HALO_CUDA_E_API, "null argument");
     const bool grouped = repacked_row_bytes(wtype, 256) != 0;

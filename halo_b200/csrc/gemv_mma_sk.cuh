@@ -97,12 +97,13 @@ struct SkLayout {
 };
 
 // ---- resident x -------------------------------------------------------------------------------------------------------------------
-template <class F, int NTOK, int NS, int KS, bool PRE>
+// NORM (single-row calls only): x is the raw row; the kernel normalises it by its rms and norm_w while converting it.
+template <class F, int NTOK, int NS, int KS, bool PRE, bool NORM = false>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
                         float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, float* __restrict__ partials,
                         uint32_t* __restrict__ counters, uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage,
-                        const __grid_constant__ PeerPush peer) {
+                        const __grid_constant__ PeerPush peer, const float* __restrict__ norm_w, float norm_eps) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     using L = SkLayout<F, NTOK, NS, KS>;
@@ -161,10 +162,17 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
             lost = true;
         }
     } else {
-        // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
-        for (uint32_t tk = 0; tk < NTOK; ++tk)
-            stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), nb, NTOK, tk,
-                          warp, kWarps, lane, F::kXLaneBytes == 8);
+        if constexpr (NORM) {
+            // fused input norm (single row): the row's rms first (one more block barrier), then the conversion below with
+            // every element multiplied by it and by norm_w
+            const float inv = block_inv_rms<kWarps>(x, nb * 256u, norm_eps, reinterpret_cast<float*>(smem + kOffRed), tid);
+            stage_row_rec<true>(smem + kOffData, x, nb, NTOK, 0, warp, kWarps, lane, F::kXLaneBytes == 8, norm_w, inv);
+        } else {
+            // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
+            for (uint32_t tk = 0; tk < NTOK; ++tk)
+                stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), nb, NTOK, tk,
+                              warp, kWarps, lane, F::kXLaneBytes == 8);
+        }
         __syncthreads();
     }
 

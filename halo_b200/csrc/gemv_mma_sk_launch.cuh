@@ -117,8 +117,25 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         }
         cudaLaunchAttribute attr[1];
         const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
+        if (c.norm_w != nullptr) {
+            if constexpr (NTOK == 1) {
+                static bool norm_attr_set = false;
+                if (!norm_attr_set) {
+                    HC_CUDA(cudaFuncSetAttribute(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kSmemBudget)));
+                    norm_attr_set = true;
+                }
+                HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE, true>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows,
+                                           g.nb, static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage,
+                                           peer_push(c, tok0), c.norm_w, c.norm_eps));
+                return 0;
+            } else {
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
+            }
+        }
         HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb,
-                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, peer_push(c, tok0)));
+                                   static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, peer_push(c, tok0),
+                                   static_cast<const float*>(nullptr), 0.0f));
         return 0;
     }
 }
@@ -129,6 +146,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     using L = SkLayout<F, NTOK, NS, KS>;
     constexpr uint32_t kXSlot = KS * L::kRec;
     static_assert(L::kOffData + 2 * kXSlot <= kSmemBudget, "two columns of x must fit next to the ring");
+    if (c.norm_w != nullptr) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL with a fused input norm: %u columns of x do not fit in shared memory", c.cols);
     const uint32_t xs_cols = std::min<uint32_t>(kMaxXSlots / 2, (kSmemBudget - L::kOffData) / kXSlot / 2);
     const uint32_t smem_bytes = L::kOffData + 2 * xs_cols * kXSlot;
     static bool attr_set = false;

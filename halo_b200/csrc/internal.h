@@ -82,6 +82,8 @@ struct GemvCall {
     uint64_t w_stride, x_stride, y_stride;  // bytes
     uint64_t row_bytes;
     const HaloCudaPeerReduce* peer = nullptr;  // row-split tensor parallelism: push the result rows to the peers instead of storing y
+    const float* norm_w = nullptr;             // fused input norm (single-row calls): x is the raw row, the kernel multiplies by rms and norm_w
+    float norm_eps = 0.0f;
 };
 int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* out);
 uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested);

@@ -102,10 +102,14 @@ __device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v
 
 /// Converts super-blocks [0, n_sb) of one x row into records starting at `area`: warp w of `n_warps` takes super-blocks
 /// w, w + n_warps, ..., four at a time so that their loads overlap.  The arithmetic does not depend on who calls it.
+/// NORM: the row is normalised on the way, element i becomes (x[i] * inv) * norm_w[i] -- the arithmetic of the CPU backend's
+/// rms_norm (backends/cpu/ops_basic.cpp:28-30) with `inv` = 1 / sqrt(mean of squares + eps) supplied by the caller.
+template <bool NORM = false>
 __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t warp,
-                                              uint32_t n_warps, uint32_t lane, bool split_halves) {
+                                              uint32_t n_warps, uint32_t lane, bool split_halves, const float* norm_w = nullptr, float inv = 1.0f) {
     constexpr uint32_t kAhead = 4;
     const float4* xr = reinterpret_cast<const float4*>(xrow);
+    const float4* wr = reinterpret_cast<const float4*>(norm_w);
     for (uint32_t sb0 = warp; sb0 < n_sb; sb0 += kAhead * n_warps) {
         float4 v[kAhead][2];
 #pragma unroll
@@ -113,12 +117,61 @@ __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, 
             const uint32_t sb = sb0 + j * n_warps;
             if (sb < n_sb) v[j][0] = xr[sb * 64u + lane], v[j][1] = xr[sb * 64u + 32u + lane];
         }
+        if constexpr (NORM) {
+#pragma unroll
+            for (uint32_t j = 0; j < kAhead; ++j) {
+                const uint32_t sb = sb0 + j * n_warps;
+                if (sb < n_sb) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float4 w = wr[sb * 64u + h * 32u + lane];
+                        v[j][h].x = __fmul_rn(__fmul_rn(v[j][h].x, inv), w.x);
+                        v[j][h].y = __fmul_rn(__fmul_rn(v[j][h].y, inv), w.y);
+                        v[j][h].z = __fmul_rn(__fmul_rn(v[j][h].z, inv), w.z);
+                        v[j][h].w = __fmul_rn(__fmul_rn(v[j][h].w, inv), w.w);
+                    }
+                }
+            }
+        }
 #pragma unroll
         for (uint32_t j = 0; j < kAhead; ++j) {
             const uint32_t sb = sb0 + j * n_warps;
             if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane, split_halves);
         }
     }
+}
+
+/// 1 / sqrt(mean of squares + eps) of a row of n floats (n a multiple of 4, 16-byte aligned), computed by the whole block
+/// in a fixed order: thread-strided partial sums, a shuffle tree per warp, the warps' sums added in warp order by every
+/// thread.  `red` is shared memory for one float per warp.  Contains one block barrier.
+template <uint32_t kWarps>
+__device__ __forceinline__ float block_inv_rms(const float* xrow, uint32_t n, float eps, float* red, uint32_t tid) {
+    const float4* xr = reinterpret_cast<const float4*>(xrow);
+    float s = 0.0f;
+    constexpr uint32_t kAhead = 4, kStride = kWarps * 32u;  // four loads in flight per thread; the additions stay in index order
+    for (uint32_t i0 = tid; i0 < n / 4u; i0 += kAhead * kStride) {
+        float4 v[kAhead];
+#pragma unroll
+        for (uint32_t j = 0; j < kAhead; ++j)
+            if (i0 + j * kStride < n / 4u) v[j] = xr[i0 + j * kStride];
+#pragma unroll
+        for (uint32_t j = 0; j < kAhead; ++j) {
+            if (i0 + j * kStride < n / 4u) {
+                s = fmaf(v[j].x, v[j].x, s);
+                s = fmaf(v[j].y, v[j].y, s);
+                s = fmaf(v[j].z, v[j].z, s);
+                s = fmaf(v[j].w, v[j].w, s);
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t d = 16; d != 0; d >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, d);
+    if ((tid & 31u) == 0) red[tid >> 5] = s;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (uint32_t w = 0; w < kWarps; ++w) total += red[w];
+    return 1.0f / sqrtf(total / static_cast<float>(n) + eps);
 }
 
 /// Bytes of global scratch stage_x_rec_kernel fills: the records of all super-blocks.

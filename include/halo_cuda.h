@@ -210,6 +210,14 @@ int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t s
 
 /* ---- the operators ------------------------------------------------------------------------------ */
 int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);
+/* MATMUL with the fused input norm of GemvArgs::norm_w / norm_eps (backend.h:292-298): y = W (rms_norm(x) * norm_w), `args->x`
+ * being the RAW row and norm_w `cols` fp32 (device, 16-byte aligned like x).  Element i of the normalised row is
+ * (x[i] * inv) * norm_w[i] with inv = 1 / sqrt(mean(x^2) + norm_eps), the arithmetic of the CPU backend's rms_norm
+ * (backends/cpu/ops_basic.cpp:28-30); the mean is summed in the kernel's own fixed order, so the result differs from
+ * rms_norm followed by halo_cuda_gemv only through that order -- the latitude the reference gives its own fused norm.
+ * As there: one x row only, and only the kernels that have it (variants 3 and 7 with x resident in shared memory);
+ * every other case returns HALO_CUDA_E_UNSUPPORTED, never a product over the raw row. */
+int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const float* norm_w, float norm_eps, HaloCudaStream stream);
 int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);
 int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaStream stream);
 

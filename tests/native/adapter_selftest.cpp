@@ -303,6 +303,48 @@ void test_load_mat(Pair& p, Report& r) {
     halo_gguf_close(file);
 }
 
+/// The fused input norm through the adapter: GemvArgs::norm_w on the cuda backend against the CPU backend's own rms_norm followed by
+/// its own gemv (the CPU backend refuses the fused form, src/backend/cpu_backend.cpp:341-342).
+void test_fused_norm(Pair& p, Report& r) {
+    const std::uint32_t N = 90, K = 2560;
+    const auto w = random_weights(DType::Q4_K, N, K, 61);
+    auto x = random_floats(K, 62);
+    for (float& v : x) v *= 2.5f;
+    auto nw = random_floats(K, 63);
+    for (float& v : nw) v = 1.0f + 0.1f * v;
+    // CPU: rms_norm into a scratch row, then gemv
+    const auto cw = p.cpu->import_host_readonly(w);
+    const auto cx = p.cpu->import_host_readonly(cbytes(x.data(), x.size() * 4));
+    const auto cn = p.cpu->import_host_readonly(cbytes(nw.data(), nw.size() * 4));
+    const auto cxn = p.cpu->allocate(K * 4, hb::Tier::Host);
+    const auto cy = p.cpu->allocate(N * 4, hb::Tier::Host);
+    p.cpu->rms_norm(*p.cst, {hb::TensorRef::of(*cx), hb::TensorRef::of(*cn), hb::TensorRef::of(*cxn), 1, K, 1e-6f, {}});
+    p.cpu->gemv(*p.cst, {DType::Q4_K, hb::TensorRef::of(*cw), hb::TensorRef::of(*cxn), hb::TensorRef::of(*cy), N, K, 1, {}});
+    std::vector<float> yc(N), yg(N);
+    p.cpu->download(*p.cst, hb::TensorRef::of(*cy), wbytes(yc.data(), yc.size() * 4));
+    p.cst->wait();
+    // cuda: one call
+    const auto gw = p.gpu->import_host_readonly(w);
+    const auto gx = p.gpu->import_host_readonly(cbytes(x.data(), x.size() * 4));
+    const auto gn = p.gpu->import_host_readonly(cbytes(nw.data(), nw.size() * 4));
+    const auto gy = p.gpu->allocate(N * 4, hb::Tier::Vram);
+    hb::GemvArgs a{DType::Q4_K, hb::TensorRef::of(*gw), hb::TensorRef::of(*gx), hb::TensorRef::of(*gy), N, K, 1, {}};
+    a.norm_w = hb::TensorRef::of(*gn);
+    a.norm_eps = 1e-6f;
+    p.gpu->gemv(*p.gst, a);
+    p.gpu->download(*p.gst, hb::TensorRef::of(*gy), wbytes(yg.data(), yg.size() * 4));
+    p.gst->wait();
+    float maxref = 0, maxerr = 0;
+    for (std::size_t i = 0; i < yc.size(); ++i) {
+        maxref = std::max(maxref, std::fabs(yc[i]));
+        maxerr = std::max(maxerr, std::fabs(yc[i] - yg[i]));
+    }
+    r.expect(maxerr <= 1e-5f * maxref, std::format("fused input norm equals the CPU backend's rms_norm + gemv to rounding: {} vs {}", maxerr, maxref));
+    a.n_vec = 1;
+    a.kernel = {1};
+    r.expect(code_of([&] { p.gpu->gemv(*p.gst, a); }) == static_cast<int>(halo::ErrorCode::Unsupported), "fused norm on a kernel without it: Error(Unsupported)");
+}
+
 void test_validation_parity(Pair& p, Report& r) {
     const std::uint32_t N = 8, K = 64, T = 2;
     const auto w = random_weights(DType::Q8_0, N, K, 3);
@@ -480,6 +522,7 @@ extern "C" int halo_adapter_selftest(char* report, std::size_t len) {
         test_registry(p, r);
         test_gemv_repacked(p, r);
         test_load_mat(p, r);
+        test_fused_norm(p, r);
         test_gemv_bitwise(p, r);
         test_validation_parity(p, r);
         test_lm_head(p, r);
