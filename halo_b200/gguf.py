@@ -205,3 +205,16 @@ def write_gguf(path: str | Path, tensors: list[tuple[str, int, int, int, np.ndar
             a = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
             out.write(a.data)
             pos = off + a.size
+
+
+def host_share(f: GgufFile, t: TensorInfo, split: int = capi.SPLIT_NONE, rank: int = 0, world: int = 1) -> tuple[DeviceMatrix, np.ndarray]:
+    """One rank's share of matrix `t` as host bytes [rows, local row bytes] (a view into the mapping for whole rows, a copy for a
+    K range), with its extents: what halo_cuda_upload_matrix would bring to the device.  For tools and the CPU tests."""
+    m = matrix_share(t.type, t.ne[1], t.ne[0], split, rank, world)
+    src_row = t.n_bytes // t.ne[1] if t.ne[1] else 0
+    data = f.tensor_data(t).reshape(t.ne[1], src_row) if t.ne[1] else np.empty((0, 0), np.uint8)
+    if m.rows == 0 or m.cols == 0:
+        return m, np.empty((m.rows, 0), np.uint8)
+    local = m.row_stride
+    byte0 = (m.k0 * src_row) // t.ne[0]
+    return m, data[m.row0:m.row0 + m.rows, byte0:byte0 + local]

@@ -97,6 +97,65 @@ def _worker(rank: int, world: int, port: int, q):
     dist.destroy_process_group()
 
 
+def _file_worker(rank: int, world: int, port: int, path: str, q):
+    """Each rank cuts its own shares out of the GGUF file with the loader's share arithmetic (no device needed)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from halo_b200 import capi, gguf
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    chk = oracle.Oracle()
+    f = gguf.GgufFile.open(path)
+    out = {}
+    for info in f.tensors():
+        rows, cols = info.ne[1], info.ne[0]
+        x = synth.activations(2, cols, 31, 2)
+        mc, wc = gguf.host_share(f, info, capi.SPLIT_COLUMN, rank, world)
+        y_col = torch.from_numpy(chk.gemv(info.type, np.ascontiguousarray(wc), x, mc.rows, cols, threads=1))
+        sizes = [gguf.matrix_share(info.type, rows, cols, capi.SPLIT_COLUMN, r, world).rows for r in range(world)]
+        gathered = [torch.zeros((2, n), dtype=torch.float32) for n in sizes]
+        gathered[rank] = y_col
+        for r in range(world):  # shares may differ in size (41 rows over 2 ranks), so every rank broadcasts its own
+            dist.broadcast(gathered[r], r)
+        mr, wr = gguf.host_share(f, info, capi.SPLIT_ROW, rank, world)
+        y_row = torch.from_numpy(chk.gemv(info.type, np.ascontiguousarray(wr), np.ascontiguousarray(x[:, mr.k0:mr.k0 + mr.cols]), rows, mr.cols, threads=1))
+        dist.all_reduce(y_row)
+        out[info.name] = (torch.cat(gathered, dim=1).numpy(), y_row.numpy())
+    q.put((rank, out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_load_their_shares_from_a_gguf_file(oracle_c, tmp_path):
+    import torch.multiprocessing as mp
+
+    from halo_b200 import gguf
+    shapes = {"blk.0.ffn_up.weight": (synth.Q4_K, 41, 1280), "blk.0.ffn_down.weight": (synth.Q6_K, 24, 1792), "blk.0.attn_q.weight": (synth.Q8_0, 30, 416),
+              "output.weight": (synth.Q4_0, 17, 800)}
+    raws = {n: synth.quant_weights(t, r, c, 31, 1 + i) for i, (n, (t, r, c)) in enumerate(shapes.items())}
+    path = tmp_path / "tp.gguf"
+    gguf.write_gguf(path, [(n, t, r, c, raws[n]) for n, (t, r, c) in shapes.items()], {"general.architecture": "qwen35"})
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_file_worker, args=(r, 2, port, str(path), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for name, (t, rows, cols) in shapes.items():
+        full = oracle_c.gemv(t, raws[name], synth.activations(2, cols, 31, 2), rows, cols)
+        for _, out in results:
+            y_col, y_row = out[name]
+            assert np.array_equal(bits(y_col), bits(full)), name                       # column shares: bitwise
+            assert np.max(np.abs(y_row - full)) <= 1e-5 * np.max(np.abs(full)), name   # row shares + all-reduce: bounded
+
+
 def test_two_gloo_ranks_column_and_row_split(oracle_c):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
