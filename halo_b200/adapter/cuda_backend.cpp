@@ -225,6 +225,14 @@ public:
     void gemv(Stream& s, const GemvArgs& a) override {
         CudaStream& cs = stream_of(s, "MATMUL");
         const HaloCudaGemv g = gemv_struct(a, "MATMUL", false);
+        if (a.gates.n_v != 0) {
+            // the GDN gates epilogue: the library has it for F32 / Q8_0 weights on the fp32 kernels and refuses the rest
+            const std::uint64_t nb = mul_u64(a.gates.n_v, 4, "MATMUL", "gates");
+            const auto* db = reinterpret_cast<const float*>(resolve(a.gates.dt_bias, nb, Access::Read, "MATMUL", "gates.dt_bias"));
+            const auto* ga = reinterpret_cast<const float*>(resolve(a.gates.a, nb, Access::Read, "MATMUL", "gates.a"));
+            check(halo_cuda_gemv_gated(ctx_, &g, db, ga, a.gates.n_v, cs.handle()));
+            return;
+        }
         if (!a.norm_w.empty()) {
             // the fused input norm: the library has it for one x row on the tensor-core skinny kernels and refuses the rest
             const auto* nw = reinterpret_cast<const float*>(resolve(a.norm_w, mul_u64(a.cols, 4, "MATMUL", "norm_w"), Access::Read, "MATMUL", "norm_w"));
@@ -372,7 +380,8 @@ private:
 
     HaloCudaGemv gemv_struct(const GemvArgs& a, const char* op, bool y_optional) const {
         HALO_CHECK(a.norm_w.empty() || std::string_view(op) == "MATMUL", ErrorCode::Unsupported, "{}: a fused norm (GemvArgs::norm_w) is for MATMUL only", op);
-        HALO_CHECK(a.gates.n_v == 0, ErrorCode::Unsupported, "{}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only", op);
+        HALO_CHECK(a.gates.n_v == 0 || (std::string_view(op) == "MATMUL" && a.norm_w.empty()), ErrorCode::Unsupported,
+                   "{}: the GDN gates epilogue (GemvArgs::gates) is for MATMUL without a fused norm", op);
         HaloCudaGemv g{};
         g.wtype = static_cast<std::uint32_t>(a.wtype);
         g.variant_id = a.kernel.variant_id != 0 ? a.kernel.variant_id : options_.default_gemv_variant;

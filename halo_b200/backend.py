@@ -91,7 +91,7 @@ class TensorRef:
 @dataclass
 class GemvArgs:
     """GemvArgs (backend.h:283-314).  norm_w / norm_eps: the fused input norm, for one x row on the tensor-core skinny kernels and
-    refused everywhere else; gates exist only to be rejected, as on the CPU backend."""
+    refused everywhere else; gates_*: the GDN gates epilogue, for F32 / Q8_0 weights on the fp32 kernels and refused everywhere else."""
     wtype: int = F32
     w: TensorRef = field(default_factory=TensorRef)
     x: TensorRef = field(default_factory=TensorRef)
@@ -104,6 +104,8 @@ class GemvArgs:
     norm_eps: float = 1e-6
     allow_gemm: bool = False
     gates_n_v: int = 0
+    gates_dt_bias: TensorRef = field(default_factory=TensorRef)
+    gates_a: TensorRef = field(default_factory=TensorRef)
     #: cuda extension: the call may not touch context scratch (the statically partitioned kernels; what
     #: halo_cuda_lm_head_noalloc computes)
     no_scratch: bool = False
@@ -285,8 +287,8 @@ class CudaBackend:
     def _gemv_struct(self, a: GemvArgs, op: str, y_optional: bool) -> capi.Gemv:
         if not a.norm_w.empty() and op != "MATMUL":
             raise HaloError(capi.E_UNSUPPORTED, f"{op}: a fused norm (GemvArgs::norm_w) is for MATMUL only")
-        if a.gates_n_v != 0:
-            raise HaloError(capi.E_UNSUPPORTED, f"{op}: the GDN gates epilogue (GemvArgs::gates) is Vulkan-only")
+        if a.gates_n_v != 0 and (op != "MATMUL" or not a.norm_w.empty()):
+            raise HaloError(capi.E_UNSUPPORTED, f"{op}: the GDN gates epilogue (GemvArgs::gates) is for MATMUL without a fused norm")
         rb = C.c_uint64()
         if a.variant_id == capi.GEMV_MMA_R:  # W is in the repacked row layout
             _check(self.lib.halo_cuda_repacked_row_bytes(a.wtype, a.cols, C.byref(rb)))
@@ -306,6 +308,11 @@ class CudaBackend:
 
     def gemv(self, s: Stream, a: GemvArgs) -> None:
         g = self._gemv_struct(a, "MATMUL", False)
+        if a.gates_n_v != 0:
+            db = self._resolve(a.gates_dt_bias, a.gates_n_v * 4, "gates.dt_bias", "MATMUL")
+            ga = self._resolve(a.gates_a, a.gates_n_v * 4, "gates.a", "MATMUL")
+            _check(self.lib.halo_cuda_gemv_gated(self.ctx, C.byref(g), db, ga, a.gates_n_v, s.handle))
+            return
         if not a.norm_w.empty():
             nw = self._resolve(a.norm_w, a.cols * 4, "norm_w", "MATMUL")
             _check(self.lib.halo_cuda_gemv_normed(self.ctx, C.byref(g), nw, a.norm_eps, s.handle))

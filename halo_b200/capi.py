@@ -109,6 +109,7 @@ SYMBOLS = {
     "halo_cuda_last_error": (C.c_size_t, [C.c_char_p, C.c_size_t]),
     "halo_cuda_gemv": (C.c_int, [_P, C.POINTER(Gemv), _P]),
     "halo_cuda_gemv_normed": (C.c_int, [_P, C.POINTER(Gemv), _P, C.c_float, _P]),
+    "halo_cuda_gemv_gated": (C.c_int, [_P, C.POINTER(Gemv), _P, _P, C.c_uint32, _P]),
     "halo_cuda_lm_head": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_get_rows": (C.c_int, [_P, C.POINTER(GetRows), _P]),
     "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),

@@ -607,6 +607,32 @@ int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const floa
     return run_gemv(ctx, c, v, static_cast<cudaStream_t>(stream));
 }
 
+int halo_cuda_gemv_gated(HaloCudaCtx* ctx, const HaloCudaGemv* args, const float* dt_bias, const float* a, uint32_t n_v, HaloCudaStream stream) {
+    if (int rc = enter(ctx)) return rc;
+    GemvCall c{};
+    if (int rc = validate_gemv(args, "MATMUL", false, &c)) return rc;
+    if (args->variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
+        return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", args->variant_id);
+    if (n_v == 0 || dt_bias == nullptr || a == nullptr) return fail(HALO_CUDA_E_API, "MATMUL: gates epilogue without n_v, dt_bias or a");
+    if (reinterpret_cast<uintptr_t>(dt_bias) % 4 != 0 || reinterpret_cast<uintptr_t>(a) % 4 != 0)
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: dt_bias and a must be 4-byte aligned");
+    if (c.rows != 2ull * n_v) return fail(HALO_CUDA_E_KERNEL, "MATMUL: the gates epilogue needs rows == 2 * n_v (beta rows, then alpha rows), got %u rows for n_v = %u", c.rows, n_v);
+    const uint64_t y_bytes = c.n_vec == 0 ? 0 : (uint64_t{c.n_vec} - 1) * c.y_stride + uint64_t{c.rows} * 4;
+    if (ranges_overlap(c.y, y_bytes, dt_bias, uint64_t{n_v} * 4) || ranges_overlap(c.y, y_bytes, a, uint64_t{n_v} * 4))
+        return fail(HALO_CUDA_E_KERNEL, "MATMUL: output y overlaps operand dt_bias or a");
+    // as in the reference (backend.h:304-309): F32 / Q8_0 weights only, and only the kernels that have the epilogue
+    if (c.wtype != HALO_CUDA_T_F32 && c.wtype != HALO_CUDA_T_Q8_0)
+        return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the gates epilogue takes F32 or Q8_0 weights, not type id %u", c.wtype);
+    const uint32_t v = resolve_variant(ctx, c, args->variant_id);
+    if (v != HALO_CUDA_GEMV_EXACT8 && !(v == HALO_CUDA_GEMV_WARP_F32 && gemv_warp_f32_supports(c)))
+        return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the fp32 variants (1, 2) have the gates epilogue");
+    if (c.n_vec == 0) return 0;
+    c.gate_dt_bias = dt_bias;
+    c.gate_a = a;
+    c.gate_n_v = n_v;
+    return run_gemv(ctx, c, v, static_cast<cudaStream_t>(stream));
+}
+
 int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan) {
     if (plan == nullptr) return fail(HALO_CUDA_E_API, "null argument");
     const bool grouped = repacked_row_bytes(wtype, 256) != 0;

@@ -21,7 +21,8 @@ template <uint32_t WT>
 __global__ void __launch_bounds__(256) gemv_exact8_kernel(const uint8_t* __restrict__ w, uint64_t w_stride,
                                                           const float* __restrict__ x, uint64_t x_stride,
                                                           float* __restrict__ y, uint64_t y_stride, uint32_t rows,
-                                                          uint32_t cols, uint32_t n_vec) {
+                                                          uint32_t cols, uint32_t n_vec, const float* __restrict__ gate_dt_bias,
+                                                          const float* __restrict__ gate_a, uint32_t gate_n_v) {
     const uint32_t lane8 = threadIdx.x & 7u;
     const uint32_t n = blockIdx.x * kExactRowsPerBlock + (threadIdx.x >> 3);
     const uint32_t t0 = blockIdx.y * kExactTokens;
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(256) gemv_exact8_kernel(const uint8_t* __restr
         for (uint32_t i = k8; i < cols; ++i) tail = __fadd_rn(tail, __fmul_rn(xr[t][i], weight_elem<WT>(row, i)));
         if (lane8 == 0 && n < rows && t0 + t < n_vec) {
             float* yr = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{t0 + t} * y_stride);
-            yr[n] = __fadd_rn(a, tail);
+            yr[n] = gated_value(__fadd_rn(a, tail), n, gate_n_v, gate_dt_bias, gate_a);
         }
     }
 }
@@ -177,7 +178,8 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_stage2(const ArgPart* _
 template <uint32_t WT>
 int launch_exact_t(const GemvCall& c, cudaStream_t s) {
     const dim3 grid((c.rows + kExactRowsPerBlock - 1) / kExactRowsPerBlock, (c.n_vec + kExactTokens - 1) / kExactTokens);
-    gemv_exact8_kernel<WT><<<grid, 256, 0, s>>>(c.w, c.w_stride, c.x, c.x_stride, c.y, c.y_stride, c.rows, c.cols, c.n_vec);
+    gemv_exact8_kernel<WT><<<grid, 256, 0, s>>>(c.w, c.w_stride, c.x, c.x_stride, c.y, c.y_stride, c.rows, c.cols, c.n_vec, c.gate_dt_bias,
+                                                c.gate_a, c.gate_n_v);
     HC_CUDA(cudaGetLastError());
     return 0;
 }

@@ -179,7 +179,8 @@ template <uint32_t WT, int MT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemv_warp_kernel(const uint8_t* __restrict__ w, uint64_t w_stride,
                                                                        const float* __restrict__ x, uint64_t x_stride,
                                                                        float* __restrict__ y, uint64_t y_stride, uint32_t rows,
-                                                                       uint32_t cols, uint32_t n_vec) {
+                                                                       uint32_t cols, uint32_t n_vec, const float* __restrict__ gate_dt_bias,
+                                                                       const float* __restrict__ gate_a, uint32_t gate_n_v) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (n >= rows) return;  // whole warps leave together
@@ -206,7 +207,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemv_warp_kernel(const ui
         float a = acc[t];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, off);
-        if (lane == 0 && t0 + t < n_vec) reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{t0 + t} * y_stride)[n] = a;
+        if (lane == 0 && t0 + t < n_vec)
+            reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(y) + uint64_t{t0 + t} * y_stride)[n] = gated_value(a, n, gate_n_v, gate_dt_bias, gate_a);
     }
 }
 
@@ -227,17 +229,19 @@ int launch_t(const GemvCall& c, cudaStream_t s) {
         if (tiles > 65535u) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: n_vec %u exceeds the launch limit", c.n_vec);
         const GemvCall d = offset(t);
         gemv_warp_kernel<WT, 4><<<dim3(gx, tiles), kWarpsPerBlock * 32, 0, s>>>(d.w, d.w_stride, d.x, d.x_stride, d.y, d.y_stride, d.rows,
-                                                                                d.cols, tiles * 4);
+                                                                                d.cols, tiles * 4, d.gate_dt_bias, d.gate_a, d.gate_n_v);
         t += tiles * 4;
     }
     if (c.n_vec - t >= 2) {
         const GemvCall d = offset(t);
-        gemv_warp_kernel<WT, 2><<<dim3(gx, 1), kWarpsPerBlock * 32, 0, s>>>(d.w, d.w_stride, d.x, d.x_stride, d.y, d.y_stride, d.rows, d.cols, 2);
+        gemv_warp_kernel<WT, 2><<<dim3(gx, 1), kWarpsPerBlock * 32, 0, s>>>(d.w, d.w_stride, d.x, d.x_stride, d.y, d.y_stride, d.rows, d.cols, 2,
+                                                                            d.gate_dt_bias, d.gate_a, d.gate_n_v);
         t += 2;
     }
     if (c.n_vec - t >= 1) {
         const GemvCall d = offset(t);
-        gemv_warp_kernel<WT, 1><<<dim3(gx, 1), kWarpsPerBlock * 32, 0, s>>>(d.w, d.w_stride, d.x, d.x_stride, d.y, d.y_stride, d.rows, d.cols, 1);
+        gemv_warp_kernel<WT, 1><<<dim3(gx, 1), kWarpsPerBlock * 32, 0, s>>>(d.w, d.w_stride, d.x, d.x_stride, d.y, d.y_stride, d.rows, d.cols, 1,
+                                                                            d.gate_dt_bias, d.gate_a, d.gate_n_v);
     }
     HC_CUDA(cudaGetLastError());
     return 0;

@@ -84,9 +84,25 @@ struct GemvCall {
     const HaloCudaPeerReduce* peer = nullptr;  // row-split tensor parallelism: push the result rows to the peers instead of storing y
     const float* norm_w = nullptr;             // fused input norm (single-row calls): x is the raw row, the kernel multiplies by rms and norm_w
     float norm_eps = 0.0f;
+    // GDN gates epilogue (GemvArgs::gates): rows == 2 * n_v; row r < n_v stores sigmoid(y), row n_v + j stores
+    // a[j] * softplus(y + dt_bias[j]) instead of y
+    const float* gate_dt_bias = nullptr;
+    const float* gate_a = nullptr;
+    uint32_t gate_n_v = 0;
 };
 int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* out);
 uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested);
+
+/// What a kernel stores for row `n` of a matmul with the GDN gates epilogue (n_v != 0), else y unchanged: the CPU backend's
+/// gdn_gates (beta_out = sigmoid(beta); g_out = a * softplus(alpha + dt_bias); backends/cpu/kernel_common.h:31-33) applied
+/// to the two row halves.  expf / log1pf are the device's (a few ulp from the host's).
+__device__ __forceinline__ float gated_value(float y, uint32_t n, uint32_t n_v, const float* __restrict__ dt_bias, const float* __restrict__ a) {
+    if (n_v == 0) return y;
+    if (n < n_v) return 1.0f / (1.0f + expf(-y));
+    const uint32_t j = n - n_v;
+    const float t = y + dt_bias[j];
+    return a[j] * (t > 20.0f ? t : log1pf(expf(t)));
+}
 
 // kernel launchers (one per translation unit); each returns a status
 int launch_gemv_exact8(const GemvCall& c, cudaStream_t s);

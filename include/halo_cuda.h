@@ -218,6 +218,12 @@ int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream st
  * As there: one x row only, and only the kernels that have it (variants 3 and 7 with x resident in shared memory);
  * every other case returns HALO_CUDA_E_UNSUPPORTED, never a product over the raw row. */
 int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const float* norm_w, float norm_eps, HaloCudaStream stream);
+/* MATMUL with the GDN gates epilogue of GemvArgs::gates (backend.h:299-313): the matmul over a model's fused beta|alpha rows
+ * (rows == 2 * n_v, beta rows first) stores, instead of y, sigmoid(y) for row r < n_v and a[j] * softplus(y + dt_bias[j]) for
+ * row n_v + j -- the matmul followed by the CPU backend's gdn_gates on the two row halves (backend.h:316-323), with the
+ * device's expf / log1pf (a few ulp from the host's).  dt_bias, a: n_v fp32 (device).  As in the reference: F32 or Q8_0
+ * weights only, on the fp32 variants (1, 2); every other case returns HALO_CUDA_E_UNSUPPORTED, never plain y. */
+int halo_cuda_gemv_gated(HaloCudaCtx* ctx, const HaloCudaGemv* args, const float* dt_bias, const float* a, uint32_t n_v, HaloCudaStream stream);
 int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* args, HaloCudaStream stream);
 int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaStream stream);
 

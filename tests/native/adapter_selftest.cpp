@@ -374,7 +374,7 @@ void test_validation_parity(Pair& p, Report& r) {
         {"view too small", [](hb::GemvArgs& a, Built&) { a.y.bytes = 16; }},
         {"misaligned fp32 operand", [](hb::GemvArgs& a, Built&) { a.x = a.x.shifted(2); a.n_vec = 1; }},
         {"fused norm refused", [](hb::GemvArgs& a, Built&) { a.norm_w = a.x; }},
-        {"gates epilogue refused", [](hb::GemvArgs& a, Built&) { a.gates.n_v = 4; }},
+        {"gates epilogue next to a fused norm refused", [](hb::GemvArgs& a, Built&) { a.gates.n_v = 4; a.norm_w = a.x; }},
         {"empty y", [](hb::GemvArgs& a, Built&) { a.y = {}; }},
     };
     for (const auto& [name, mut] : cases) {

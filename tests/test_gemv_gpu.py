@@ -234,7 +234,8 @@ def test_validation_error_classes(hz):
     assert _code(lambda: be.gemv(st, a)) == "Unsupported"      # fused norm is Vulkan-only
     a = _args(be)
     a.gates_n_v = 4
-    assert _code(lambda: be.gemv(st, a)) == "Unsupported"
+    a.norm_w = a.x
+    assert _code(lambda: be.gemv(st, a)) == "Unsupported"      # gates next to a fused norm: refused, as everywhere in the reference
     a = _args(be)
     other = hb.CudaBackend(0)
     a.x = hb.TensorRef.of(other.allocate(2 * 64 * 4))
