@@ -152,9 +152,20 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
         if (tid == 0) {
             mbar_init(xbar, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            mbar_expect_tx(xbar, nb * kRec);
-            for (uint32_t off = 0; off < nb * kRec; off += 32768u)  // records are multiples of 16 bytes
-                bulk_g2s(smem_base + kOffData + off, xstage + off, min(32768u, nb * kRec - off), xbar);
+            // the records of the super-blocks this CTA walks: all of them, or -- for a range shorter than a unit's columns --
+            // the cyclic run that starts where the range starts, i.e. at most two contiguous pieces
+            const uint32_t c_begin = tb.start[cta], c_count = tb.start[cta + 1] - c_begin;
+            uint32_t lo[2] = {0u, 0u}, hi[2] = {nb, 0u};
+            if (KS == 1 && c_count < cpu) {  // two-slice partitions give every CTA whole units
+                const uint32_t first = (c_begin % cpu) * KS, last = first + c_count * KS, wrap = cpu * KS;
+                lo[0] = min(first, nb), hi[0] = min(min(last, wrap), nb);
+                lo[1] = 0u, hi[1] = last > wrap ? min(last - wrap, nb) : 0u;
+            }
+            mbar_expect_tx(xbar, ((hi[0] - lo[0]) + (hi[1] - lo[1])) * kRec);
+#pragma unroll
+            for (int p = 0; p < 2; ++p)
+                for (uint32_t off = lo[p] * kRec; off < hi[p] * kRec; off += 32768u)  // records are multiples of 16 bytes
+                    bulk_g2s(smem_base + kOffData + off, xstage + off, min(32768u, hi[p] * kRec - off), xbar);
         }
         __syncthreads();
         if (!mbar_wait(xbar, 0)) {
@@ -162,16 +173,22 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
             lost = true;
         }
     } else {
-        if constexpr (NORM) {
-            // fused input norm (single row): the row's rms first (one more block barrier), then the conversion below with
-            // every element multiplied by it and by norm_w
-            const float inv = block_inv_rms<kWarps>(x, nb * 256u, norm_eps, reinterpret_cast<float*>(smem + kOffRed), tid);
-            stage_row_rec<true>(smem + kOffData, x, nb, NTOK, 0, warp, kWarps, lane, F::kXLaneBytes == 8, norm_w, inv);
-        } else {
-            // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
+        // A CTA whose range is shorter than a unit's columns walks only those columns (super-blocks k * KS + ks for its
+        // columns k, cyclically from where its range starts): it converts just that part of x.  Wider ranges take all of it.
+        const uint32_t c_begin = tb.start[cta], c_count = tb.start[cta + 1] - c_begin;
+        float inv = 1.0f;
+        // fused input norm (single row): the row's rms first (one more block barrier); the conversion then multiplies every
+        // element by it and by norm_w
+        if constexpr (NORM) inv = block_inv_rms<kWarps>(x, nb * 256u, norm_eps, reinterpret_cast<float*>(smem + kOffRed), tid);
+        // every warp converts whole super-blocks of x on its own (scale included): one pass, one barrier
+        if (KS == 1 && c_count < cpu) {  // two-slice partitions give every CTA whole units
             for (uint32_t tk = 0; tk < NTOK; ++tk)
-                stage_row_rec(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride), nb, NTOK, tk,
-                              warp, kWarps, lane, F::kXLaneBytes == 8);
+                stage_row_rec<NORM, true>(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride),
+                                          nb, NTOK, tk, warp, kWarps, lane, F::kXLaneBytes == 8, norm_w, inv, (c_begin % cpu) * KS, c_count * KS, cpu * KS);
+        } else {
+            for (uint32_t tk = 0; tk < NTOK; ++tk)
+                stage_row_rec<NORM, false>(smem + kOffData, reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride),
+                                           nb, NTOK, tk, warp, kWarps, lane, F::kXLaneBytes == 8, norm_w, inv);
         }
         __syncthreads();
     }

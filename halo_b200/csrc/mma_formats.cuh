@@ -104,23 +104,37 @@ __device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v
 /// w, w + n_warps, ..., four at a time so that their loads overlap.  The arithmetic does not depend on who calls it.
 /// NORM: the row is normalised on the way, element i becomes (x[i] * inv) * norm_w[i] -- the arithmetic of the CPU backend's
 /// rms_norm (backends/cpu/ops_basic.cpp:28-30) with `inv` = 1 / sqrt(mean of squares + eps) supplied by the caller.
-template <bool NORM = false>
+/// PART: only the super-blocks (first + j) mod wrap for j < count are converted (a CTA that walks a few columns of K needs
+/// no more); otherwise all of them.
+template <bool NORM = false, bool PART = false>
 __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t warp,
-                                              uint32_t n_warps, uint32_t lane, bool split_halves, const float* norm_w = nullptr, float inv = 1.0f) {
+                                              uint32_t n_warps, uint32_t lane, bool split_halves, const float* norm_w = nullptr, float inv = 1.0f,
+                                              uint32_t first = 0, uint32_t count = 0, uint32_t wrap = 0) {
     constexpr uint32_t kAhead = 4;
     const float4* xr = reinterpret_cast<const float4*>(xrow);
     const float4* wr = reinterpret_cast<const float4*>(norm_w);
-    for (uint32_t sb0 = warp; sb0 < n_sb; sb0 += kAhead * n_warps) {
+    if constexpr (!PART) count = n_sb;
+    auto sb_of = [&](uint32_t j) {  // the j-th super-block to convert; n_sb (= none) past the end or past the row
+        if constexpr (!PART) {
+            return j;
+        } else {
+            if (j >= count) return n_sb;
+            uint32_t sb = first + j;
+            if (sb >= wrap) sb -= wrap;
+            return sb;
+        }
+    };
+    for (uint32_t j0 = warp; j0 < count; j0 += kAhead * n_warps) {
         float4 v[kAhead][2];
 #pragma unroll
         for (uint32_t j = 0; j < kAhead; ++j) {
-            const uint32_t sb = sb0 + j * n_warps;
+            const uint32_t sb = sb_of(j0 + j * n_warps);
             if (sb < n_sb) v[j][0] = xr[sb * 64u + lane], v[j][1] = xr[sb * 64u + 32u + lane];
         }
         if constexpr (NORM) {
 #pragma unroll
             for (uint32_t j = 0; j < kAhead; ++j) {
-                const uint32_t sb = sb0 + j * n_warps;
+                const uint32_t sb = sb_of(j0 + j * n_warps);
                 if (sb < n_sb) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -135,7 +149,7 @@ __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, 
         }
 #pragma unroll
         for (uint32_t j = 0; j < kAhead; ++j) {
-            const uint32_t sb = sb0 + j * n_warps;
+            const uint32_t sb = sb_of(j0 + j * n_warps);
             if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane, split_halves);
         }
     }
