@@ -155,17 +155,17 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
             // the records of the super-blocks this CTA walks: all of them, or -- for a range shorter than a unit's columns --
             // the cyclic run that starts where the range starts, i.e. at most two contiguous pieces
             const uint32_t c_begin = tb.start[cta], c_count = tb.start[cta + 1] - c_begin;
-            uint32_t lo[2] = {0u, 0u}, hi[2] = {nb, 0u};
+            uint32_t lo[2] = {0u, 0u}, hi[2] = {nb, 0u}, at[2] = {0u, 0u};  // super-blocks [lo, hi) go to records at, at + 1, ...
             if (KS == 1 && c_count < cpu) {  // two-slice partitions give every CTA whole units
                 const uint32_t first = (c_begin % cpu) * KS, last = first + c_count * KS, wrap = cpu * KS;
                 lo[0] = min(first, nb), hi[0] = min(min(last, wrap), nb);
-                lo[1] = 0u, hi[1] = last > wrap ? min(last - wrap, nb) : 0u;
+                lo[1] = 0u, hi[1] = last > wrap ? min(last - wrap, nb) : 0u, at[1] = wrap - first;
             }
             mbar_expect_tx(xbar, ((hi[0] - lo[0]) + (hi[1] - lo[1])) * kRec);
 #pragma unroll
             for (int p = 0; p < 2; ++p)
-                for (uint32_t off = lo[p] * kRec; off < hi[p] * kRec; off += 32768u)  // records are multiples of 16 bytes
-                    bulk_g2s(smem_base + kOffData + off, xstage + off, min(32768u, hi[p] * kRec - off), xbar);
+                for (uint32_t off = 0; off < (hi[p] - lo[p]) * kRec; off += 32768u)  // records are multiples of 16 bytes
+                    bulk_g2s(smem_base + kOffData + at[p] * kRec + off, xstage + lo[p] * kRec + off, min(32768u, (hi[p] - lo[p]) * kRec - off), xbar);
         }
         __syncthreads();
         if (!mbar_wait(xbar, 0)) {
@@ -193,6 +193,9 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
         __syncthreads();
     }
 
+    // Under a partial conversion record j holds the super-block of the j-th column of this CTA's range, not super-block j.
+    const uint32_t run_begin = tb.start[cta];
+    const bool run_part = KS == 1 && tb.start[cta + 1] - run_begin < cpu;
     const XLane<G> xl = make_xlane<NTOK, F::kXLaneBytes>(g, t);
     // fragment row g of the MMA reads slot row F::slot_row(g) (a format may permute the rows of a tile against bank conflicts)
     const uint32_t row = F::slot_row(g);
@@ -214,7 +217,7 @@ gemv_sk_resident_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_c
                     if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
                     lost = true;  // warp-uniform: every lane polled the same barrier
                 } else {
-                    F::template item<G, NTOK>(slot0 + slot * kSlot, t, smem + kOffData + sb * kRec, xl, smem + L::kOffZero, yacc, [&]() {
+                    F::template item<G, NTOK>(slot0 + slot * kSlot, t, smem + kOffData + (KS == 1 && run_part ? cons.col - run_begin : sb) * kRec, xl, smem + L::kOffZero, yacc, [&]() {
                         __syncwarp();
                         slot = slot + 1 == NS ? 0 : slot + 1;
                         parity ^= (slot == 0);

@@ -79,6 +79,15 @@ struct Geometry {
     void *counters, *partials;
 };
 
+/// x records a CTA of the resident kernels holds in shared memory: under a one-slice partition whose every CTA walks less
+/// than a unit's columns, the longest range; otherwise all super-blocks.
+inline uint32_t resident_records(const Geometry& g) {
+    if (g.ks != 1) return g.nb;
+    uint32_t longest = 0;
+    for (uint32_t c = 0; c < g.table.parts; ++c) longest = std::max(longest, g.table.start[c + 1] - g.table.start[c]);
+    return longest < g.table.cols_per_unit ? longest : g.nb;
+}
+
 template <class F, int NTOK>
 int geometry(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s, Geometry* g) {
     constexpr int G = (NTOK + 3) / 4;
@@ -97,7 +106,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     if constexpr (L::kOffData >= kSmemBudget) {
         return fail(HALO_CUDA_E_KERNEL, "MATMUL: ring of %d stages does not fit", NS);
     } else {
-        const uint32_t smem_bytes = L::kOffData + g.nb * L::kRec;
+        const uint32_t smem_bytes = L::kOffData + resident_records(g) * L::kRec;
         static bool attr_set = false;
         if (!attr_set) {
             HC_CUDA(cudaFuncSetAttribute(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -174,7 +183,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
 template <class F, int NTOK, int KS>
 int launch_sliced(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint32_t tok0, cudaStream_t s) {
     if constexpr (NTOK <= kResidentMaxTok) {
-        const uint64_t x_bytes = uint64_t{g.nb} * XRec<NTOK>::kBytes;
+        const uint64_t x_bytes = uint64_t{resident_records(g)} * XRec<NTOK>::kBytes;
         if (SkLayout<F, NTOK, kRingStages, KS>::kOffData + x_bytes <= kSmemBudget) return launch_resident<F, NTOK, kRingStages, KS>(ctx, c, g, tok0, s);
     }
     return launch_streamed<F, NTOK, KS>(ctx, c, g, tok0, s);

@@ -105,7 +105,7 @@ __device__ __forceinline__ void stage_superblock(uint8_t* area, const float4 (&v
 /// NORM: the row is normalised on the way, element i becomes (x[i] * inv) * norm_w[i] -- the arithmetic of the CPU backend's
 /// rms_norm (backends/cpu/ops_basic.cpp:28-30) with `inv` = 1 / sqrt(mean of squares + eps) supplied by the caller.
 /// PART: only the super-blocks (first + j) mod wrap for j < count are converted (a CTA that walks a few columns of K needs
-/// no more); otherwise all of them.
+/// no more) and record j of the area belongs to the j-th of them; otherwise all are converted, record sb to super-block sb.
 template <bool NORM = false, bool PART = false>
 __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, uint32_t n_sb, uint32_t n_tok, uint32_t tok, uint32_t warp,
                                               uint32_t n_warps, uint32_t lane, bool split_halves, const float* norm_w = nullptr, float inv = 1.0f,
@@ -150,7 +150,8 @@ __device__ __forceinline__ void stage_row_rec(uint8_t* area, const float* xrow, 
 #pragma unroll
         for (uint32_t j = 0; j < kAhead; ++j) {
             const uint32_t sb = sb_of(j0 + j * n_warps);
-            if (sb < n_sb) stage_superblock(area, v[j], sb, n_tok, tok, lane, split_halves);
+            // a partial conversion stores its records compactly, in the order of the run
+            if (sb < n_sb) stage_superblock(area, v[j], PART ? j0 + j * n_warps : sb, n_tok, tok, lane, split_halves);
         }
     }
 }
