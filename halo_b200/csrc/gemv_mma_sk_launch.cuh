@@ -6,7 +6,7 @@
 namespace halo_cuda {
 namespace sk {
 
-constexpr int kResidentMaxTok = 4;  // larger batches always stream x
+constexpr int kResidentMaxTok = 8;  // larger batches always stream x (sixteen rows of records do not fit next to any ring)
 // Stages of a warp's weight ring.  Two (one tile being read, one in flight) measured faster than three or four on every
 // shape: the per-warp streams already keep far more bytes in flight than the memory system needs, and deeper rings
 // only spread the DRAM accesses over more rows at a time.
