@@ -456,7 +456,19 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a CUDA device: the matmul path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL may announce its version on stdout when it builds the communicator; the contract of this script is one JSON line
+        # there, so the communicator is built (first collective) with stdout pointed at stderr
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     be = hb.CudaBackend(local_rank)
     st = be.create_stream()
     lib, ctx = be.lib, be.ctx
