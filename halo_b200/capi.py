@@ -19,6 +19,7 @@ SPLIT_NONE, SPLIT_COLUMN, SPLIT_ROW = 0, 1, 2
 
 OP_GET_ROWS, OP_GEMV, OP_LM_HEAD = 0, 3, 14
 GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16, GEMV_MMA_M1, GEMV_MMA_R = 0, 1, 2, 3, 4, 5, 6, 7
+GEMV_MMA_I8X2 = 8
 FLAG_ALLOW_GEMM = 1
 FLAG_NO_SCRATCH = 0x80000000
 

@@ -21,6 +21,7 @@ constexpr HaloCudaVariant kGemvVariants[] = {
     {HALO_CUDA_GEMM_TCGEN05_BF16, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_bf16"},
     {HALO_CUDA_GEMV_MMA_M1, HALO_CUDA_OP_GEMV, 3, "gemv_mma_m1"},
     {HALO_CUDA_GEMV_MMA_R, HALO_CUDA_OP_GEMV, 5, "gemv_mma_r"},
+    {HALO_CUDA_GEMV_MMA_I8X2, HALO_CUDA_OP_GEMV, 6, "gemv_mma_i8x2"},
 };
 constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
 constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
@@ -75,6 +76,15 @@ int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, v
         if (zeroed) HC_CUDA(cudaMemsetAsync(ctx->workspace[slot], 0, want, stream));
     }
     *out = ctx->workspace[slot];
+    return 0;
+}
+
+bool note_smem_raised(HaloCudaCtx* ctx, const void* kernel) { return ctx->smem_raised.insert(kernel).second; }
+
+int allow_dynamic_smem(HaloCudaCtx* ctx, const void* kernel, uint32_t bytes) {
+    if (ctx->smem_raised.count(kernel) != 0) return 0;
+    HC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    note_smem_raised(ctx, kernel);
     return 0;
 }
 
@@ -150,6 +160,7 @@ uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t req
             if (is_gemm && (!gemm_ok || !gemm_tcgen05_supports(c))) continue;
             if ((p.variant_id == HALO_CUDA_GEMV_MMA_F16X2 || p.variant_id == HALO_CUDA_GEMV_MMA_M1) && !gemv_mma_supports(c)) continue;
             if (p.variant_id == HALO_CUDA_GEMV_WARP_F32 && !gemv_warp_f32_supports(c)) continue;
+            if (p.variant_id == HALO_CUDA_GEMV_MMA_I8X2 && (!gemv_i8_supports(c) || (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) != 0)) continue;
             return p.variant_id;
         }
     }
@@ -157,6 +168,9 @@ uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t req
     // prefill-sized; otherwise one numerics family for every batch size, so that a row's bits do not depend
     // on how many rows share the call (include/halo/backend/backend.h:300-304).
     if (gemm_ok && c.n_vec >= 64 && gemm_tcgen05_supports(c)) return HALO_CUDA_GEMM_TCGEN05_F16;
+    // Q4_K: the int8 tensor-core family at every batch size; calls that may not touch context scratch keep the fp16 family,
+    // whose statically partitioned kernels need none
+    if ((c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) == 0 && gemv_i8_supports(c)) return HALO_CUDA_GEMV_MMA_I8X2;
     if (gemv_mma_supports(c)) return HALO_CUDA_GEMV_MMA_F16X2;
     if (gemv_warp_f32_supports(c)) return HALO_CUDA_GEMV_WARP_F32;
     return HALO_CUDA_GEMV_EXACT8;
@@ -181,6 +195,12 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
             if (!gemv_mma_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_m1 needs Q4_K weights in dense 16-byte-aligned rows");
             return launch_gemv_mma_m1(ctx, c, s);
+        case HALO_CUDA_GEMV_MMA_I8X2:
+            if (!gemv_i8_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_i8x2 needs Q4_K weights in dense 16-byte-aligned rows and 16-byte-aligned x");
+            if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH)
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_i8x2 uses context scratch");
+            return launch_gemv_i8(ctx, c, s);
         case HALO_CUDA_GEMV_MMA_R:
             if (!gemv_mma_r_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_r needs repacked 16-byte-aligned rows, cols %% 256 == 0 and 16-byte-aligned x");
@@ -599,8 +619,9 @@ int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const floa
     if (c.n_vec != 1) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row, not %u", c.n_vec);
     if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm belongs to the kernels that use context scratch");
     const uint32_t v = resolve_variant(ctx, c, args->variant_id);
-    const bool has_it = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c));
-    if (!has_it) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7) have the fused input norm");
+    const bool has_it = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c)) ||
+                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c));
+    if (!has_it) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7, 8) have the fused input norm");
     if (c.rows == 0) return 0;
     c.norm_w = norm_w;
     c.norm_eps = norm_eps;
@@ -666,7 +687,8 @@ int halo_cuda_gemv_reduce(HaloCudaCtx* ctx, const HaloCudaGemv* args, const Halo
     if (c.rows == 0 || c.n_vec == 0) return 0;  // every rank sees the same shape, so every rank skips
     if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the peer epilogue belongs to the kernels that use context scratch");
     const uint32_t v = resolve_variant(ctx, c, args->variant_id);
-    const bool pushes = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c));
+    const bool pushes = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c)) ||
+                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c));
     if (!pushes) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7) have the peer epilogue");
     c.peer = peers;
     const cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -375,11 +375,7 @@ int launch_t(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
     HC_CUDA(cudaGetLastError());
     CUtensorMap xmap;
     if (int rc = x_map(ws, c.n_vec, c.cols, BF16, &xmap)) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemm_q4k_tcgen05_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
-        attr_set = true;
-    }
+    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemm_q4k_tcgen05_kernel<BF16>), kGemmSmem)) return rc;
     const dim3 grid((c.rows + kBN - 1) / kBN, (c.n_vec + kBM - 1) / kBM);
     gemm_q4k_tcgen05_kernel<BF16><<<grid, kGemmThreads, kGemmSmem, s>>>(xmap, c.w, c.w_stride, c.y, c.y_stride, c.rows, c.n_vec, c.cols / kBK,
                                                                           ctx->error_word_dev);

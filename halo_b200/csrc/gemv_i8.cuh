@@ -1,0 +1,432 @@
+// The int8 tensor-core skinny kernels (variant gemv_mma_i8x2): x travels as two signed 8-bit digits per element, the
+// 4-bit codes go into the MMA as unsigned bytes, and every sum up to the per-sub-block scale is an exact integer.
+//
+// x is quantised per super-block (256 elements, what one warp converts at a time): s = the power of two that puts the
+// super-block's largest magnitude in (2^14, 32639], xq = rint(x * s) = 256 * hi + lo with hi, lo in [-128, 127].  The
+// error of the product is therefore |x * s - xq| <= 1/2 per element, i.e. at most 2^-15 of the super-block's largest
+// magnitude; everything behind it is exact until the fp32 epilogue:
+//     S_s  = sum over the 32 elements of sub-block s of q * xq                      (int32, mma.sync m16n8k32 u8 x s8)
+//     A_p  = sc_p * S_p + sc_{4+p} * S_{4+p},   M_p = m_p * X_p + m_{4+p} * X_{4+p}    (int32; X_s = sum of xq over sub-block s)
+//     u_p  = fma(-dmin, float(M_p), d * float(A_p))                                  p = 0 .. 3
+//     P_p  = fma(1 / s, u_p, P_p)                                                    over the super-blocks of the walk, in order
+//     y    = (P_0 + P_1) + (P_2 + P_3),  then the K slices and the CTAs' partials as in the other balanced kernels.
+// That order is the same for every batch size, so a row's bits do not depend on how many rows share the call
+// (include/halo/backend/backend.h:300-304).  A call with ONE x row gets it with a quarter of the MMA work per sub-block:
+// x sits in the column pair (2p, 2p + 1) of B for the sub-blocks s = p (mod 4) (hi digit, lo digit; the other columns
+// read zeros), so one accumulator tile carries four sub-blocks and lane t of a row finishes P_t; two shuffles add them.
+//
+// The partition, the per-warp TMA weight ring, the K slices and the cross-CTA reduction are those of gemv_mma_sk.cuh.
+#pragma once
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "gemv_mma_sk.cuh"
+
+namespace halo_cuda {
+namespace i8 {
+
+using namespace mma;
+using sk::ColumnWalk;
+
+__device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+/// The first MMA of a chain: C = 0 comes from the zero register.
+__device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// x records of NTOK rows, per super-block:
+//   digits  [sub-block 0..7][column 0..2 * NTOK - 1][32 B]   column 2 * tok = hi digits, 2 * tok + 1 = lo digits of row tok;
+//                                                            byte i of a column = element i of the sub-block
+//   meta    [row][48 B]                                      int32 pairs (X_p, X_{4+p}) for p = 0..3, then 1 / s as fp32
+// The digit area and the meta area are separate arrays (all super-blocks of one, then all of the other), in shared
+// memory as in the scratch the pre-staging kernel fills.
+constexpr uint32_t kDigitBytes = 512, kMetaBytes = 48;
+inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
+inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * rec_bytes(n_tok); }
+
+/// One super-block (index sb) of x row `tok` into the records at `digits` / `meta`, by one warp: lane l holds elements
+/// 8 l .. 8 l + 7 in (v0, v1).  A super-block with a NaN or an infinity gets 1 / s = NaN, which poisons exactly the sums it
+/// enters (the reference's per-row NaN, src/backend/backend.cpp:91-96).
+__device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta, float4 v0, float4 v1, uint32_t sb, uint32_t n_tok, uint32_t tok,
+                                                 uint32_t lane) {
+    float m = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                    fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    const bool finite = m < __int_as_float(0x7F800000);  // false for NaN too (fmaxf drops NaNs: checked per element below)
+    const int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xFFu) - 127;
+    int se = (m > 0.0f && finite) ? 14 - e : 0;
+    se = max(-100, min(100, se));
+    float s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
+    if (m * s > 32639.0f) se -= 1, s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
+    const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    int q[8], h[8], sum = 0;
+    bool bad = !finite;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        bad |= f[i] != f[i];
+        q[i] = __float2int_rn(fminf(fmaxf(f[i] * s, -32639.0f), 32639.0f));
+        h[i] = (q[i] + 128) >> 8;
+        sum += q[i];
+    }
+    bad = __any_sync(0xFFFFFFFFu, bad);
+    // hi digits h; lo digits q - 256 h are the low bytes of q (two's complement)
+    uint2 hi, lo;
+    hi.x = prmt(prmt(h[0], h[1], 0x0040), prmt(h[2], h[3], 0x0040), 0x5410);
+    hi.y = prmt(prmt(h[4], h[5], 0x0040), prmt(h[6], h[7], 0x0040), 0x5410);
+    lo.x = prmt(prmt(q[0], q[1], 0x0040), prmt(q[2], q[3], 0x0040), 0x5410);
+    lo.y = prmt(prmt(q[4], q[5], 0x0040), prmt(q[6], q[7], 0x0040), 0x5410);
+    const uint32_t sub = lane >> 2, pos = (lane & 3u) * 8u;
+    uint8_t* d = digits + uint64_t{sb} * (kDigitBytes * n_tok) + sub * (64u * n_tok) + tok * 64u + pos;
+    *reinterpret_cast<uint2*>(d) = hi;
+    *reinterpret_cast<uint2*>(d + 32) = lo;
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    uint8_t* mt = meta + uint64_t{sb} * (kMetaBytes * n_tok) + tok * kMetaBytes;
+    if ((lane & 3u) == 0) reinterpret_cast<int*>(mt)[(sub & 3u) * 2u + (sub >> 2)] = sum;
+    if (lane == 0) reinterpret_cast<float*>(mt)[8] = bad ? __int_as_float(0x7FC00000) : __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
+}
+
+/// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block of one row into the scratch records.
+static __global__ void __launch_bounds__(512) stage_x_i8_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch, uint32_t nb,
+                                                                uint32_t n_tok) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t tk = blockIdx.x, sb = blockIdx.y * 16u + (threadIdx.x >> 5);
+    if (sb >= nb) return;
+    const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    const uint32_t lane = threadIdx.x & 31u;
+    stage_superblock(scratch, scratch + uint64_t{nb} * kDigitBytes * n_tok, xr[sb * 64u + 2u * lane], xr[sb * 64u + 2u * lane + 1u], sb, n_tok, tk, lane);
+}
+
+// ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows (the extra 16 bytes keep the fragment reads conflict-free)
+struct Q4Ki {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1;
+    static constexpr bool kAllowSlices = true;
+
+    /// Lane constants of the single-row form.
+    struct One {
+        const uint8_t* bp[4];  // B base per sub-block phase: this lane's digits, or zeros
+        uint32_t bstep[4];     // bytes per super-block of that base (0 for the zeros)
+        uint32_t sel, sh;      // byte selector of this lane's scale codes; 4 where its sub-blocks come from the high nibbles
+    };
+    __device__ static __forceinline__ One make_one(const uint8_t* digits, const uint8_t* zeros, uint32_t g, uint32_t t) {
+        One o;
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {
+            const bool real = (g >> 1) == static_cast<uint32_t>(ph);
+            o.bp[ph] = real ? digits + (g & 1u) * 32u + t * 8u : zeros + t * 8u;
+            o.bstep[ph] = real ? kDigitBytes : 0u;
+        }
+        o.sel = t | 0x4440u;
+        o.sh = (t & 1u) * 4u;
+        return o;
+    }
+
+    /// One row's share of the epilogue: the 6-bit codes of sub-blocks t and 4 + t (src/tensor/quant.cpp:236-244), the integer
+    /// sums, the fp32 step.  S0 / S1: the sub-block sums (already without the high-nibble factor), X: (X_t, X_{4+t}).
+    __device__ static __forceinline__ float finish_pair(const uint4 h, uint32_t sel, int S0, int S1, int2 X) {
+        const uint32_t by = prmt(h.y, 0u, sel), bz = prmt(h.z, 0u, sel), bw = prmt(h.w, 0u, sel);
+        const int sc0 = by & 63u, m0 = bz & 63u;
+        const int sc1 = (bw & 15u) | ((by >> 2) & 0x30u), m1 = (bw >> 4) | ((bz >> 2) & 0x30u);
+        const int A = sc0 * S0 + sc1 * S1, M = m0 * X.x + m1 * X.y;
+        const __half2 dh = *reinterpret_cast<const __half2*>(&h.x);
+        return __fmaf_rn(-__high2float(dh), __int2float_rn(M), __fmul_rn(__low2float(dh), __int2float_rn(A)));
+    }
+
+    /// A single x row: P[0], P[1] are this lane's P_t of rows g and g + 8.
+    template <class Release>
+    __device__ static __forceinline__ void item_one(const uint8_t* r0, uint32_t t, const One& o, uint32_t rec, const uint8_t* meta, float (&P)[2],
+                                                    Release&& release) {
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        const uint4 h0 = *reinterpret_cast<const uint4*>(r0), h1 = *reinterpret_cast<const uint4*>(r1);
+        const uint8_t* bq[4];
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) bq[ph] = o.bp[ph] + rec * o.bstep[ph];
+        int c[2][4];  // tile h: sub-blocks 4h .. 4h + 3, one per column pair
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint2 q0 = *reinterpret_cast<const uint2*>(r0 + 16 + 32 * j + 8 * t);
+            const uint2 q1 = *reinterpret_cast<const uint2*>(r1 + 16 + 32 * j + 8 * t);
+            const uint2 bl = *reinterpret_cast<const uint2*>(bq[(2 * j) & 3] + (2 * j) * 64);
+            const uint2 bh = *reinterpret_cast<const uint2*>(bq[(2 * j + 1) & 3] + (2 * j + 1) * 64);
+            if ((j & 1) == 0) imma0(c[j >> 1], q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, bl.x, bl.y);
+            else imma(c[j >> 1], q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, bl.x, bl.y);
+            // the high nibbles stay in place: 16 q as an unsigned byte, the factor leaves the sum by an exact shift
+            imma(c[j >> 1], q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u, bh.x, bh.y);
+        }
+        release();  // every byte of the slot has been consumed
+        const uint8_t* mt = meta + rec * kMetaBytes;
+        const int2 X = *reinterpret_cast<const int2*>(mt + t * 8u);
+        const float inv = *reinterpret_cast<const float*>(mt + 32);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int S0 = (c[0][2 * rr] * 256 + c[0][2 * rr + 1]) >> o.sh, S1 = (c[1][2 * rr] * 256 + c[1][2 * rr + 1]) >> o.sh;
+            P[rr] = __fmaf_rn(inv, finish_pair(rr ? h1 : h0, o.sel, S0, S1, X), P[rr]);
+        }
+    }
+
+    /// 2 .. 16 x rows: P[gi][rr][p] of rows g, g + 8 and x row 4 gi + t.
+    template <int G, int NTOK, class Release>
+    __device__ static __forceinline__ void item_many(const uint8_t* r0, uint32_t t, uint32_t g, const uint8_t* dig, const uint8_t* meta, float (&P)[G][2][4],
+                                                     Release&& release) {
+        constexpr uint32_t kSub = 64u * NTOK;
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        const uint4 hh[2] = {*reinterpret_cast<const uint4*>(r0), *reinterpret_cast<const uint4*>(r1)};
+        uint32_t boff[G], moff[G];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            boff[gi] = min(8u * gi + g, 2u * NTOK - 1u) * 32u + t * 8u;
+            moff[gi] = min(4u * gi + t, static_cast<uint32_t>(NTOK - 1)) * kMetaBytes;
+        }
+        // the 6-bit codes of both rows, four per word: [0] sub-blocks 0..3, [1] sub-blocks 4..7
+        uint32_t sc[2][2], mn[2][2];
+        float dq[2], dmn[2];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const uint4 h = hh[rr];
+            sc[rr][0] = h.y & 0x3F3F3F3Fu;
+            sc[rr][1] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+            mn[rr][0] = h.z & 0x3F3F3F3Fu;
+            mn[rr][1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            const __half2 dh = *reinterpret_cast<const __half2*>(&h.x);
+            dq[rr] = __low2float(dh), dmn[rr] = __high2float(dh);
+        }
+        auto code = [](uint32_t word, int idx) { return static_cast<int>((word >> (8 * idx)) & 0xFFu); };
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {  // phases p = 2 jj, 2 jj + 1: sub-blocks p, p + 4 (chunks jj and jj + 2)
+            int A[G][2][2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int j = jj + 2 * half;
+                const uint2 q0 = *reinterpret_cast<const uint2*>(r0 + 16 + 32 * j + 8 * t);
+                const uint2 q1 = *reinterpret_cast<const uint2*>(r1 + 16 + 32 * j + 8 * t);
+                const uint32_t l0 = q0.x & 0x0F0F0F0Fu, l1 = q1.x & 0x0F0F0F0Fu, l2 = q0.y & 0x0F0F0F0Fu, l3 = q1.y & 0x0F0F0F0Fu;
+                const uint32_t u0 = q0.x & 0xF0F0F0F0u, u1 = q1.x & 0xF0F0F0F0u, u2 = q0.y & 0xF0F0F0F0u, u3 = q1.y & 0xF0F0F0F0u;
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const uint2 bl = *reinterpret_cast<const uint2*>(dig + (2 * j) * kSub + boff[gi]);
+                    const uint2 bh = *reinterpret_cast<const uint2*>(dig + (2 * j + 1) * kSub + boff[gi]);
+                    int cl[4], ch[4];
+                    imma0(cl, l0, l1, l2, l3, bl.x, bl.y);
+                    imma0(ch, u0, u1, u2, u3, bh.x, bh.y);
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int Sl = cl[2 * rr] * 256 + cl[2 * rr + 1], Sh = (ch[2 * rr] * 256 + ch[2 * rr + 1]) >> 4;
+                        const int wl = code(sc[rr][half], 2 * jj), wh = code(sc[rr][half], 2 * jj + 1);
+                        if (half == 0) A[gi][rr][0] = wl * Sl, A[gi][rr][1] = wh * Sh;
+                        else A[gi][rr][0] += wl * Sl, A[gi][rr][1] += wh * Sh;
+                    }
+                }
+            }
+            if (jj == 1) release();
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                const int4 X = *reinterpret_cast<const int4*>(meta + moff[gi] + jj * 16);  // (X_p, X_{4+p}, X_{p+1}, X_{5+p}), p = 2 jj
+                const float inv = *reinterpret_cast<const float*>(meta + moff[gi] + 32);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int M0 = code(mn[rr][0], 2 * jj) * X.x + code(mn[rr][1], 2 * jj) * X.y;
+                    const int M1 = code(mn[rr][0], 2 * jj + 1) * X.z + code(mn[rr][1], 2 * jj + 1) * X.w;
+                    const float u0 = __fmaf_rn(-dmn[rr], __int2float_rn(M0), __fmul_rn(dq[rr], __int2float_rn(A[gi][rr][0])));
+                    const float u1 = __fmaf_rn(-dmn[rr], __int2float_rn(M1), __fmul_rn(dq[rr], __int2float_rn(A[gi][rr][1])));
+                    P[gi][rr][2 * jj] = __fmaf_rn(inv, u0, P[gi][rr][2 * jj]);
+                    P[gi][rr][2 * jj + 1] = __fmaf_rn(inv, u1, P[gi][rr][2 * jj + 1]);
+                }
+            }
+        }
+    }
+};
+
+// Shared-memory layout: header (mma_common.cuh) | weight ring | slice sums (KS > 1) | zeros (single row) | digits | meta
+template <class F, int NTOK, int NS, int KS>
+struct Layout {
+    static constexpr int G = (NTOK + 3) / 4;
+    static constexpr uint32_t kSlot = 16 * F::kPitch;
+    static constexpr uint32_t kOffSlices = kOffRing + kSkWarps * NS * kSlot;
+    static constexpr uint32_t kRedBytes = KS > 1 ? (kSkWarps / KS) * (KS - 1) * 32 * 2 * G * 4 : 0;
+    static constexpr uint32_t kOffZero = (kOffSlices + kRedBytes + 127u) & ~127u;
+    // a single row's digits start 64 bytes off the zeros' 128-byte phase: the lanes of a half warp that read x and those that
+    // read zeros then never meet on a bank
+    static constexpr uint32_t kOffDigits = kOffZero + (NTOK == 1 ? 512u + 64u : 0u);
+    static constexpr uint32_t bytes(uint32_t nb) { return kOffDigits + nb * rec_bytes(NTOK); }
+};
+
+template <class F, int NTOK, int NS, int KS, bool PRE, bool NORM = false>
+__global__ void __launch_bounds__(kSkWarps * 32, 1)
+gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
+               float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, float* __restrict__ partials, uint32_t* __restrict__ counters,
+               uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage, const __grid_constant__ PeerPush peer,
+               const float* __restrict__ norm_w, float norm_eps) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    using L = Layout<F, NTOK, NS, KS>;
+    constexpr int G = L::G, R = kSkWarps / KS;
+    constexpr uint32_t kThreads = kSkWarps * 32, kSlot = L::kSlot;
+    static_assert(kSkWarps <= kMaxWarps && NS <= 6, "shared-memory header layout");
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t r = warp % R, ks = warp / R;
+    const uint32_t n_rb = (rows + 15u) / 16u, cpu = tb.cols_per_unit;
+    const uint32_t cta = blockIdx.x;  // the grid has exactly tb.parts CTAs
+    uint8_t* digits = smem + L::kOffDigits;
+    uint8_t* meta = digits + nb * (kDigitBytes * NTOK);
+
+    const uint32_t bars = smem_base + kOffBars + warp * NS * 8u;
+    const uint32_t ring = smem_base + kOffRing + warp * NS * kSlot;
+    asm volatile("griddepcontrol.launch_dependents;");  // the next kernel in the stream may start filling its ring
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) mbar_init(bars + s * 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    ColumnWalk prod;
+    prod.init(tb.start[cta], tb.start[cta + 1], cpu);
+    uint32_t fill_slot = 0;
+    auto refill = [&]() {  // the tile of the producer's column -> slot fill_slot (positions past the matrix have no tiles)
+        if (prod.col >= prod.end) return;
+        const uint32_t prb = prod.unit * R + r, psb = prod.k * KS + ks;
+        if (prb < n_rb && psb < nb) {
+            if (lane == 0) {
+                mbar_expect_tx(bars + fill_slot * 8u, kSlot);
+                sk::tma_item_g2s<F>(ring + fill_slot * kSlot, &wmap, psb, prb * 16u, bars + fill_slot * 8u);
+            }
+            fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
+        }
+        prod.step(cpu);
+    };
+#pragma unroll
+    for (int it = 0; it < NS; ++it) refill();
+    // The weights never depend on the kernel before this one, so the ring is filled first; only now wait for it.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    bool lost = false;
+    if constexpr (NTOK == 1)
+        for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffZero)[i] = 0u;
+    if constexpr (PRE) {
+        const uint32_t xbar = smem_base + kOffXBar;
+        if (tid == 0) {
+            mbar_init(xbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            const uint32_t total = nb * rec_bytes(NTOK);  // digits, then meta: one contiguous run in the scratch as in shared memory
+            mbar_expect_tx(xbar, total);
+            for (uint32_t off = 0; off < total; off += 32768u) bulk_g2s(smem_base + L::kOffDigits + off, xstage + off, min(32768u, total - off), xbar);
+        }
+        __syncthreads();
+        if (!mbar_wait(xbar, 0)) {
+            if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+            lost = true;
+        }
+    } else {
+        float inv_rms = 1.0f;
+        if constexpr (NORM) inv_rms = block_inv_rms<kSkWarps>(x, nb * 256u, norm_eps, reinterpret_cast<float*>(smem + kOffRed), tid);
+        // every warp loads its super-blocks first (two at a time), then converts them: one round trip to memory per pair
+        for (uint32_t tk = 0; tk < NTOK; ++tk) {
+            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+            const float4* wr = reinterpret_cast<const float4*>(norm_w);
+            for (uint32_t sb0 = warp; sb0 < nb; sb0 += 2 * kSkWarps) {
+                const uint32_t sb1 = sb0 + kSkWarps;
+                float4 v[2][2], w[2][2];
+                v[0][0] = xr[sb0 * 64u + 2u * lane], v[0][1] = xr[sb0 * 64u + 2u * lane + 1u];
+                if (sb1 < nb) v[1][0] = xr[sb1 * 64u + 2u * lane], v[1][1] = xr[sb1 * 64u + 2u * lane + 1u];
+                if constexpr (NORM) {
+                    w[0][0] = wr[sb0 * 64u + 2u * lane], w[0][1] = wr[sb0 * 64u + 2u * lane + 1u];
+                    if (sb1 < nb) w[1][0] = wr[sb1 * 64u + 2u * lane], w[1][1] = wr[sb1 * 64u + 2u * lane + 1u];
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (i == 1 && sb1 >= nb) break;
+                    if constexpr (NORM) {  // the CPU backend's rms_norm arithmetic (backends/cpu/ops_basic.cpp:28-30), unfused multiplies
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            v[i][hf].x = __fmul_rn(__fmul_rn(v[i][hf].x, inv_rms), w[i][hf].x);
+                            v[i][hf].y = __fmul_rn(__fmul_rn(v[i][hf].y, inv_rms), w[i][hf].y);
+                            v[i][hf].z = __fmul_rn(__fmul_rn(v[i][hf].z, inv_rms), w[i][hf].z);
+                            v[i][hf].w = __fmul_rn(__fmul_rn(v[i][hf].w, inv_rms), w[i][hf].w);
+                        }
+                    }
+                    stage_superblock(digits, meta, v[i][0], v[i][1], i == 0 ? sb0 : sb1, NTOK, tk, lane);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + g * F::kPitch;
+    float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
+    [[maybe_unused]] typename F::One one;
+    if constexpr (NTOK == 1) one = F::make_one(digits, smem + L::kOffZero, g, t);
+    float P[G][2][NTOK == 1 ? 1 : 4];
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+            for (int p = 0; p < (NTOK == 1 ? 1 : 4); ++p) P[gi][rr][p] = 0.0f;
+
+    uint32_t slot = 0, parity = 0;
+    ColumnWalk cons;
+    cons.init(tb.start[cta], tb.start[cta + 1], cpu);
+    // A warp that lost a copy keeps walking (its sums are garbage, the error word says so): its siblings wait for it at the barriers.
+    while (cons.col < cons.end) {
+        const uint32_t rb = cons.unit * R + r, sb = cons.k * KS + ks;
+        if (rb < n_rb) {
+            if (sb < nb) {
+                if (!lost && !mbar_wait(bars + slot * 8u, parity)) {
+                    if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                    lost = true;  // warp-uniform: every lane polled the same barrier
+                }
+                auto release = [&]() {
+                    __syncwarp();
+                    slot = slot + 1 == NS ? 0 : slot + 1;
+                    parity ^= (slot == 0);
+                    refill();
+                };
+                if constexpr (NTOK == 1) {
+                    float (&P1)[2] = *reinterpret_cast<float (*)[2]>(&P[0][0][0]);
+                    static_assert(sizeof(P) == 2 * sizeof(float), "single-row accumulators");
+                    F::item_one(slot0 + slot * kSlot, t, one, sb, meta, P1, release);
+                } else {
+                    F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + sb * (kDigitBytes * NTOK), meta + sb * (kMetaBytes * NTOK), P, release);
+                }
+            } else {
+                refill();  // keeps the producer in step
+            }
+            if (cons.k + 1 == cpu || cons.col + 1 == cons.end) {  // the row block, or this CTA's share of it, is done
+                float yacc[G][2];
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        if constexpr (NTOK == 1) {
+                            float v = P[gi][rr][0];
+                            v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));  // (P_0 + P_1), (P_2 + P_3)
+                            v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
+                            yacc[gi][rr] = v;
+                            P[gi][rr][0] = 0.0f;
+                        } else {
+                            yacc[gi][rr] = __fadd_rn(__fadd_rn(P[gi][rr][0], P[gi][rr][1]), __fadd_rn(P[gi][rr][2], P[gi][rr][3]));
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
+                        }
+                    }
+                sk::finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, g, peer);
+            }
+        } else {
+            refill();
+        }
+        cons.step(cpu);
+    }
+    if (lost) sk::linger_after_loss();
+}
+
+}  // namespace i8
+}  // namespace halo_cuda

@@ -569,12 +569,7 @@ int launch_n(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, cudaStream_t s)
     constexpr int G = (NTOK + 3) / 4;
     const uint32_t nb = c.cols / 256u;
     const Plan p = plan_for(nb, NTOK, kOffRing + kRowBlocks * KS * NS * kSlotBytes, (KS - 1) * kRowBlocks * 32 * 2 * G * 4);
-    static bool attr_set = false;
-    if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_kernel<NTOK, KS, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kSmemBudget)));
-        attr_set = true;
-    }
+    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemv_mma_q4k_kernel<NTOK, KS, NS>), kSmemBudget)) return rc;
     const uint32_t grid = (c.rows + 16u * kRowBlocks - 1) / (16u * kRowBlocks);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
@@ -614,11 +609,7 @@ int launch_m1(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok, cudaStream_t s)
     if (chunk > nb) chunk = nb;
     const uint32_t data = chunk * per_sb, red = (KS - 1) * kRowBlocks * 32 * 2 * 4;
     const uint32_t smem_bytes = off_xs + (data > red ? data : red);
-    static bool attr_set = false;
-    if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemv_mma_q4k_m1_kernel<KS, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)));
-        attr_set = true;
-    }
+    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemv_mma_q4k_m1_kernel<KS, NS>), kSmemBudget)) return rc;
     CUtensorMap wmap;
     if (int rc = weight_map(c, &wmap)) return rc;
     const uint32_t grid = (c.rows + 16u * kRowBlocks - 1) / (16u * kRowBlocks);

@@ -107,12 +107,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         return fail(HALO_CUDA_E_KERNEL, "MATMUL: ring of %d stages does not fit", NS);
     } else {
         const uint32_t smem_bytes = L::kOffData + resident_records(g) * L::kRec;
-        static bool attr_set = false;
-        if (!attr_set) {
-            HC_CUDA(cudaFuncSetAttribute(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kSmemBudget)));
-            attr_set = true;
-        }
+        if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE>), kSmemBudget)) return rc;
         const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
         float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
         CUtensorMap wmap;
@@ -128,12 +123,7 @@ int launch_resident(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
         const cudaLaunchConfig_t cfg = pdl_config(g.table.parts, smem_bytes, s, attr);
         if (c.norm_w != nullptr) {
             if constexpr (NTOK == 1) {
-                static bool norm_attr_set = false;
-                if (!norm_attr_set) {
-                    HC_CUDA(cudaFuncSetAttribute(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(kSmemBudget)));
-                    norm_attr_set = true;
-                }
+                if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE, true>), kSmemBudget)) return rc;
                 HC_CUDA(cudaLaunchKernelEx(&cfg, gemv_sk_resident_kernel<F, NTOK, NS, KS, PRE, true>, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows,
                                            g.nb, static_cast<float*>(g.partials), static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage,
                                            peer_push(c, tok0), c.norm_w, c.norm_eps));
@@ -158,12 +148,7 @@ int launch_streamed(HaloCudaCtx* ctx, const GemvCall& c, const Geometry& g, uint
     if (c.norm_w != nullptr) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL with a fused input norm: %u columns of x do not fit in shared memory", c.cols);
     const uint32_t xs_cols = std::min<uint32_t>(kMaxXSlots / 2, (kSmemBudget - L::kOffData) / kXSlot / 2);
     const uint32_t smem_bytes = L::kOffData + 2 * xs_cols * kXSlot;
-    static bool attr_set = false;
-    if (!attr_set) {
-        HC_CUDA(cudaFuncSetAttribute(gemv_sk_streamed_kernel<F, NTOK, NS, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kSmemBudget)));
-        attr_set = true;
-    }
+    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemv_sk_streamed_kernel<F, NTOK, NS, KS>), kSmemBudget)) return rc;
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
     CUtensorMap wmap;

@@ -63,6 +63,9 @@ struct HaloCudaCtx {
     void* staging[2] = {nullptr, nullptr};
     uint64_t staging_bytes = 0;
     cudaEvent_t staging_done[2][8] = {};
+    // Kernels whose dynamic shared-memory limit has been raised on THIS device (the attribute is per device, so the
+    // bookkeeping is per context, not per process).
+    std::unordered_set<const void*> smem_raised;
 };
 
 namespace halo_cuda {
@@ -72,6 +75,10 @@ int enter(HaloCudaCtx* ctx);
 /// Returns ctx scratch of at least `bytes` (grows with cudaMalloc; earlier contents are dropped; `zeroed` clears a
 /// newly allocated block in stream order).
 int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out, bool zeroed = false);
+/// Raises the dynamic shared-memory limit of `kernel` to `bytes` on ctx's device, once per context.
+int allow_dynamic_smem(HaloCudaCtx* ctx, const void* kernel, uint32_t bytes);
+/// The bookkeeping of allow_dynamic_smem without the driver call: true when (ctx, kernel) was not yet recorded.
+bool note_smem_raised(HaloCudaCtx* ctx, const void* kernel);
 
 /// A validated gemv: strides resolved to bytes, geometry checked.
 struct GemvCall {
@@ -118,6 +125,8 @@ int launch_gemv_sk_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q6kr(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, cudaStream_t s);
 int launch_gemv_mma_r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_i8(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+bool gemv_i8_supports(const GemvCall& c);
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout
 int launch_repack(uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride, uint32_t rows, uint32_t cols, cudaStream_t s);

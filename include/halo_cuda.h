@@ -58,7 +58,9 @@ extern "C" {
 #define HALO_CUDA_GEMM_TCGEN05_BF16 5 /* same with bf16 operands */
 #define HALO_CUDA_GEMV_MMA_M1 6       /* tensor-core single-row specialist (one launch per x row) */
 #define HALO_CUDA_GEMV_MMA_R 7        /* tensor-core skinny kernel over REPACKED Q6_K / Q8_0 / Q4_0 rows (halo_cuda_repack_rows) */
-#define HALO_CUDA_GEMV_VARIANT_MAX 7
+#define HALO_CUDA_GEMV_MMA_I8X2 8     /* tensor-core skinny kernel, x as two signed 8-bit digits per element (16-bit fixed point per
+                                         256-element super-block), integer MMA; raw Q4_K rows */
+#define HALO_CUDA_GEMV_VARIANT_MAX 8
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
 #define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch: the tensor-core variants then take their
@@ -83,7 +85,8 @@ typedef struct HaloCudaDeviceInfo {
 typedef struct HaloCudaVariant {
     uint32_t id;
     uint32_t op;
-    uint32_t family; /* 0 = fp32 exact order, 1 = fp32 reordered, 2 = tensor-core skinny, 3 = tensor-core single-row, 4 = fp16 GEMM */
+    uint32_t family; /* 0 = fp32 exact order, 1 = fp32 reordered, 2 = tensor-core skinny, 3 = tensor-core single-row, 4 = fp16 GEMM,
+                        5 = tensor-core skinny over repacked rows, 6 = int8 tensor-core skinny */
     const char* name;
 } HaloCudaVariant;
 
