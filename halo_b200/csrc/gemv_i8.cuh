@@ -27,7 +27,6 @@ namespace halo_cuda {
 namespace i8 {
 
 using namespace mma;
-using sk::ColumnWalk;
 
 __device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -288,20 +287,26 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    ColumnWalk prod;
-    prod.init(tb.start[cta], tb.start[cta + 1], cpu);
-    uint32_t fill_slot = 0;
-    auto refill = [&]() {  // the tile of the producer's column -> slot fill_slot (positions past the matrix have no tiles)
-        if (prod.col >= prod.end) return;
-        const uint32_t prb = prod.unit * R + r, psb = prod.k * KS + ks;
-        if (prb < n_rb && psb < nb) {
-            if (lane == 0) {
-                mbar_expect_tx(bars + fill_slot * 8u, kSlot);
-                sk::tma_item_g2s<F>(ring + fill_slot * kSlot, &wmap, psb, prb * 16u, bars + fill_slot * 8u);
-            }
-            fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
+    // This warp's tiles: for every unit the CTA's column range [c0, c1) touches, the columns k (super-block k * KS + ks) of
+    // that unit inside the range, as long as the row block and the super-block exist.  The producer (ring fill) and the
+    // consumer walk them independently; later units have later row blocks, so the first row block past the matrix ends both.
+    const uint32_t c0 = tb.start[cta], c1 = tb.start[cta + 1];
+    const uint32_t kmax = nb > ks ? min(cpu, (nb - ks + KS - 1) / KS) : 0u;  // this warp's columns in a whole unit
+    const uint32_t unit0 = c0 / cpu;
+    auto seg_end = [&](uint32_t unit) { return unit * R + r < n_rb && unit * cpu < c1 ? min(kmax, c1 - unit * cpu) : 0u; };
+    uint32_t p_unit = unit0, p_k = c0 - unit0 * cpu, p_end = seg_end(unit0), fill_slot = 0;
+    auto settle = [&]() {  // moves the producer to the unit of its next tile, if any
+        while (p_k >= p_end && (p_unit + 1) * cpu < c1 && (p_unit + 1) * R + r < n_rb) ++p_unit, p_k = 0, p_end = seg_end(p_unit);
+    };
+    settle();
+    auto refill = [&]() {  // the producer's tile -> slot fill_slot
+        if (p_k >= p_end) return;
+        if (lane == 0) {
+            mbar_expect_tx(bars + fill_slot * 8u, kSlot);
+            sk::tma_item_g2s<F>(ring + fill_slot * kSlot, &wmap, p_k * KS + ks, (p_unit * R + r) * 16u, bars + fill_slot * 8u);
         }
-        prod.step(cpu);
+        fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
+        if (++p_k >= p_end) settle();
     };
 #pragma unroll
     for (int it = 0; it < NS; ++it) refill();
@@ -326,39 +331,49 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             lost = true;
         }
     } else {
+        static_assert(NTOK == 1, "batches arrive pre-staged");
+        // The row is converted in the kernel, one super-block per warp and round.  The first round (super-blocks 0 .. 15) is
+        // what every warp's first tiles need: the block waits for it; the later rounds (their loads already in flight) finish
+        // behind an mbarrier that only the tiles of super-block 16 and up wait for.
+        const uint32_t late_warps = nb > kSkWarps ? min(nb - kSkWarps, kSkWarps) : 0u;
+        if (tid == 0 && late_warps != 0) {
+            mbar_init(smem_base + kOffXBar + 8u, late_warps);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
         float inv_rms = 1.0f;
         if constexpr (NORM) inv_rms = block_inv_rms<kSkWarps>(x, nb * 256u, norm_eps, reinterpret_cast<float*>(smem + kOffRed), tid);
-        // every warp loads its super-blocks first (two at a time), then converts them: one round trip to memory per pair
-        for (uint32_t tk = 0; tk < NTOK; ++tk) {
-            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
-            const float4* wr = reinterpret_cast<const float4*>(norm_w);
-            for (uint32_t sb0 = warp; sb0 < nb; sb0 += 2 * kSkWarps) {
-                const uint32_t sb1 = sb0 + kSkWarps;
-                float4 v[2][2], w[2][2];
-                v[0][0] = xr[sb0 * 64u + 2u * lane], v[0][1] = xr[sb0 * 64u + 2u * lane + 1u];
-                if (sb1 < nb) v[1][0] = xr[sb1 * 64u + 2u * lane], v[1][1] = xr[sb1 * 64u + 2u * lane + 1u];
-                if constexpr (NORM) {
-                    w[0][0] = wr[sb0 * 64u + 2u * lane], w[0][1] = wr[sb0 * 64u + 2u * lane + 1u];
-                    if (sb1 < nb) w[1][0] = wr[sb1 * 64u + 2u * lane], w[1][1] = wr[sb1 * 64u + 2u * lane + 1u];
-                }
+        const float4* xr = reinterpret_cast<const float4*>(x);
+        const float4* wr = reinterpret_cast<const float4*>(norm_w);
+        auto fetch = [&](uint32_t sb, float4 (&v)[2]) {
+            v[0] = xr[sb * 64u + 2u * lane], v[1] = xr[sb * 64u + 2u * lane + 1u];
+            if constexpr (NORM) {  // the CPU backend's rms_norm arithmetic (backends/cpu/ops_basic.cpp:28-30), unfused multiplies
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    if (i == 1 && sb1 >= nb) break;
-                    if constexpr (NORM) {  // the CPU backend's rms_norm arithmetic (backends/cpu/ops_basic.cpp:28-30), unfused multiplies
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            v[i][hf].x = __fmul_rn(__fmul_rn(v[i][hf].x, inv_rms), w[i][hf].x);
-                            v[i][hf].y = __fmul_rn(__fmul_rn(v[i][hf].y, inv_rms), w[i][hf].y);
-                            v[i][hf].z = __fmul_rn(__fmul_rn(v[i][hf].z, inv_rms), w[i][hf].z);
-                            v[i][hf].w = __fmul_rn(__fmul_rn(v[i][hf].w, inv_rms), w[i][hf].w);
-                        }
-                    }
-                    stage_superblock(digits, meta, v[i][0], v[i][1], i == 0 ? sb0 : sb1, NTOK, tk, lane);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float4 w = wr[sb * 64u + 2u * lane + hf];
+                    v[hf].x = __fmul_rn(__fmul_rn(v[hf].x, inv_rms), w.x);
+                    v[hf].y = __fmul_rn(__fmul_rn(v[hf].y, inv_rms), w.y);
+                    v[hf].z = __fmul_rn(__fmul_rn(v[hf].z, inv_rms), w.z);
+                    v[hf].w = __fmul_rn(__fmul_rn(v[hf].w, inv_rms), w.w);
                 }
             }
-        }
+        };
+        float4 v0[2], v1[2];
+        const bool first = warp < nb, second = warp + kSkWarps < nb;
+        if (first) fetch(warp, v0);
+        if (second) fetch(warp + kSkWarps, v1);
+        if (first) stage_superblock(digits, meta, v0[0], v0[1], warp, 1, 0, lane);
         __syncthreads();
+        if (second) {
+            stage_superblock(digits, meta, v1[0], v1[1], warp + kSkWarps, 1, 0, lane);
+            for (uint32_t sb = warp + 2 * kSkWarps; sb < nb; sb += kSkWarps) {
+                fetch(sb, v0);
+                stage_superblock(digits, meta, v0[0], v0[1], sb, 1, 0, lane);
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_base + kOffXBar + 8u) : "memory");
+        }
     }
+    bool late_ready = false;  // this warp has seen the later rounds of the x conversion complete
 
     const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + g * F::kPitch;
     float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
@@ -373,57 +388,58 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             for (int p = 0; p < (NTOK == 1 ? 1 : 4); ++p) P[gi][rr][p] = 0.0f;
 
     uint32_t slot = 0, parity = 0;
-    ColumnWalk cons;
-    cons.init(tb.start[cta], tb.start[cta + 1], cpu);
+    auto release = [&]() {
+        __syncwarp();
+        slot = slot + 1 == NS ? 0 : slot + 1;
+        parity ^= (slot == 0);
+        refill();
+    };
     // A warp that lost a copy keeps walking (its sums are garbage, the error word says so): its siblings wait for it at the barriers.
-    while (cons.col < cons.end) {
-        const uint32_t rb = cons.unit * R + r, sb = cons.k * KS + ks;
-        if (rb < n_rb) {
-            if (sb < nb) {
-                if (!lost && !mbar_wait(bars + slot * 8u, parity)) {
-                    if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
-                    lost = true;  // warp-uniform: every lane polled the same barrier
-                }
-                auto release = [&]() {
-                    __syncwarp();
-                    slot = slot + 1 == NS ? 0 : slot + 1;
-                    parity ^= (slot == 0);
-                    refill();
-                };
-                if constexpr (NTOK == 1) {
-                    float (&P1)[2] = *reinterpret_cast<float (*)[2]>(&P[0][0][0]);
-                    static_assert(sizeof(P) == 2 * sizeof(float), "single-row accumulators");
-                    F::item_one(slot0 + slot * kSlot, t, one, sb, meta, P1, release);
-                } else {
-                    F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + sb * (kDigitBytes * NTOK), meta + sb * (kMetaBytes * NTOK), P, release);
-                }
-            } else {
-                refill();  // keeps the producer in step
-            }
-            if (cons.k + 1 == cpu || cons.col + 1 == cons.end) {  // the row block, or this CTA's share of it, is done
-                float yacc[G][2];
-#pragma unroll
-                for (int gi = 0; gi < G; ++gi)
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        if constexpr (NTOK == 1) {
-                            float v = P[gi][rr][0];
-                            v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));  // (P_0 + P_1), (P_2 + P_3)
-                            v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
-                            yacc[gi][rr] = v;
-                            P[gi][rr][0] = 0.0f;
-                        } else {
-                            yacc[gi][rr] = __fadd_rn(__fadd_rn(P[gi][rr][0], P[gi][rr][1]), __fadd_rn(P[gi][rr][2], P[gi][rr][3]));
-#pragma unroll
-                            for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
-                        }
+    for (uint32_t unit = unit0, k_lo = c0 - unit0 * cpu; unit * cpu < c1; ++unit, k_lo = 0) {
+        if (unit * R + r >= n_rb) break;
+        const uint32_t k_hi = min(kmax, c1 - unit * cpu);
+        for (uint32_t k = k_lo; k < k_hi; ++k) {
+            const uint32_t sb = k * KS + ks;
+            if constexpr (!PRE) {
+                if (sb >= kSkWarps && !late_ready) {
+                    if (!mbar_wait(smem_base + kOffXBar + 8u, 0)) {
+                        if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                        lost = true;
                     }
-                sk::finish_block<G, NTOK, KS>(yacc, cons.unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, g, peer);
+                    late_ready = true;
+                }
             }
-        } else {
-            refill();
+            if (!lost && !mbar_wait(bars + slot * 8u, parity)) {
+                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                lost = true;  // warp-uniform: every lane polled the same barrier
+            }
+            if constexpr (NTOK == 1) {
+                float (&P1)[2] = *reinterpret_cast<float (*)[2]>(&P[0][0][0]);
+                static_assert(sizeof(P) == 2 * sizeof(float), "single-row accumulators");
+                F::item_one(slot0 + slot * kSlot, t, one, sb, meta, P1, release);
+            } else {
+                F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + sb * (kDigitBytes * NTOK), meta + sb * (kMetaBytes * NTOK), P, release);
+            }
         }
-        cons.step(cpu);
+        // the row block, or this CTA's share of it, is done
+        float yacc[G][2];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                if constexpr (NTOK == 1) {
+                    float v = P[gi][rr][0];
+                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));  // (P_0 + P_1), (P_2 + P_3)
+                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
+                    yacc[gi][rr] = v;
+                    P[gi][rr][0] = 0.0f;
+                } else {
+                    yacc[gi][rr] = __fadd_rn(__fadd_rn(P[gi][rr][0], P[gi][rr][1]), __fadd_rn(P[gi][rr][2], P[gi][rr][3]));
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
+                }
+            }
+        sk::finish_block<G, NTOK, KS>(yacc, unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, g, peer);
     }
     if (lost) sk::linger_after_loss();
 }
