@@ -524,7 +524,17 @@ int plan_share(uint32_t wtype, uint64_t rows, uint64_t cols, const HaloCudaUploa
         s->byte0 = b * ti.block_bytes;
     }
     s->row_bytes = s->cols / ti.block_elems * ti.block_bytes;
-    s->repack = how != nullptr && how->repack != 0 && s->rows != 0 && s->cols != 0 && s->cols % 256 == 0 && repacked_row_bytes(wtype, s->cols) != 0;
+    // The repacked layout selects the kernel variant, and with it whether a row split reduces through the peer epilogue or a
+    // collective: every rank of a row split must decide alike, so the decision looks at EVERY rank's share, not at this one.
+    bool groups = s->cols != 0 && s->cols % 256 == 0;
+    if (split == HALO_CUDA_SPLIT_ROW && world > 1) {
+        for (uint32_t r = 0; r < world && groups; ++r) {
+            uint64_t b, e;
+            even_part(cols / ti.block_elems, world, r, &b, &e);
+            groups = e > b && (e - b) * ti.block_elems % 256 == 0;
+        }
+    }
+    s->repack = how != nullptr && how->repack != 0 && s->rows != 0 && groups && repacked_row_bytes(wtype, s->cols) != 0;
     return 0;
 }
 

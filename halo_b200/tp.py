@@ -51,6 +51,19 @@ def row_ranges(wtype: int, cols: int, tp: int) -> list[tuple[int, int]]:
     return [(b * be, e * be) for b, e in split_even(cols // be, tp)]
 
 
+def repacks(wtype: int, rows: int, cols: int, mode: str, tp: int) -> bool:
+    """Whether the ranks of a split keep their shares in the repacked row layout of the tensor-core kernels (Q6_K / Q8_0 / Q4_0,
+    whole 256-element groups).  The layout selects the kernel variant and with it how a row split is reduced (peer epilogue or
+    collective), so the answer is a function of the GLOBAL shape: every rank computes the same one.  A row split repacks only
+    when every rank's K share is a non-empty whole number of groups."""
+    from .synth import Q4_0, Q6_K, Q8_0
+    if wtype not in (Q6_K, Q8_0, Q4_0) or rows == 0 or cols == 0:
+        return False
+    if mode == "row":
+        return all(e > b and (e - b) % 256 == 0 for b, e in row_ranges(wtype, cols, tp))
+    return cols % 256 == 0
+
+
 @dataclass
 class Shard:
     mode: str            # "column" | "row"

@@ -78,7 +78,7 @@ class CudaTp:
         shard = tp.shard_weight(wtype, w, rows, cols, mode, self.rank, self.world)
         buf = self.be.import_host_readonly(shard.weights.reshape(-1))
         variant = 0
-        if wtype in (synth.Q6_K, synth.Q8_0, synth.Q4_0) and shard.cols % 256 == 0 and shard.rows > 0:
+        if tp.repacks(wtype, rows, cols, mode, self.world) and shard.rows > 0:
             # what a loader does once per weight: the repacked row layout of the tensor-core kernel for these types
             st = hb.Stream(self.be, self.stream())
             packed = self.be.repack(st, wtype, hb.TensorRef.of(buf), shard.rows, shard.cols)

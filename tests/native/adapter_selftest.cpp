@@ -115,9 +115,10 @@ bool bitwise(const std::vector<float>& a, const std::vector<float>& b) {
 
 void test_registry(Pair& p, Report& r) {
     const auto v = p.gpu->variants(hb::OpId::Gemv);
-    const char* names[] = {"gemv_exact8", "gemv_warp_f32", "gemv_mma_f16x2", "gemm_tcgen05_f16", "gemm_tcgen05_bf16", "gemv_mma_m1", "gemv_mma_r"};
-    r.expect(v.size() == 7, "MATMUL has seven registered variants");
-    for (std::size_t i = 0; i < v.size() && i < 7; ++i)
+    const char* names[] = {"gemv_exact8", "gemv_warp_f32", "gemv_mma_f16x2", "gemm_tcgen05_f16", "gemm_tcgen05_bf16", "gemv_mma_m1", "gemv_mma_r",
+                           "gemv_mma_i8x2"};
+    r.expect(v.size() == 8, "MATMUL has eight registered variants");
+    for (std::size_t i = 0; i < v.size() && i < 8; ++i)
         r.expect(v[i].id == i + 1 && v[i].name == names[i] && v[i].op == hb::OpId::Gemv, std::format("variant id {} is {}", i + 1, names[i]));
     r.expect(code_of([&] { (void)p.gpu->variants(hb::OpId::RmsNorm); }) == static_cast<int>(ErrorCode::Unsupported), "variants(RMS_NORM) is Unsupported");
     r.expect(p.gpu->kind() == hb::kKindCuda && !p.gpu->lost(), "kind and lost()");
@@ -339,7 +340,8 @@ void test_fused_norm(Pair& p, Report& r) {
         maxref = std::max(maxref, std::fabs(yc[i]));
         maxerr = std::max(maxerr, std::fabs(yc[i] - yg[i]));
     }
-    r.expect(maxerr <= 1e-5f * maxref, std::format("fused input norm equals the CPU backend's rms_norm + gemv to rounding: {} vs {}", maxerr, maxref));
+    // the default Q4_K kernel rounds x to 16 bits per super-block: 2e-4 of the largest output is that family's own bar
+    r.expect(maxerr <= 2e-4f * maxref, std::format("fused input norm equals the CPU backend's rms_norm + gemv to rounding: {} vs {}", maxerr, maxref));
     a.n_vec = 1;
     a.kernel = {1};
     r.expect(code_of([&] { p.gpu->gemv(*p.gst, a); }) == static_cast<int>(halo::ErrorCode::Unsupported), "fused norm on a kernel without it: Error(Unsupported)");

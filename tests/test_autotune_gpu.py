@@ -27,7 +27,7 @@ def test_tune_persist_lookup_and_plan(tmp_path):
     for bucket, lo, hi in T_BUCKETS[:2]:
         op = CudaGemvTunable(be, synth.Q4_K, rows, cols, hi, bucket, copies=2)
         names = {c.get("variant") for c in op.candidates()}
-        assert {capi.GEMV_EXACT8, capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2} <= names and capi.GEMM_TCGEN05_F16 not in names
+        assert {capi.GEMV_EXACT8, capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2, capi.GEMV_MMA_I8X2} <= names and capi.GEMM_TCGEN05_F16 not in names
         results[bucket] = tune(db, key, [op], opts)[0]
         assert results[bucket].winner is not None
         assert all(c.valid for c in results[bucket].candidates), "every registered decode variant must pass validation on Q4_K"
@@ -52,4 +52,4 @@ def test_tune_persist_lookup_and_plan(tmp_path):
     a.n_vec = 1
     assert be.resolve_variant(a) == plan["1"].get("variant")
     be.plan_clear()
-    assert be.resolve_variant(a) == capi.GEMV_MMA_F16X2
+    assert be.resolve_variant(a) == capi.GEMV_MMA_I8X2

@@ -68,11 +68,11 @@ def test_gemm_gate_only_allow_gemm_takes_the_gemm(hz):
     xb = be.allocate(m * k * 4)
     yb = be.allocate(m * n * 4)
     a = hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wb), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m)
-    assert be.resolve_variant(a) == capi.GEMV_MMA_F16X2
+    assert be.resolve_variant(a) == capi.GEMV_MMA_I8X2
     a.allow_gemm = True
     assert be.resolve_variant(a) == capi.GEMM_TCGEN05_F16
     a.n_vec = 8
-    assert be.resolve_variant(a) == capi.GEMV_MMA_F16X2          # decode-sized batches never take the GEMM
+    assert be.resolve_variant(a) == capi.GEMV_MMA_I8X2           # decode-sized batches never take the GEMM
 
 
 def test_gemm_config2_full_size_against_the_skinny_kernel(hz):

@@ -127,7 +127,8 @@ def test_matmul_over_an_uploaded_operand(be, model, checker, t, n_vec):
     share = upload_matrix(be, st, f, info, capi.SPLIT_COLUMN, 1, 3)
     part = want[:, share.row0:share.row0 + share.rows]
     assert np.array_equal(bits(product(share.ref(), capi.GEMV_EXACT8, share.rows)), bits(part))
-    assert np.max(np.abs(product(share.ref(), 0, share.rows) - part)) <= 1e-5 * np.max(np.abs(want))
+    # (Q4_K: the default is the int8 family, which rounds x to 16 bits per super-block)
+    assert np.max(np.abs(product(share.ref(), 0, share.rows) - part)) <= (2e-4 if t == synth.Q4_K else 1e-5) * np.max(np.abs(want))
 
 
 def test_upload_refusals(be, model):

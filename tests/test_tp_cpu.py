@@ -176,3 +176,27 @@ def test_two_gloo_ranks_column_and_row_split(oracle_c):
         assert np.array_equal(bits(y_col), bits(full))                       # column split: bitwise
         assert np.max(np.abs(y_row - full)) <= 1e-5 * np.max(np.abs(full))   # row split + all-reduce: bounded
     assert np.array_equal(bits(results[0][2]), bits(results[1][2]))          # every rank holds the same reduced y
+
+
+def test_every_rank_of_a_split_chooses_the_same_kernel_layout():
+    """The repacked layout selects the kernel variant, and the variant selects how a row split is reduced (peer epilogue or
+    collective): ranks that disagreed would wait for each other in different protocols.  With blocks of 32 elements the K
+    shares can be uneven across ranks (K = 544 over two ranks: 288 and 256 columns), so the decision must come from the
+    global shape -- in the Python split and in the loader of the C ABI alike."""
+    from halo_b200 import capi, gguf
+    cases = [(synth.Q8_0, 40, 544, 2), (synth.Q4_0, 40, 544, 2), (synth.Q8_0, 40, 1536, 4), (synth.Q8_0, 40, 1536, 2), (synth.Q6_K, 40, 5120, 8),
+             (synth.Q4_0, 40, 768, 3), (synth.Q8_0, 40, 17408, 4), (synth.Q6_K, 3, 512, 4), (synth.Q4_K, 40, 5120, 8)]
+    for wtype, rows, cols, world in cases:
+        for mode, split in (("row", capi.SPLIT_ROW), ("column", capi.SPLIT_COLUMN)):
+            want = tp.repacks(wtype, rows, cols, mode, world)
+            variants = set()
+            for rank in range(world):
+                m = gguf.matrix_share(wtype, rows, cols, split, rank, world, repack=True)
+                if m.rows and m.cols:  # a rank without rows holds nothing and launches nothing
+                    variants.add(m.variant_id)
+            assert len(variants) <= 1, (wtype, rows, cols, world, mode)
+            if variants:
+                assert (variants == {capi.GEMV_MMA_R}) == want, (wtype, rows, cols, world, mode)
+    assert not tp.repacks(synth.Q8_0, 40, 544, "row", 2)       # 288 + 256 columns: one rank could repack, the other not
+    assert tp.repacks(synth.Q8_0, 40, 1536, "row", 2) and not tp.repacks(synth.Q8_0, 40, 1536, "row", 4)
+    assert tp.repacks(synth.Q6_K, 40, 5120, "row", 8)           # 3,3,3,3,2,2,2,2 super-blocks: all whole groups

@@ -52,11 +52,12 @@ def test_noalloc_lm_head_equals_regular_lm_head_twice_in_a_row():
         assert np.array_equal(got[1].view(np.uint32), want[1].view(np.uint32))
         assert np.array_equal(got[2], want[2])
         assert got[0][n_vec - 1, 2] == 1 and got[2][n_vec - 1] == 0
-        # and the default kernels (context scratch allowed) agree with it to rounding: same ids, logits within 1e-5 of the largest
+        # and the default kernels (context scratch allowed) agree with it to their own rounding: same ids, logits within 2e-4 of the
+        # largest (Q4_K's default is the int8 family, 16-bit fixed-point x) or 1e-5 (a kernel named by the caller)
         free = _run(be, st, be.lm_head, wtype, w, x, rows, cols, valid, variant)
         ok = np.isfinite(want[1])
         assert np.array_equal(free[2], want[2])
-        assert np.max(np.abs(free[1][ok] - want[1][ok])) <= 1e-5 * np.max(np.abs(want[1][ok]))
+        assert np.max(np.abs(free[1][ok] - want[1][ok])) <= (2e-4 if variant == 0 else 1e-5) * np.max(np.abs(want[1][ok]))
 
 
 def test_noalloc_lm_head_rejects_what_does_not_fit_and_needs_a_logits_buffer():
