@@ -32,8 +32,8 @@ sys.path.insert(0, str(ROOT))
 N_ROWS, K_COLS = 17408, 5120
 COPIES = 16
 PREFILL_M = 2048
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel on this shape (ncu, see profiles/)
-NCU_DRAM_BYTES_PER_LAUNCH = 50_198_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel on this shape (one ncu capture)
+NCU_DRAM_BYTES_PER_LAUNCH = 50_189_312
 FALLBACK_HBM_GBS, FALLBACK_TFLOPS = 6650.0, 1590.0
 
 
@@ -111,21 +111,65 @@ def cpu_pass(chk, w_copies, x, threads):
     return y
 
 
-def cpu_baseline(copies: int, passes: int):
+def cpu_baseline(copies: int = 4, passes: int = 6):
+    """The reference's own CPU backend on the headline workload (Q4_K 17408 x 5120, M = 1), all host threads: one warm pass over
+    every copy, then `passes` timed passes (24 calls with the defaults)."""
     import oracle
     from halo_b200 import synth
     chk = oracle.best_checker()
     threads = chk.default_threads()
     w, x = make_inputs(0)
     ws = [w.copy() for _ in range(copies)]
-    cpu_pass(chk, ws[:1], x, threads)  # warm-up
+    cpu_pass(chk, ws, x, threads)  # warm-up: the thread pool is up, every copy has been touched
     t0 = time.perf_counter()
     for _ in range(passes):
         cpu_pass(chk, ws, x, threads)
     dt = time.perf_counter() - t0
     wbytes = N_ROWS * synth.row_bytes(synth.Q4_K, K_COLS)
     return {"value": passes * copies * wbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": chk.kind,
-            "sample": f"{passes} passes over {copies} copies of the Q4_K {N_ROWS}x{K_COLS} matrix, M=1 ({passes * copies} calls)"}, dt
+            "sample": f"{passes} passes over {copies} copies of the Q4_K {N_ROWS}x{K_COLS} matrix, M=1 ({passes * copies} calls after a warm pass)"}, dt
+
+
+def cpu_baselines_other_configs():
+    """The same CPU backend on a bounded sample of every other configuration (one warm call, then `calls` timed): the down-projection
+    shapes at M = 1, 4, 8; the prefill GEMM at M = 2048 on a 512-row slice of N; one Gated-DeltaNet and one GQA layer of the token
+    sweep at M = 1; the Q4_0 FFN shape and an 8192-row slab of the output head at M = 16."""
+    import oracle
+    from halo_b200 import synth
+    chk = oracle.best_checker()
+    threads = chk.default_threads()
+    out = []
+
+    def timed(wtype, n, k, m, calls):
+        w = synth.quant_weights(wtype, n, k, 3, 1)
+        x = synth.activations(m, k, 3, 2)
+        chk.gemv(wtype, w, x, n, k, threads=threads)
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            chk.gemv(wtype, w, x, n, k, threads=threads)
+        return (time.perf_counter() - t0) / calls, n * synth.row_bytes(wtype, k)
+
+    for name, wtype in (("cfg1 q6_k down", synth.Q6_K), ("cfg1 q8_0 down", synth.Q8_0)):
+        for m in (1, 4, 8):
+            dt, nbytes = timed(wtype, 5120, 17408, m, 4)
+            out.append({"config": name, "m": m, "value": nbytes / dt / 1e9, "unit": "GB/s", "sample": "4 calls, full shape 5120 x 17408"})
+    dt, _ = timed(synth.Q4_K, 512, 5120, PREFILL_M, 2)
+    out.append({"config": "cfg2 q4_k prefill", "m": PREFILL_M, "value": 2.0 * PREFILL_M * 512 * 5120 / dt / 1e12, "unit": "TFLOP/s",
+                "sample": "2 calls on a 512-row slice of N = 17408 (the CPU's time is linear in N)"})
+    gdn, gqa = sweep_layers()
+    for name, layer in (("cfg3 one GDN layer", gdn), ("cfg3 one GQA layer", gqa)):
+        secs = nbytes = 0.0
+        for members, wtype, k, _ in layer:
+            for _, n in members:
+                dt, b = timed(wtype, n, k, 1, 2)
+                secs, nbytes = secs + dt, nbytes + b
+        out.append({"config": name, "m": 1, "value": nbytes / secs / 1e9, "unit": "GB/s", "sample": "every projection of the layer, 2 calls each"})
+    dt, nbytes = timed(synth.Q4_0, 17408, 5120, 16, 3)
+    out.append({"config": "cfg4 q4_0 ffn gate / up", "m": 16, "value": nbytes / dt / 1e9, "unit": "GB/s", "sample": "3 calls, full shape"})
+    dt, nbytes = timed(synth.Q4_0, 8192, 5120, 16, 3)
+    out.append({"config": "cfg4 q4_0 head", "m": 16, "value": nbytes / dt / 1e9, "unit": "GB/s",
+                "sample": "3 calls on one 8192-row slab of the 151936-row head (the CPU walks the head slab by slab)"})
+    return {"cores": threads, "kind": chk.kind, "rows": out}
 
 
 def run_reference(args) -> None:
@@ -157,34 +201,29 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-# BASELINE config 3, one layer of each kind: (name, type, N, K, split).  GDN layers: qkv / z / beta / alpha / out; GQA layers:
-# q / k / v / o; every layer: FFN gate / up / down.  attn_v and ffn_down are Q6_K, everything else Q4_K.
+# The per-token decode weight sweep: a 64-layer hybrid stack (48 Gated-DeltaNet + 16 GQA layers, hidden 5120, FFN 17408) in
+# which every projection is a matmul.  Projections that read the same x are one grouped operand (the reference's fused qkv,
+# beta|alpha and gate|up operands, src/models/qwen35.cpp:79-96, 220-253): one launch instead of one per member.
+#   (members [(name, N)], type, K, split)
 def sweep_layers():
     from halo_b200 import synth
     q4, q6 = synth.Q4_K, synth.Q6_K
-    ffn = [("ffn_gate", q4, 17408, 5120, "column"), ("ffn_up", q4, 17408, 5120, "column"), ("ffn_down", q6, 5120, 17408, "row")]
-    gdn = [("gdn_qkv", q4, 10240, 5120, "column"), ("gdn_z", q4, 6144, 5120, "column"), ("gdn_beta", q4, 48, 5120, "column"),
-           ("gdn_alpha", q4, 48, 5120, "column"), ("gdn_out", q4, 5120, 6144, "row")] + ffn
-    gqa = [("attn_q", q4, 5120, 5120, "column"), ("attn_k", q4, 1024, 5120, "column"), ("attn_v", q6, 1024, 5120, "column"),
-           ("attn_o", q4, 5120, 5120, "row")] + ffn
+    ffn = [([("ffn_gate", 17408), ("ffn_up", 17408)], q4, 5120, "column"), ([("ffn_down", 5120)], q6, 17408, "row")]
+    gdn = [([("gdn_qkv", 10240), ("gdn_z", 6144), ("gdn_beta", 48), ("gdn_alpha", 48)], q4, 5120, "column"), ([("gdn_out", 5120)], q4, 6144, "row")] + ffn
+    gqa = [([("attn_q", 5120), ("attn_k", 1024)], q4, 5120, "column"), ([("attn_v", 1024)], q6, 5120, "column"),
+           ([("attn_o", 5120)], q4, 5120, "row")] + ffn
     return gdn, gqa
 
 
-def time_token_slice(layers, m: int, steps: int, world: int):
-    """One x row set through every projection of `layers`, `steps` times: ms per pass (max over ranks) and whether the pass
-    ran as a CUDA graph."""
+def time_token_pass(projs, xs_of, m: int, steps: int, world: int):
+    """One x row set through every projection, `steps` times: ms per pass (max over ranks) and whether the pass ran as a CUDA graph."""
     import torch
     import torch.distributed as dist
-    xs = {}
-    for projs in layers:
-        for _, p in projs:
-            if p.shard.cols not in xs:
-                xs[p.shard.cols] = torch.randn((m, p.shard.cols), device="cuda", dtype=torch.float32)
+    xs = xs_of(m)
 
     def one_token():
-        for projs in layers:
-            for _, p in projs:
-                p(xs[p.shard.cols])
+        for p in projs:
+            p(xs[p.shard.cols])
 
     for _ in range(3):
         one_token()
@@ -224,49 +263,106 @@ def time_token_slice(layers, m: int, steps: int, world: int):
     return ms, graphed
 
 
-def tp_sweep(local_rank: int, rank: int, world: int, steps: int):
-    """Per-token decode weight sweep over an 8-layer slice (6 Gated-DeltaNet + 2 GQA layers) of the 64-layer stack of
-    BASELINE config 3, tensor-parallel over `world` GPUs: column split for qkv / gate / up, row split for out / o / down.
-    With more than one GPU the row splits are timed twice: partial products + NCCL all-reduce, and the matmul kernel's
-    peer-memory epilogue (rows pushed to the peers over NVLink, added by a small kernel).  Aggregate weight GB/s
-    includes the reductions."""
-    from halo_b200 import synth, tp_cuda
+def tp_sweep(local_rank: int, rank: int, world: int, steps: int, n_layers: int = 64):
+    """The full per-token decode weight sweep, tensor-parallel over `world` GPUs: column split for the grouped qkv / gate|up
+    operands, row split for out / o / down.  With more than one GPU the row splits are timed twice: partial products + NCCL
+    all-reduce, and the matmul kernel's peer-memory epilogue (rows pushed to the peers over NVLink, added by a small kernel).
+    Every distinct projection is also checked against the single-GPU product of the same weights (largest relative error)."""
+    import torch
+    import torch.distributed as dist
+
+    from halo_b200 import synth, tp, tp_cuda
     rt = tp_cuda.CudaTp(local_rank, rank, world)
+    one = tp_cuda.CudaTp(local_rank, 0, 1) if world > 1 else None
     gdn, gqa = sweep_layers()
-    host, out, total_bytes = {}, {}, 0
-    for how in (("nccl", "peer_epilogue") if world > 1 else ("none",)):
-        if how == "peer_epilogue":
-            rt.enable_peer_reduce(4 * 5120)  # the widest row-split result: 4 x rows of 5120
-        layers, total_bytes = [], 0
-        for li in range(8):
-            projs = []
-            for name, wtype, n, k, mode in (gqa if li % 4 == 3 else gdn):
-                key = (wtype, n, k)
-                if key not in host:
-                    host[key] = synth.quant_weights(wtype, n, k, 7, len(host) + 1)
-                projs.append((name, rt.load(wtype, host[key], n, k, mode)))
-                total_bytes += n * synth.row_bytes(wtype, k)
-            layers.append(projs)
+    host, loaded, total_bytes, launches = {}, [], 0, 0
+
+    def host_w(wtype, n, k):
+        key = (wtype, n, k)
+        if key not in host:
+            host[key] = synth.quant_weights(wtype, n, k, 7, len(host) + 1)
+        return host[key]
+
+    if world > 1:
+        rt.enable_peer_reduce(4 * 5120)  # the widest row-split result: 4 x rows of 5120
+    # every layer owns its weights in HBM (no reuse through L2); (shard, buffer, variant) are shared by the two reduction modes
+    for li in range(n_layers):
+        for members, wtype, k, mode in (gqa if li % 4 == 3 else gdn):
+            ws = [(host_w(wtype, n, k), n) for _, n in members]
+            if mode == "column":
+                proj, _ = rt.load_group(wtype, ws, k)
+            else:
+                proj = rt.load(wtype, ws[0][0], ws[0][1], k, "row")
+            loaded.append((proj.shard, proj.buf, proj.variant))
+            total_bytes += sum(n * synth.row_bytes(wtype, k) for _, n in members)
+            launches += 1
+
+    def projections(fused: bool):
+        keep, rt.peers = rt.peers, (rt.peers if fused else None)
+        out = [rt._projection(sh, buf, variant) for sh, buf, variant in loaded]
+        rt.peers = keep
+        return out
+
+    def xs_of(m):
+        torch.manual_seed(1234 + m)
+        return {k: torch.randn((m, k), device="cuda", dtype=torch.float32) for k in (5120, 6144, 17408)}
+
+    out = {}
+    modes = (("nccl", False), ("peer_epilogue", True)) if world > 1 else (("none", False),)
+    for how, fused in modes:
+        projs = projections(fused)
         for m in (1, 4):
-            ms, graphed = time_token_slice(layers, m, steps, world)
+            ms, graphed = time_token_pass(projs, xs_of, m, steps, world)
             out[f"m{m}" if how != "peer_epilogue" else f"m{m}_peer_epilogue"] = {
-                "ms_per_token_slice": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9,
-                "launches_per_token_slice": sum(len(p) for p in layers), "allreduces_per_token_slice": 16 if how == "nccl" else 0,
+                "ms_per_token": ms, "weight_gbs": total_bytes / (ms * 1e-3) / 1e9, "launches_per_token": launches,
                 "row_split_reduction": how, "cuda_graph": graphed}
-        for projs in layers:
-            for _, p in projs:
-                rt._weights.pop(id(p.shard)).free()
-    out["workload"] = (f"cfg3 slice: 8 of 64 layers (6 GDN + 2 GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K weights in total, "
-                       f"tp={world}: column split qkv/gate/up, row split + reduction out/o/down")
+    # parity: the layer-0 instance of every distinct projection against the single-GPU product of the same weights
+    parity = {}
+    if world > 1:
+        xs = xs_of(4)
+        seen = set()
+        for how, fused in modes:
+            worst = 0.0
+            projs = projections(fused)
+            idx = 0
+            for li in range(min(n_layers, 4)):
+                for members, wtype, k, mode in (gqa if li % 4 == 3 else gdn):
+                    key = (how, tuple(members), k)
+                    p = projs[idx]
+                    idx += 1
+                    if key in seen:
+                        continue
+                    seen.add(key)
+                    y = p(xs[k])
+                    at = 0
+                    for (name, n) in members:
+                        full = one.load(wtype, host_w(wtype, n, k), n, k, "column")(xs[k])
+                        if mode == "row":
+                            got, want = y, full
+                        else:
+                            n0, n1 = tp.column_ranges(n, world)[rank]
+                            got, want = y[:, at:at + (n1 - n0)], full[:, n0:n1]
+                            at += n1 - n0
+                        if want.numel():
+                            worst = max(worst, float((got - want).abs().max() / full.abs().max()))
+                        one._weights.popitem()[1].free()
+            t = torch.tensor([worst], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            parity[how] = float(t.item())
+    out["parity_rel_err_vs_single_gpu"] = parity
+    out["workload"] = (f"cfg3: {n_layers} layers ({n_layers - n_layers // 4} GDN + {n_layers // 4} GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K "
+                       f"weights per token, tp={world}: column split of the grouped qkv / gate|up operands, row split + reduction out / o / down")
     out["scaling"] = "strong"
+    for _, buf, _ in loaded:
+        buf.free()
     rt.close()
     return out
 
 
 def decode_shapes(be, st, rank: int, world: int, reps: int):
-    """The other decode-shaped configurations, one line each: BASELINE config 1 (Q6_K / Q8_0 down projection, M = 1, 4, 8)
-    and config 4 (Q4_0 MTP head: FFN shape and the vocabulary-split output head with an all-gather of the logits,
-    M = 16).  Weights of these three types are repacked once at load, like any loader of this backend does; a
+    """The other decode-shaped configurations, one line each: the Q6_K / Q8_0 down projection 5120 x 17408 at M = 1, 4, 8, and the
+    Q4_0 MTP-head layer at M = 16 (eh_proj, q / k / v / o, gate / up / down, and the vocabulary-split LM head -- matmul + argmax -- with
+    an all-gather of the logits).  Weights of these three types are repacked once at load, like any loader of this backend does; a
     step cycles enough distinct weight copies to exceed L2.  Timed with CUDA events on the launching stream."""
     import torch
     import torch.distributed as dist
@@ -277,7 +373,10 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
     pk = peaks()
     vocab = 151936
     cases = [("cfg1 q6_k down", synth.Q6_K, 5120, 17408, (1, 4, 8), False), ("cfg1 q8_0 down", synth.Q8_0, 5120, 17408, (1, 4, 8), False),
-             ("cfg4 q4_0 ffn", synth.Q4_0, 17408, 5120, (16,), False), ("cfg4 q4_0 head, vocab split", synth.Q4_0, vocab // world, 5120, (16,), True)]
+             ("cfg4 q4_0 eh_proj", synth.Q4_0, 5120, 10240, (16,), False), ("cfg4 q4_0 attn q / o", synth.Q4_0, 5120, 5120, (16,), False),
+             ("cfg4 q4_0 attn k / v", synth.Q4_0, 1024, 5120, (16,), False), ("cfg4 q4_0 ffn gate / up", synth.Q4_0, 17408, 5120, (16,), False),
+             ("cfg4 q4_0 ffn down", synth.Q4_0, 5120, 17408, (16,), False),
+             ("cfg4 q4_0 lm_head (matmul + argmax), vocab split", synth.Q4_0, vocab // world, 5120, (16,), True)]
     out = []
     e0, e1 = C.c_void_p(), C.c_void_p()
     lib.halo_cuda_event_create(ctx, C.byref(e0))
@@ -285,7 +384,7 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
     for name, wtype, n, k, ms_list, gather in cases:
         w = synth.quant_weights(wtype, n, k, 11 + rank, 1)
         wbytes = w.nbytes
-        copies = max(1, min(4, int(300e6 // wbytes)))
+        copies = max(2, min(128, -(-int(300e6) // wbytes)))  # at least 300 MB of distinct weights per cycle: more than twice L2
         raw = be.import_host_readonly(w.reshape(-1))
         packed = [be.repack(st, wtype, hb.TensorRef.of(raw), n, k) for _ in range(copies)]
         st.wait()
@@ -295,13 +394,20 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
             yb = be.allocate(m * n * 4)
             structs = [be._gemv_struct(hb.GemvArgs(wtype, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, capi.GEMV_MMA_R),
                                        "MATMUL", False) for b in packed]
+            heads = []
+            if gather:  # the LM head proper: the matmul over this rank's vocabulary shard, the argmax of its rows, the shard's row offset
+                resb = be.allocate(m * 12)
+                for g in structs:
+                    h = capi.LmHead()
+                    h.gemv, h.result, h.ids, h.valid_rows, h.row_offset = g, resb.ptr, None, 0, rank * n
+                    heads.append(h)
             yt = torch.empty((m, n), dtype=torch.float32, device="cuda")
             full = torch.empty((world, m, n), dtype=torch.float32, device="cuda") if gather and world > 1 else None
             ts = torch.cuda.ExternalStream(st.handle)
 
             def one():
-                for g in structs:
-                    rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+                for i, g in enumerate(structs):
+                    rc = lib.halo_cuda_lm_head(ctx, C.byref(heads[i]), st.handle) if heads else lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
                     if rc != 0:
                         raise hb.HaloError(rc, capi.last_error())
                     if full is not None:  # the logits of every shard on every rank
@@ -342,6 +448,8 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
                         "rel_err_vs_exact": float(np.max(np.abs(y - ye)) / np.max(np.abs(ye)))})
             xb.free()
             yb.free()
+            if heads:
+                resb.free()
         for b in packed:
             b.free()
         raw.free()
@@ -596,7 +704,18 @@ def run_ours(args) -> None:
         for _ in range(1 if args.profile else 3):
             prefill_pass()
         pms = timed(prefill_pass, psteps) / psteps
-        # parity of what was timed: 8 tokens against the tensor-core skinny kernel (near-fp32 accuracy)
+        # parity of what was timed against the oracle: all M x rows on a 128-row slice of N (the CPU's cost is linear in N)
+        rel_oracle = None
+        if rank == 0 and not args.profile:
+            import oracle
+            n_slice = 128
+            y_all = np.empty((pm, N_ROWS), np.float32)
+            be.download(st, hb.TensorRef.of(ypb), y_all)
+            st.wait()
+            ref = oracle.best_checker().gemv(synth.Q4_K, w.reshape(N_ROWS, rb)[:n_slice], xp, n_slice, K_COLS)
+            rel_oracle = float(np.max(np.abs(y_all[:, :n_slice] - ref)) / np.max(np.abs(ref)))
+            del y_all
+        # and 8 tokens over all of N against the tensor-core skinny kernel of the fp16 family (near-fp32 accuracy)
         yg = np.empty((8, N_ROWS), np.float32)
         be.download(st, hb.TensorRef(ypb, 0, 8 * N_ROWS * 4), yg)
         chk = hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[0]), hb.TensorRef.of(xpb), hb.TensorRef.of(ypb), N_ROWS, K_COLS, 8,
@@ -611,6 +730,7 @@ def run_ours(args) -> None:
         prefill = {"metric": "q4_k_mul_mat_tflops_m2048", "value": tf, "unit": "TFLOP/s", "ms_per_call": pms,
                    "variant": {i: n for i, n, _ in be.variants(capi.OP_GEMV)}.get(pvariant, str(pvariant)), "dtype": "f16 operands, f32 accumulate",
                    "rel_err_vs_skinny_kernel": float(np.max(np.abs(yg - ys)) / np.max(np.abs(ys))),
+                   "rel_err_vs_oracle": rel_oracle, "oracle_sample": f"all {pm} x rows on the first 128 of {N_ROWS} W rows",
                    "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pkk["bf16_tflops"], "unit": "TFLOP/s",
                                 "frac": tf / world / pkk["bf16_tflops"], "frac_of_sustained": tf / world / pkk["bf16_tflops_sustained"],
                                 "traffic": None, "peak_source": pkk["source"], "flops_per_launch": flops},
@@ -676,16 +796,33 @@ def run_ours(args) -> None:
         if world > 1:
             dist.destroy_process_group()
         return
-    cpu = None if args.profile else cpu_baseline(4, 3)[0]
+    cpu = None
+    if not args.profile:
+        cpu = cpu_baseline()[0]
+        cpu["by_config"] = cpu_baselines_other_configs()
+    # compact copies of the other halves of the metric under `config` (the detailed objects follow as keys of their own)
+    r3 = lambda v: None if v is None else round(float(v), 4)  # noqa: E731
+    summary = {}
+    if prefill is not None:
+        summary["prefill_q4k_tcgen05"] = {"m2048_tflops": r3(prefill["value"]), "m2048_ms": r3(prefill["ms_per_call"]),
+                                          "m2048_frac_of_bf16_burst": r3(prefill["roofline"]["frac"]),
+                                          "by_m": [{"m": r["m"], "ms": r3(r["ms_per_call"]), "tflops_per_gpu": r3(r["tflops_per_gpu"])} for r in prefill["by_m"]],
+                                          "column_split": prefill.get("column_split"), "rel_err_vs_oracle": prefill.get("rel_err_vs_oracle")}
+    if shapes is not None:
+        summary["decode_shapes"] = [{"shape": r["shape"], "m": r["m"], "us": r3(r["us_per_call"]), "frac_of_hbm": r3(r["frac_of_hbm_per_gpu"]),
+                                     "rel_err": r["rel_err_vs_exact"]} for r in shapes]
+    if sweep is not None:
+        summary["tp_sweep"] = {k: ({"ms": r3(v["ms_per_token"]), "gbs": r3(v["weight_gbs"]), "launches": v["launches_per_token"]} if k.startswith("m") else v)
+                               for k, v in sweep.items() if k != "workload"}
     line = {
         "metric": "q4_k_mul_mat_weight_gbs_m1", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": n_warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1 per GPU, {COPIES} distinct weight copies per step",
                    "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
-                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err},
+                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err, **summary},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of this kernel and shape, profiles/",
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of one launch of this kernel on this shape",
                      "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": algo_bytes},
         "cpu_baseline": cpu,

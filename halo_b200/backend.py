@@ -202,6 +202,12 @@ class CudaBackend:
     def lost(self) -> bool:
         return bool(self.lib.halo_cuda_ctx_lost(self.ctx))
 
+    def scratch_bytes(self) -> int:
+        """Context scratch the kernels have allocated on demand so far."""
+        n = C.c_uint64()
+        _check(self.lib.halo_cuda_ctx_scratch_bytes(self.ctx, C.byref(n)))
+        return n.value
+
     def variants(self, op: int) -> list[tuple[int, str, int]]:
         n = C.c_uint32()
         arr = (capi.Variant * 16)()

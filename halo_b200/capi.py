@@ -92,6 +92,8 @@ SYMBOLS = {
     "halo_cuda_stream_destroy": (C.c_int, [_P, _P]),
     "halo_cuda_stream_sync": (C.c_int, [_P, _P, C.c_uint64]),
     "halo_cuda_ctx_lost": (C.c_int, [_P]),
+    "halo_cuda_ctx_set_peer_wait_polls": (C.c_int, [_P, C.c_uint32]),
+    "halo_cuda_ctx_scratch_bytes": (C.c_int, [_P, C.POINTER(C.c_uint64)]),
     "halo_cuda_memcpy_h2d_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),
     "halo_cuda_memcpy_d2h_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),
     "halo_cuda_memcpy_d2d_async": (C.c_int, [_P, _P, _P, C.c_uint64, _P]),

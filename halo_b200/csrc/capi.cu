@@ -176,6 +176,24 @@ uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t req
     return HALO_CUDA_GEMV_EXACT8;
 }
 
+/// The outputs of an LM head (result triples, optional ids) must not overlap x, w, the logits or each other
+/// (the no_overlap checks of src/backend/cpu_backend.cpp:146-155 for the head's operands, cpu_backend.cpp:669-720).
+int lm_head_outputs_disjoint(const GemvCall& c, const void* result, const void* ids, const char* op) {
+    const uint64_t res_bytes = uint64_t{c.n_vec} * 12, ids_bytes = ids != nullptr ? uint64_t{c.n_vec} * 4 : 0;
+    const uint64_t x_ext = (uint64_t{c.n_vec} - 1) * c.x_stride + uint64_t{c.cols} * 4;
+    const uint64_t w_ext = c.rows == 0 ? 0 : (uint64_t{c.rows} - 1) * c.w_stride + c.row_bytes;
+    const uint64_t y_ext = c.y == nullptr ? 0 : (uint64_t{c.n_vec} - 1) * c.y_stride + uint64_t{c.rows} * 4;
+    struct R { const void* p; uint64_t n; const char* name; };
+    const R outs[2] = {{result, res_bytes, "result"}, {ids, ids_bytes, "ids"}};
+    const R ins[3] = {{c.x, x_ext, "x"}, {c.w, w_ext, "w"}, {c.y, y_ext, "logits"}};
+    for (const R& o : outs)
+        for (const R& i : ins)
+            if (o.p != nullptr && i.p != nullptr && ranges_overlap(o.p, o.n, i.p, i.n))
+                return fail(HALO_CUDA_E_KERNEL, "%s: output %s overlaps operand %s", op, o.name, i.name);
+    if (ids != nullptr && ranges_overlap(ids, ids_bytes, result, res_bytes)) return fail(HALO_CUDA_E_KERNEL, "%s: output ids overlaps operand result", op);
+    return 0;
+}
+
 namespace {
 int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream_t s) {
     const uint32_t v = resolve_variant(ctx, c, requested);
@@ -437,6 +455,19 @@ int halo_cuda_stream_sync(HaloCudaCtx* ctx, HaloCudaStream stream, uint64_t time
 }
 
 int halo_cuda_ctx_lost(HaloCudaCtx* ctx) { return ctx != nullptr && ctx->lost ? 1 : 0; }
+
+int halo_cuda_ctx_scratch_bytes(HaloCudaCtx* ctx, uint64_t* bytes) {
+    if (ctx == nullptr || bytes == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    *bytes = 0;
+    for (uint64_t b : ctx->workspace_bytes) *bytes += b;
+    return 0;
+}
+
+int halo_cuda_ctx_set_peer_wait_polls(HaloCudaCtx* ctx, uint32_t polls) {
+    if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
+    ctx->peer_wait_polls = polls == 0 ? 1u << 22 : polls;
+    return 0;
+}
 
 int halo_cuda_memcpy_h2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream) {
     if (int rc = enter(ctx)) return rc;
@@ -735,19 +766,7 @@ int halo_cuda_lm_head(HaloCudaCtx* ctx, const HaloCudaLmHead* a, HaloCudaStream 
     if (a->result == nullptr) return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: operand result is empty");
     if (reinterpret_cast<uintptr_t>(a->result) % 4 != 0 || reinterpret_cast<uintptr_t>(a->ids) % 4 != 0)
         return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: result / ids are not 4-byte aligned");
-    const uint64_t res_bytes = uint64_t{c.n_vec} * 12, ids_bytes = a->ids != nullptr ? uint64_t{c.n_vec} * 4 : 0;
-    const uint64_t x_ext = (uint64_t{c.n_vec} - 1) * c.x_stride + uint64_t{c.cols} * 4;
-    const uint64_t w_ext = c.rows == 0 ? 0 : (uint64_t{c.rows} - 1) * c.w_stride + c.row_bytes;
-    const uint64_t y_ext = c.y == nullptr ? 0 : (uint64_t{c.n_vec} - 1) * c.y_stride + uint64_t{c.rows} * 4;
-    struct R { const void* p; uint64_t n; const char* name; };
-    const R outs[2] = {{a->result, res_bytes, "result"}, {a->ids, ids_bytes, "ids"}};
-    const R ins[3] = {{c.x, x_ext, "x"}, {c.w, w_ext, "w"}, {c.y, y_ext, "logits"}};
-    for (const R& o : outs)
-        for (const R& i : ins)
-            if (o.p != nullptr && i.p != nullptr && ranges_overlap(o.p, o.n, i.p, i.n))
-                return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: output %s overlaps operand %s", o.name, i.name);
-    if (a->ids != nullptr && ranges_overlap(a->ids, ids_bytes, a->result, res_bytes))
-        return fail(HALO_CUDA_E_KERNEL, "LM_HEAD: output ids overlaps operand result");
+    if (int rc = lm_head_outputs_disjoint(c, a->result, a->ids, "LM_HEAD")) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Logits go to the caller's buffer when one is given, else to context scratch; the argmax then runs over
     // exactly the values the gemv stored (cpu_backend.cpp:734-750).

@@ -66,6 +66,9 @@ struct HaloCudaCtx {
     // Kernels whose dynamic shared-memory limit has been raised on THIS device (the attribute is per device, so the
     // bookkeeping is per context, not per process).
     std::unordered_set<const void*> smem_raised;
+    // How often the reduction kernel of a row split re-reads a peer's word (about 0.2 us apart) before it declares the sender lost
+    // (about a second by default; halo_cuda_ctx_set_peer_wait_polls lowers it, which is how the tests make the wait run out).
+    uint32_t peer_wait_polls = 1u << 22;
 };
 
 namespace halo_cuda {
@@ -99,6 +102,7 @@ struct GemvCall {
 };
 int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCall* out);
 uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested);
+int lm_head_outputs_disjoint(const GemvCall& c, const void* result, const void* ids, const char* op);
 
 /// What a kernel stores for row `n` of a matmul with the GDN gates epilogue (n_v != 0), else y unchanged: the CPU backend's
 /// gdn_gates (beta_out = sigmoid(beta); g_out = a * softplus(alpha + dt_bias); backends/cpu/kernel_common.h:31-33) applied

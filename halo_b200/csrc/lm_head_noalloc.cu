@@ -64,6 +64,7 @@ extern "C" int halo_cuda_lm_head_noalloc(HaloCudaCtx* ctx, const HaloCudaLmHead*
     if (a->result == nullptr) return fail(HALO_CUDA_E_KERNEL, "LM_HEAD (no-alloc): operand result is empty");
     if (reinterpret_cast<uintptr_t>(a->result) % 4 != 0 || reinterpret_cast<uintptr_t>(a->ids) % 4 != 0)
         return fail(HALO_CUDA_E_KERNEL, "LM_HEAD (no-alloc): result / ids are not 4-byte aligned");
+    if (int rc = lm_head_outputs_disjoint(c, a->result, a->ids, "LM_HEAD (no-alloc)")) return rc;
     const uint64_t need = argmax_scratch_bytes(c.rows, c.n_vec);
     if (need > uint64_t{kNoAllocMaxParts} * kPartBytes)
         return fail(HALO_CUDA_E_UNSUPPORTED,

@@ -230,6 +230,11 @@ struct PeerPush {
 __device__ __forceinline__ unsigned long long peer_word(float v, uint32_t tag) {
     return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
 }
+/// The push of one tagged word: a relaxed system-scope store, the counterpart of the receiver's relaxed system-scope load
+/// (a plain store racing that load would be a data race in the PTX memory model; this costs the same).
+__device__ __forceinline__ void peer_store(unsigned long long* p, unsigned long long w) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
 
 /// Sums of one row block (this lane: rows g and g + 8 for its G token columns) -> y: directly when this CTA covered
 /// all of the unit's columns, else through the partial store and the last-arriver reduction.  `part` holds 2 records
@@ -299,8 +304,8 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
                 const uint64_t at = slot + uint64_t{peer.tok0 + tk} * rows;  // the pushed rows are dense: [x row][W row]
                 const unsigned long long w0 = peer_word(sum[gi][0], next), w1 = peer_word(sum[gi][1], next);
                 for (uint32_t p = 0; p < peer.world; ++p) {
-                    if (n0 < rows) peer.slots[p][at + n0] = w0;
-                    if (n1 < rows) peer.slots[p][at + n1] = w1;
+                    if (n0 < rows) peer_store(peer.slots[p] + at + n0, w0);
+                    if (n1 < rows) peer_store(peer.slots[p] + at + n1, w1);
                 }
             }
         }

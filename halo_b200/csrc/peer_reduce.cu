@@ -10,8 +10,6 @@
 namespace halo_cuda {
 namespace {
 
-constexpr uint32_t kPolls = 1u << 22;  // reads of one word (~0.25 us apart once sleeping) before its sender is declared lost
-
 __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -20,7 +18,8 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long
 
 __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t n_vec,
                                                           const unsigned long long* __restrict__ slots, uint32_t* epoch, uint32_t* blocks_done,
-                                                          uint32_t world, uint32_t capacity, uint32_t* error_word) {
+                                                          uint32_t world, uint32_t capacity, uint32_t* error_word,
+                                                          uint32_t polls /* reads of one word (~0.2 us apart once sleeping) before its sender is declared lost */) {
     const uint32_t next = *epoch + 1u, set = next & 1u;
     const uint64_t count = uint64_t{rows} * n_vec;
     const unsigned long long* base = slots + uint64_t{set} * world * capacity;
@@ -31,7 +30,7 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
             const unsigned long long* src = base + uint64_t{p} * capacity + i;
             unsigned long long w = ld_relaxed_sys(src);
             for (uint32_t n = 0; static_cast<uint32_t>(w >> 32) != next; ++n) {
-                if (n == kPolls) {
+                if (n >= polls) {
                     lost = true;
                     break;
                 }
@@ -64,7 +63,7 @@ int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, 
     const uint64_t count = uint64_t{rows} * n_vec;
     const uint32_t grid = static_cast<uint32_t>(count / 1024 < 1 ? 1 : count / 1024 > 64 ? 64 : count / 1024);
     peer_finish_kernel<<<grid, 256, 0, s>>>(y, y_stride, rows, n_vec, static_cast<const unsigned long long*>(p.slots[p.rank]), p.epoch, p.done,
-                                            p.world, p.capacity, ctx->error_word_dev);
+                                            p.world, p.capacity, ctx->error_word_dev, ctx->peer_wait_polls);
     HC_CUDA(cudaGetLastError());
     return 0;
 }

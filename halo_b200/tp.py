@@ -91,6 +91,23 @@ def shard_weight(wtype: int, w: np.ndarray, rows: int, cols: int, mode: str, ran
     raise ValueError(f"unknown split mode {mode!r}")
 
 
+def shard_group(wtype: int, members: list[tuple[np.ndarray, int]], cols: int, rank: int, tp: int) -> tuple[Shard, list[tuple[int, int]]]:
+    """Several projections that read the same x (the reference's fused qkv, beta|alpha and gate|up operands,
+    src/models/qwen35.cpp:79-96, 220-253) as ONE column-split operand: every member is split over the ranks on its own and a
+    rank's rows are its member shares back to back, so that one matmul per rank produces its slice of every member.
+    `members`: (dense rows as uint8 [rows, row_bytes], rows).  Returns the shard and, per member, (offset, rows) of its
+    slice inside the rank's y."""
+    parts, where, at = [], [], 0
+    for w, rows in members:
+        s = shard_weight(wtype, w, rows, cols, "column", rank, tp)
+        parts.append(s.weights)
+        where.append((at, s.rows))
+        at += s.rows
+    rb = row_bytes(wtype, cols)
+    weights = np.concatenate(parts, axis=0) if at else np.empty((0, rb), np.uint8)
+    return Shard("column", rank, tp, wtype, at, cols, 0, 0, weights), where
+
+
 class TpProjection:
     """y = x W^T over a tensor-parallel group.
 

@@ -88,6 +88,21 @@ class CudaTp:
         shard.weights = np.empty((0, 0), np.uint8)  # the host copy is not needed any more
         return self._projection(shard, buf, variant)
 
+    def load_group(self, wtype: int, members: list[tuple[np.ndarray, int]], cols: int) -> tuple[tp.TpProjection, list[tuple[int, int]]]:
+        """Projections that share one x, loaded as one column-split operand (one launch per rank instead of one per member);
+        returns the projection and each member's (offset, rows) inside this rank's y."""
+        shard, where = tp.shard_group(wtype, members, cols, self.rank, self.world)
+        buf = self.be.import_host_readonly(shard.weights.reshape(-1)) if shard.rows else self.be.allocate(16)
+        variant = 0
+        if tp.repacks(wtype, shard.rows, cols, "column", self.world) and shard.rows > 0:
+            st = hb.Stream(self.be, self.stream())
+            packed = self.be.repack(st, wtype, hb.TensorRef.of(buf), shard.rows, shard.cols)
+            torch.cuda.current_stream(self.device).synchronize()
+            buf.free()
+            buf, variant = packed, capi.GEMV_MMA_R
+        shard.weights = np.empty((0, 0), np.uint8)
+        return self._projection(shard, buf, variant), where
+
     def load_file(self, f: gguf.GgufFile, info: gguf.TensorInfo, mode: str) -> tp.TpProjection:
         """The same projection straight from a GGUF file: the loader cuts this rank's share out of the mapping, stages it through
         pinned memory and repacks it on the device where the kernels have a repacked layout."""
@@ -102,9 +117,11 @@ class CudaTp:
         self._weights[id(shard)] = buf
         if mode == "row" and self.peers is not None and variant_pushes(wtype, variant):
             # the matmul kernel pushes its rows to the peers and a small kernel adds them: no separate collective
-            return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v, reduce=True), None, fused=True)
-        return tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v),
-                               self.all_reduce if mode == "row" else None)
+            p = tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v, reduce=True), None, fused=True)
+        else:
+            p = tp.TpProjection(shard, lambda s, x, _b=buf, _v=variant: self.matmul(s, _b, x, _v), self.all_reduce if mode == "row" else None)
+        p.buf, p.variant = buf, variant  # what a caller needs to build the same projection with another reduction
+        return p
 
     def matmul(self, s: tp.Shard, wbuf: hb.Buffer, x: torch.Tensor, variant: int = 0, reduce: bool = False) -> torch.Tensor:
         x = x.contiguous()

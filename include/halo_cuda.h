@@ -162,6 +162,16 @@ int halo_cuda_stream_destroy(HaloCudaCtx* ctx, HaloCudaStream stream);
  * A timeout returns HALO_CUDA_E_BACKEND and marks the context lost (Backend::lost(), backend.h:517-520). */
 int halo_cuda_stream_sync(HaloCudaCtx* ctx, HaloCudaStream stream, uint64_t timeout_ns);
 int halo_cuda_ctx_lost(HaloCudaCtx* ctx); /* 1 once a wait timed out or the device faulted, else 0 */
+/* Bounds the device-side wait of halo_cuda_gemv_reduce's adding kernel: it re-reads a peer's word at most `polls` times (about
+ * 0.2 us apart; default 2^22, about a second) before it gives up, raises the context's error word and stores nothing, after which
+ * the next halo_cuda_stream_sync returns HALO_CUDA_E_BACKEND and the context is lost (Backend::lost(), backend.h:517-520).  The
+ * reference injects its failures on the host (tests/unit/runtime/test_engine_faults.cpp:102-357); this knob is the counterpart for
+ * the one wait that lives on the device.  polls == 0 restores the default. */
+int halo_cuda_ctx_set_peer_wait_polls(HaloCudaCtx* ctx, uint32_t polls);
+/* Bytes of context scratch (staged activations, split-K partials, LM-head logits and argmax partials) the context holds right now:
+ * memory the kernels allocated on demand beyond the caller's operands.  Stays 0 for a context that only ever made calls that need
+ * none (the exact / fp32 variants, HALO_CUDA_GEMV_FLAG_NO_SCRATCH, halo_cuda_lm_head_noalloc). */
+int halo_cuda_ctx_scratch_bytes(HaloCudaCtx* ctx, uint64_t* bytes);
 /* Backend::upload / download / copy (backend.h:549-552, 476-481); src of an upload must stay valid until the sync. */
 int halo_cuda_memcpy_h2d_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream);
 int halo_cuda_memcpy_d2h_async(HaloCudaCtx* ctx, void* dst, const void* src, uint64_t bytes, HaloCudaStream stream);
@@ -244,7 +254,7 @@ int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaSt
  *   slots[p]: rank p's receive buffer as mapped on this rank (own: the local pointer), 2 * world * capacity * 8 bytes
  *   epoch, done: two zeroed words of this rank's own memory
  * rows * n_vec must not exceed capacity; the ranks must issue the same sequence of reductions.  Only the tensor-core
- * skinny variants (3, 7) push; others: E_UNSUPPORTED. */
+ * skinny variants (3, 7, 8) push; others: E_UNSUPPORTED. */
 #define HALO_CUDA_MAX_PEERS 8
 typedef struct HaloCudaPeerReduce {
     uint32_t world, rank, capacity, reserved;

@@ -200,3 +200,23 @@ def test_every_rank_of_a_split_chooses_the_same_kernel_layout():
     assert not tp.repacks(synth.Q8_0, 40, 544, "row", 2)       # 288 + 256 columns: one rank could repack, the other not
     assert tp.repacks(synth.Q8_0, 40, 1536, "row", 2) and not tp.repacks(synth.Q8_0, 40, 1536, "row", 4)
     assert tp.repacks(synth.Q6_K, 40, 5120, "row", 8)           # 3,3,3,3,2,2,2,2 super-blocks: all whole groups
+
+
+def test_grouped_projections_are_the_members_side_by_side(oracle_c):
+    """qkv | z | beta | alpha as one operand: every rank's y holds its column share of each member, bitwise what the member's own
+    projection gives (a row's arithmetic never looks at other rows in the CPU order)."""
+    cols, m, ranks = 1024, 2, 3
+    sizes = [80, 48, 6, 6]
+    ws = [synth.quant_weights(synth.Q4_K, n, cols, 41, i + 1) for i, n in enumerate(sizes)]
+    x = synth.activations(m, cols, 41, 9)
+
+    def matmul(s, xl):
+        return oracle_c.gemv(s.wtype, s.weights, np.ascontiguousarray(xl), s.rows, s.cols)
+
+    for r in range(ranks):
+        shard, where = tp.shard_group(synth.Q4_K, list(zip(ws, sizes)), cols, r, ranks)
+        assert shard.rows == sum(n for _, n in where)
+        y = tp.TpProjection(shard, matmul)(x)
+        for (at, n), w, rows in zip(where, ws, sizes):
+            own = tp.TpProjection(tp.shard_weight(synth.Q4_K, w, rows, cols, "column", r, ranks), matmul)(x)
+            assert own.shape[1] == n and np.array_equal(bits(y[:, at:at + n]), bits(own))

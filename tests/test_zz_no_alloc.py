@@ -80,3 +80,34 @@ def test_noalloc_lm_head_rejects_what_does_not_fit_and_needs_a_logits_buffer():
     assert rc == capi.E_UNSUPPORTED
     assert "fixed scratch" in capi.last_error()
     st.wait()
+
+
+def test_noalloc_lm_head_takes_no_context_scratch_and_checks_aliases_like_the_regular_one():
+    """On a context of its own the allocation-free entry point leaves the context's on-demand scratch at zero bytes, where the
+    regular one grows it; and it refuses outputs that overlap an operand with the same error class."""
+    import ctypes as C
+    be = hb.CudaBackend(0)
+    st = be.create_stream()
+    wtype, rows, cols, n_vec = synth.Q4_K, 9000, 512, 3
+    w = synth.quant_weights(wtype, rows, cols, 17, 1)
+    x = synth.activations(n_vec, cols, 17, 2)
+    assert be.scratch_bytes() == 0
+    got = _run(be, st, be.lm_head_noalloc, wtype, w, x, rows, cols)
+    assert be.scratch_bytes() == 0, "the allocation-free LM head grew context scratch"
+    want = _run(be, st, be.lm_head, wtype, w, x, rows, cols, no_scratch=True)  # same kernels through the regular entry point
+    assert be.scratch_bytes() > 0  # ... which keeps its logits / argmax partials in context scratch
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[2], want[2])
+    # aliasing: result inside the logits buffer, ids inside x -- refused before anything is enqueued, by both entry points
+    wb = be.import_host_readonly(w.reshape(-1))
+    xb = be.import_host_readonly(x)
+    lb = be.allocate(n_vec * rows * 4)
+    rb = be.allocate(n_vec * 12)
+    for entry in (be.lib.halo_cuda_lm_head_noalloc, be.lib.halo_cuda_lm_head):
+        for result, ids in ((lb.ptr + 64, None), (rb.ptr, xb.ptr), (rb.ptr, rb.ptr + 4)):
+            h = capi.LmHead()
+            h.gemv.wtype, h.gemv.rows, h.gemv.cols, h.gemv.n_vec = wtype, rows, cols, n_vec
+            h.gemv.w, h.gemv.x, h.gemv.y = wb.ptr, xb.ptr, lb.ptr
+            h.result, h.ids = result, ids
+            assert entry(be.ctx, C.byref(h), st.handle) == capi.E_KERNEL, capi.last_error()
+            assert "overlaps" in capi.last_error()
+    st.wait()
