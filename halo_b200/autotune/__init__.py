@@ -8,4 +8,5 @@ here is one HALO's own ProfileLookup can open: same tables, same application id,
 from .candidate import Candidate  # noqa: F401
 from .db import DbError, ProfileDb  # noqa: F401
 from .key import OpKey, ProfileKey, b200_profile_key  # noqa: F401
-from .tuner import CandidateResult, OpTuneResult, TuneOptions, select_kernel, tune  # noqa: F401
+from .cost_model import CostEstimate, CostInputs, CostModel, calibrate_gflops_per_thread  # noqa: F401
+from .tuner import CandidateResult, OpTuneResult, TuneOptions, UnsupportedError, plan_candidates, select_kernel, tune  # noqa: F401

@@ -7,7 +7,10 @@ Behaviour follows the reference (src/autotune/tuner.cpp:106-188, tests/unit/auto
  * a candidate whose coefficient of variation exceeds max_cv (0.05) is unstable and cannot win;
  * the winner is the smallest median ns among valid and stable candidates, ties go to the smallest canonical string;
  * with no eligible candidate there is no winner and an existing stored winner stays;
- * winners are stored per backend label.
+ * winners are stored per backend label;
+ * strategies decide WHICH candidates are measured: exhaustive (all), grid (per parameter every grid_stride-th distinct value
+   plus the last), random (a seeded partial Fisher-Yates over SplitMix64: portable and pinned), heuristic (the heuristic_keep
+   best by the cost model's prediction; needs a cost model and cost inputs); bayesian is refused before any run.
 Lookup (src/autotune/lookup.cpp:72-148): an exact key match beats a compatible one; among compatible keys the fewest
 differing version-tolerant fields, then the newest; a stored winner that is not among the current candidates is skipped.
 """
@@ -18,10 +21,15 @@ from dataclasses import dataclass, field
 from typing import Protocol
 
 from .candidate import Candidate
+from .cost_model import CostEstimate, CostInputs, CostModel
 from .db import ProfileDb
 from .key import OpKey, ProfileKey
 
 MIN_WARMUP, MIN_ITERATIONS = 5, 20
+
+
+class UnsupportedError(ValueError):
+    """The reference's Error(Unsupported): a documented feature this version does not have."""
 
 
 class TunableOp(Protocol):
@@ -31,6 +39,7 @@ class TunableOp(Protocol):
     def candidates(self) -> list[Candidate]: ...
     def validate(self, c: Candidate) -> bool: ...
     def run(self, c: Candidate) -> float: ...  # one call; returns its duration in ns (device time where available)
+    # optional: def cost(self, c: Candidate) -> CostInputs | None  (what the candidate does, for the cost model)
 
 
 @dataclass
@@ -39,7 +48,12 @@ class TuneOptions:
     iterations: int = MIN_ITERATIONS
     max_cv: float = 0.05
     allow_nonconformant: bool = False
-    strategy: str = "exhaustive"
+    strategy: str = "exhaustive"  # exhaustive | grid | random | heuristic (bayesian: refused)
+    grid_stride: int = 1
+    random_budget: int = 8
+    seed: int = 0
+    heuristic_keep: int = 4
+    cost_model: CostModel | None = None
 
 
 @dataclass
@@ -50,10 +64,11 @@ class CandidateResult:
     stability: str = "unknown"  # stable | unstable
     stats: dict = field(default_factory=dict)
     rejected: str | None = None
+    predicted: CostEstimate | None = None
 
     def to_json(self) -> dict:
         return {"candidate": self.candidate.to_string(), "valid": self.valid, "measured": self.measured, "stability": self.stability,
-                "stats": self.stats, "rejected": self.rejected}
+                "stats": self.stats, "rejected": self.rejected, "predicted": self.predicted.to_json() if self.predicted else None}
 
 
 @dataclass
@@ -74,15 +89,79 @@ def sample_stats(samples: list[float]) -> dict:
             "cv": sd / mean if mean > 0 else 0.0}
 
 
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64(state: int) -> tuple[int, int]:
+    state = (state + 0x9E3779B97F4A7C15) & _M64
+    z = state
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return state, z ^ (z >> 31)
+
+
+def _op_cost(op, c: Candidate):
+    f = getattr(op, "cost", None)
+    return f(c) if f is not None else None
+
+
+def plan_candidates(all_: list[Candidate], o: TuneOptions, cost=None) -> list[Candidate]:
+    """The candidates a strategy measures, in order (src/autotune/tuner.cpp:36-104)."""
+    if o.strategy == "exhaustive":
+        return list(all_)
+    if o.strategy == "random":
+        if o.random_budget < 1:
+            raise ValueError("tune: random_budget must be >= 1 (Config)")
+        pool, k, state = list(all_), min(o.random_budget, len(all_)), o.seed & _M64
+        for i in range(k):  # j uniform-ish in [i, n): the high 64 bits of r * (n - i)
+            state, r = _splitmix64(state)
+            j = i + ((r * (len(pool) - i)) >> 64)
+            pool[i], pool[j] = pool[j], pool[i]
+        return pool[:k]
+    if o.strategy == "grid":
+        if o.grid_stride < 1:
+            raise ValueError("tune: grid_stride must be >= 1 (Config)")
+        values: dict[str, set[int]] = {}
+        for c in all_:
+            for name, v in c.params:
+                values.setdefault(name, set()).add(v)
+        kept = {name: set(sorted(vs)[::o.grid_stride]) | {max(vs)} for name, vs in values.items()}
+        return [c for c in all_ if all(v in kept[name] for name, v in c.params)]
+    if o.strategy == "heuristic":
+        if o.cost_model is None:
+            raise ValueError("tune: HEURISTIC needs a cost model (Config)")
+        if o.heuristic_keep < 1:
+            raise ValueError("tune: heuristic_keep must be >= 1 (Config)")
+        if cost is None:
+            raise ValueError("tune: HEURISTIC needs cost inputs (Config)")
+        ranked = []
+        for c in all_:
+            inputs = cost(c)
+            if inputs is None:
+                raise ValueError(f"tune: candidate {c.to_string()} has no cost inputs (Config)")
+            ranked.append((o.cost_model.estimate(inputs).total_ns, c.to_string(), c))
+        ranked.sort(key=lambda r: (r[0], r[1]))
+        return [c for _, _, c in ranked[:o.heuristic_keep]]
+    if o.strategy == "bayesian":
+        raise UnsupportedError("tune: BAYESIAN strategy is not implemented (Unsupported)")
+    raise ValueError(f"tune: unknown strategy {o.strategy!r} (Config)")
+
+
 def tune_one(op: TunableOp, options: TuneOptions) -> OpTuneResult:
-    if options.strategy != "exhaustive":
-        raise ValueError(f"tuner: strategy {options.strategy!r} is not implemented (Unsupported)")
+    if options.strategy == "bayesian":
+        raise UnsupportedError("tune: BAYESIAN strategy is not implemented (Unsupported)")
     if not options.allow_nonconformant and (options.warmup < MIN_WARMUP or options.iterations < MIN_ITERATIONS):
         raise ValueError(f"tuner: {options.warmup} warm-up + {options.iterations} timed runs is below the {MIN_WARMUP} + {MIN_ITERATIONS} the "
                          "methodology asks for; pass allow_nonconformant to override")
     results: list[CandidateResult] = []
-    for c in op.candidates():
+    everything = op.candidates()
+    if not everything:
+        return OpTuneResult(op.key, op.backend, options.strategy, [])
+    for c in plan_candidates(everything, options, lambda cand: _op_cost(op, cand)):
         cr = CandidateResult(c)
+        inputs = _op_cost(op, c)
+        if inputs is not None and options.cost_model is not None:
+            cr.predicted = options.cost_model.estimate(inputs)
         if not op.validate(c):
             cr.valid, cr.rejected = False, "validation failed"
             results.append(cr)
@@ -105,6 +184,8 @@ def tune_one(op: TunableOp, options: TuneOptions) -> OpTuneResult:
 
 def tune(db: ProfileDb, key: ProfileKey, ops: list[TunableOp], options: TuneOptions | None = None) -> list[OpTuneResult]:
     options = options or TuneOptions()
+    if options.strategy == "bayesian":  # refused up front, before any operator runs and whatever the operators offer
+        raise UnsupportedError("tune: BAYESIAN strategy is not implemented (Unsupported)")
     out = []
     for op in ops:
         r = tune_one(op, options)

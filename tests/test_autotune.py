@@ -195,3 +195,112 @@ def test_decode_buckets_share_one_numerics_family():
     plan = T.decode_family_plan(results, fam)
     # T = 1 picks family 2 (variant 3); the 2-4 bucket must stay in that family although variant 6 measured faster
     assert plan == {"1": Candidate.of(variant=3), "2-4": Candidate.of(variant=3)}
+
+
+# ---- strategies and the cost model (tests/unit/autotune/test_tuner.cpp:50-118, 206-225, 391-440) -----------------------------
+
+def _grid(a, b):
+    return [Candidate.of(chunk=x, threads=y) for x in a for y in b]
+
+
+def _texts(cs):
+    return [c.to_string() for c in cs]
+
+
+def test_strategies_exhaustive_and_grid():
+    from halo_b200.autotune import plan_candidates
+    every = _grid((16, 32, 64, 128), (1, 2, 4, 8))
+    assert plan_candidates(every, TuneOptions(strategy="exhaustive")) == every
+    g = plan_candidates(every, TuneOptions(strategy="grid", grid_stride=2))  # per dimension keep indices 0, 2 and the last
+    assert _texts(g) == ["chunk=16;threads=1", "chunk=16;threads=4", "chunk=16;threads=8", "chunk=64;threads=1", "chunk=64;threads=4",
+                         "chunk=64;threads=8", "chunk=128;threads=1", "chunk=128;threads=4", "chunk=128;threads=8"]
+    assert plan_candidates(every, TuneOptions(strategy="grid", grid_stride=1)) == every
+    with pytest.raises(ValueError):
+        plan_candidates(every, TuneOptions(strategy="grid", grid_stride=0))
+
+
+def test_random_strategy_is_seeded_and_pinned():
+    from halo_b200.autotune import plan_candidates
+    every = _grid((16, 32, 64, 128), (1, 2, 4, 8))
+    o = TuneOptions(strategy="random", random_budget=5, seed=42)
+    a = plan_candidates(every, o)
+    assert plan_candidates(every, o) == a and len(a) == 5 and len(set(_texts(a))) == 5  # same seed, same picks, no replacement
+    # the reference pins these five for seed 42 (SplitMix64 partial Fisher-Yates; tests/unit/autotune/test_tuner.cpp:82-84)
+    assert _texts(a) == ["chunk=64;threads=8", "chunk=16;threads=8", "chunk=32;threads=2", "chunk=32;threads=8", "chunk=32;threads=1"]
+    assert plan_candidates(every, TuneOptions(strategy="random", random_budget=5, seed=43)) != a
+    assert len(plan_candidates(every, TuneOptions(strategy="random", random_budget=100, seed=42))) == len(every)
+    with pytest.raises(ValueError):
+        plan_candidates(every, TuneOptions(strategy="random", random_budget=0))
+
+
+class CostedOp(FakeOp):
+    """FakeOp whose candidates also report what they cost: `predicted` ns as bytes over a 1 GB/s tier."""
+
+    def __init__(self, script, predicted, **kw):
+        super().__init__(script, **kw)
+        self.predicted = predicted
+
+    def cost(self, c):
+        from halo_b200.autotune import CostInputs
+        return CostInputs(flops=0.0, bytes=int(self.predicted[c.get("variant")]), tier="vram", parallelism=1, launches=0)
+
+
+def _unit_model():
+    from halo_b200.autotune import CostModel
+    return CostModel(bandwidth_gbps={"vram": 1.0}, bandwidth_threads=1, gflops_per_thread=1.0)
+
+
+def test_heuristic_keeps_the_best_predicted_and_bayesian_is_refused(tmp_path):
+    from halo_b200.autotune import UnsupportedError, plan_candidates
+    op = CostedOp({v: ([100.0], True) for v in (1, 2, 3, 4, 5)}, {1: 500, 2: 100, 3: 300, 4: 100, 5: 900})
+    o = TuneOptions(strategy="heuristic", heuristic_keep=3, cost_model=_unit_model())
+    assert _texts(plan_candidates(op.candidates(), o, op.cost)) == ["variant=2", "variant=4", "variant=3"]  # ties: smallest text first
+    with pytest.raises(ValueError):
+        plan_candidates(op.candidates(), TuneOptions(strategy="heuristic", heuristic_keep=3), op.cost)  # no cost model
+    with pytest.raises(ValueError):
+        plan_candidates(op.candidates(), o, None)                                                       # no cost inputs
+    db = ProfileDb(tmp_path / "p.db")
+    with pytest.raises(UnsupportedError):
+        tune(db, KEY, [op], TuneOptions(strategy="bayesian"))
+    assert sum(op.calls.values()) == 0  # refused up front: nothing ran, nothing was stored
+    with pytest.raises(UnsupportedError):
+        tune(db, KEY, [FakeOp({})], TuneOptions(strategy="bayesian"))
+    assert select_kernel(db, KEY, OP, "cuda", op.candidates()) == (None, "default")
+
+
+def test_heuristic_measures_only_the_prefilter(tmp_path):
+    # prediction and reality disagree: the prefilter keeps 1 and 2; 3 (really the fastest) is never measured -- the documented trade-off
+    op = CostedOp({1: ([900.0], True), 2: ([800.0], True), 3: ([100.0], True)}, {1: 10, 2: 20, 3: 30})
+    db = ProfileDb(tmp_path / "p.db")
+    r = tune(db, KEY, [op], TuneOptions(strategy="heuristic", heuristic_keep=2, cost_model=_unit_model()))[0]
+    assert len(r.candidates) == 2 and r.winner == Candidate.of(variant=2) and op.calls[3] == 0
+    assert r.candidates[0].predicted is not None and r.candidates[0].predicted.total_ns == 10.0
+
+
+def test_cost_model_formula_and_calibration():
+    from halo_b200.autotune import CostInputs, CostModel, calibrate_gflops_per_thread
+    m = CostModel(bandwidth_gbps={"host": 50.0}, bandwidth_threads=4, gflops_per_thread=2.0, launch_ns=100, sync_ns=10)
+    c = CostInputs(flops=8000, bytes=50000, tier="host", parallelism=2, launches=1, syncs=3)
+    e = m.estimate(c)  # compute 8000 / (2 * 2); memory 50000 / (50 * 2/4): bandwidth scales with 2 of 4 threads
+    assert (e.t_compute_ns, e.t_memory_ns, e.total_ns, e.memory_bound) == (2000.0, 2000.0, 2000.0 + 30.0 + 100.0, True)
+    c.parallelism = 8  # memory saturates at 4 threads, compute keeps scaling
+    e = m.estimate(c)
+    assert (e.t_compute_ns, e.t_memory_ns) == (500.0, 1000.0)
+    c.tier = "vram"
+    with pytest.raises(ValueError):
+        m.estimate(c)
+    c.tier, m.gflops_per_thread = "host", 0.0
+    with pytest.raises(ValueError):
+        m.estimate(c)
+    assert calibrate_gflops_per_thread(4e6, 1e6, 2) == 2.0
+    with pytest.raises(ValueError):
+        calibrate_gflops_per_thread(1, 0, 1)
+    rows = [{"tier": "host", "threads": 8, "read_gbps": 60.0}, {"tier": "vram", "threads": 8, "read_gbps": 200.0}]
+    m = CostModel.from_measurements(rows, 1.5)
+    assert m.bandwidth_gbps == {"host": 60.0, "vram": 200.0} and m.bandwidth_threads == 8
+    with pytest.raises(ValueError):
+        CostModel.from_measurements([rows[0], dict(rows[1], threads=4)], 1.0)
+    with pytest.raises(ValueError):
+        CostModel.from_measurements([dict(rows[0], read_gbps=0.0)], 1.0)
+    with pytest.raises(ValueError):
+        CostModel.from_measurements([], 1.0)
