@@ -598,6 +598,32 @@ def run_ours(args) -> None:
     variant = be.resolve_variant(calls[0])
     vname = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}[variant]
 
+    # ---- which kernel runs: the autotuner's.  The headline shape is tuned into a fresh profile database (this box has none), the
+    # database is reopened read-only and its winner installed as the backend's plan, as a host does at engine creation.
+    kernel_choice = None
+    if not args.profile and args.variant == 0:
+        import tempfile
+
+        from halo_b200.autotune import ProfileDb
+        from halo_b200.autotune import plan as tune_plan
+        one = (("1", 1, 1),)
+        with tempfile.TemporaryDirectory() as d:
+            db_path = os.path.join(d, "profile.db")
+            db = ProfileDb(db_path)
+            pkey = tune_plan.profile_key_of(be)
+            tuned = tune_plan.tune_shapes(be, db, pkey, tune_plan.BASELINE_SHAPES[:1], one)[tune_plan.BASELINE_SHAPES[0]]["1"]
+            db.close()
+            ro = ProfileDb(db_path, readonly=True)
+            ch = tune_plan.install(be, ro, pkey, tune_plan.BASELINE_SHAPES[:1], one)[0]
+            ro.close()
+        names = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}
+        kernel_choice = {"source": ch.source, "variant": names.get(ch.variant), "strategy": "exhaustive",
+                         "candidates_us": {names[r.candidate.get("variant")]: (round(r.stats["median"] / 1e3, 2) if r.measured else None)
+                                           for r in tuned.candidates},
+                         "rejected": {names[r.candidate.get("variant")]: r.rejected for r in tuned.candidates if r.rejected}}
+        variant = be.resolve_variant(calls[0])
+        vname = names[variant]
+
     def one_pass():
         for g in structs:
             rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
@@ -820,7 +846,7 @@ def run_ours(args) -> None:
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1 per GPU, {COPIES} distinct weight copies per step",
                    "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
-                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err, **summary},
+                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err, "kernel_choice": kernel_choice, **summary},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of one launch of this kernel on this shape",
                      "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,

@@ -18,7 +18,10 @@ class CudaGemvTunable:
     backend = "cuda"
 
     def __init__(self, be: hb.CudaBackend, wtype: int, rows: int, cols: int, n_vec: int, bucket: str, *, allow_gemm: bool = False,
-                 copies: int | None = None, launches_per_run: int = 8, seed: int = 0):
+                 copies: int | None = None, launches_per_run: int = 8, seed: int = 0, only_family: int | None = None):
+        """only_family: offer only the variants of one numerics family (the decode buckets of a shape must share the family of
+        its single-row winner, include/halo/backend/backend.h:300-304)."""
+        self.only_family = only_family
         self.be, self.wtype, self.rows, self.cols, self.n_vec, self.allow_gemm = be, wtype, rows, cols, n_vec, allow_gemm
         self.key = OpKey.matmul(bucket, cols, rows, synth.TYPE_NAMES[wtype])
         self.st = be.create_stream()
@@ -55,8 +58,26 @@ class CudaGemvTunable:
                 continue  # one launch per row: not a candidate for wide batches
             if vid == capi.GEMV_MMA_R and not self.wr:
                 continue  # no repacked layout for this type
+            if self.only_family is not None and _fam != self.only_family:
+                continue
             out.append(Candidate.of(variant=vid))
         return out
+
+    def close(self) -> None:
+        """Gives the operator's device buffers back."""
+        self.st.wait()
+        for b in self.wb + self.wr + [self.xb, self.yb, self.yref]:
+            b.free()
+        self.wb, self.wr = [], []
+
+    def cost(self, c: Candidate):
+        """What a candidate does, for the cost model: the reference's own accounting of a matmul
+        (include/halo/backends/cpu/traffic.h:94-99: weight bytes + 4 M K read, 4 M N written; 2 M N K flops), one launch, every SM."""
+        from .cost_model import CostInputs
+        rb = synth.row_bytes(self.wtype, self.cols)
+        nbytes = self.rows * rb + 4 * self.n_vec * self.cols + 4 * self.n_vec * self.rows
+        return CostInputs(flops=2.0 * self.n_vec * self.rows * self.cols, bytes=nbytes, tier="vram", parallelism=self.be.info().sm_count,
+                          launches=self.n_vec if c.get("variant") == capi.GEMV_MMA_M1 else 1)
 
     def _reference(self) -> np.ndarray:
         if self._ref is None:

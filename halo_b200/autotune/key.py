@@ -67,7 +67,7 @@ class OpKey:
         return OpKey("MATMUL", f"T={t_bucket},K={cols},N={rows},w={wname}")
 
 
-# decode / verify batch buckets (ADR-001 5.6) and the prefill sizes of BASELINE config 2
+# decode / verify batch buckets (ADR-001 5.6)
 T_BUCKETS: tuple[tuple[str, int, int], ...] = (("1", 1, 1), ("2-4", 2, 4), ("5-8", 5, 8), ("9-16", 9, 16))
 
 

@@ -64,18 +64,19 @@ int enter(HaloCudaCtx* ctx) {
 }
 
 int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, void** out, bool zeroed) {
-    if (bytes > ctx->workspace_bytes[slot]) {
-        // Work already enqueued may still read the old block: drain before releasing it.
+    HaloCudaCtx::Scratch& sc = ctx->scratch[stream];  // the calling stream's own set: nothing another stream runs touches it
+    if (bytes > sc.bytes[slot]) {
+        // Work already enqueued on this stream may still read the old block: drain before releasing it.
         HC_CUDA(cudaStreamSynchronize(stream));
-        if (ctx->workspace[slot] != nullptr) HC_CUDA(cudaFree(ctx->workspace[slot]));
-        ctx->workspace[slot] = nullptr;
-        ctx->workspace_bytes[slot] = 0;
+        if (sc.block[slot] != nullptr) HC_CUDA(cudaFree(sc.block[slot]));
+        sc.block[slot] = nullptr;
+        sc.bytes[slot] = 0;
         const uint64_t want = (bytes + (1u << 20) - 1) & ~uint64_t{(1u << 20) - 1};
-        HC_CUDA(cudaMalloc(&ctx->workspace[slot], want));
-        ctx->workspace_bytes[slot] = want;
-        if (zeroed) HC_CUDA(cudaMemsetAsync(ctx->workspace[slot], 0, want, stream));
+        HC_CUDA(cudaMalloc(&sc.block[slot], want));
+        sc.bytes[slot] = want;
+        if (zeroed) HC_CUDA(cudaMemsetAsync(sc.block[slot], 0, want, stream));
     }
-    *out = ctx->workspace[slot];
+    *out = sc.block[slot];
     return 0;
 }
 
@@ -309,8 +310,9 @@ int halo_cuda_ctx_destroy(HaloCudaCtx* ctx) {
             }
             cudaMemPoolDestroy(ctx->pool);
         }
-        for (void* p : ctx->workspace)
-            if (p != nullptr) cudaFree(p);
+        for (auto& kv : ctx->scratch)
+            for (void* p : kv.second.block)
+                if (p != nullptr) cudaFree(p);
         if (ctx->error_word_host != nullptr) cudaFreeHost(ctx->error_word_host);
         for (int i = 0; i < 2; ++i) {
             if (ctx->staging[i] != nullptr) cudaFreeHost(ctx->staging[i]);
@@ -420,7 +422,15 @@ int halo_cuda_stream_destroy(HaloCudaCtx* ctx, HaloCudaStream stream) {
     if (ctx == nullptr) return fail(HALO_CUDA_E_API, "null context");
     if (stream == nullptr) return 0;
     HC_CUDA(cudaSetDevice(ctx->device));
-    HC_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const auto it = ctx->scratch.find(s);
+    if (it != ctx->scratch.end()) {  // the stream's scratch goes with it, once its work has drained
+        cudaStreamSynchronize(s);
+        for (void* p : it->second.block)
+            if (p != nullptr) cudaFree(p);
+        ctx->scratch.erase(it);
+    }
+    HC_CUDA(cudaStreamDestroy(s));
     return 0;
 }
 
@@ -459,7 +469,8 @@ int halo_cuda_ctx_lost(HaloCudaCtx* ctx) { return ctx != nullptr && ctx->lost ? 
 int halo_cuda_ctx_scratch_bytes(HaloCudaCtx* ctx, uint64_t* bytes) {
     if (ctx == nullptr || bytes == nullptr) return fail(HALO_CUDA_E_API, "null argument");
     *bytes = 0;
-    for (uint64_t b : ctx->workspace_bytes) *bytes += b;
+    for (const auto& kv : ctx->scratch)
+        for (uint64_t b : kv.second.bytes) *bytes += b;
     return 0;
 }
 

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
+#include <unordered_map>
 #include <unordered_set>
 #include <vector>
 
@@ -41,12 +42,16 @@ struct HaloCudaCtx {
     cudaDeviceProp prop{};
     bool lost = false;
     // Scratch for kernels that need global memory beyond their operands (activation staging, split-K
-    // partials).  Grown on demand, reused in stream order; one thread drives a context.
+    // partials).  Grown on demand and reused in stream order, so every stream has a set of its own: calls on different
+    // streams of one context may overlap on the device without sharing counters, partials or staged x.  One thread drives a context.
     // Slot 0 serves the matmul kernels, slot 1 the LM head (its logits and argmax partials live across a matmul),
     // slot 2 the row-block counters of the balanced kernels (zeroed when allocated, left zeroed by every kernel),
     // slot 3 their partial sums.
-    void* workspace[4] = {nullptr, nullptr, nullptr, nullptr};
-    uint64_t workspace_bytes[4] = {0, 0, 0, 0};
+    struct Scratch {
+        void* block[4] = {nullptr, nullptr, nullptr, nullptr};
+        uint64_t bytes[4] = {0, 0, 0, 0};
+    };
+    std::unordered_map<cudaStream_t, Scratch> scratch;
     std::vector<halo_cuda::PlanEntry> plan;
     // One word of mapped pinned host memory that kernels OR error bits into (bit 0: a bounded device-side wait
     // expired).  The host reads it after every stream wait; a set bit marks the context lost.

@@ -168,7 +168,10 @@ int halo_cuda_ctx_lost(HaloCudaCtx* ctx); /* 1 once a wait timed out or the devi
  * reference injects its failures on the host (tests/unit/runtime/test_engine_faults.cpp:102-357); this knob is the counterpart for
  * the one wait that lives on the device.  polls == 0 restores the default. */
 int halo_cuda_ctx_set_peer_wait_polls(HaloCudaCtx* ctx, uint32_t polls);
-/* Bytes of context scratch (staged activations, split-K partials, LM-head logits and argmax partials) the context holds right now:
+/* Streams and scratch: the kernels' on-demand scratch is kept per stream, so calls on different streams of one context may overlap on
+ * the device; calls on ONE stream reuse that stream's scratch in stream order.  halo_cuda_stream_destroy releases the stream's scratch.
+ * (halo_cuda_lm_head_noalloc is the exception: its fixed array is shared by every call on the GPU.)
+ * Bytes of context scratch (staged activations, split-K partials, LM-head logits and argmax partials) the context holds right now:
  * memory the kernels allocated on demand beyond the caller's operands.  Stays 0 for a context that only ever made calls that need
  * none (the exact / fp32 variants, HALO_CUDA_GEMV_FLAG_NO_SCRATCH, halo_cuda_lm_head_noalloc). */
 int halo_cuda_ctx_scratch_bytes(HaloCudaCtx* ctx, uint64_t* bytes);
