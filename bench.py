@@ -611,10 +611,10 @@ def run_ours(args) -> None:
             db_path = os.path.join(d, "profile.db")
             db = ProfileDb(db_path)
             pkey = tune_plan.profile_key_of(be)
-            tuned = tune_plan.tune_shapes(be, db, pkey, tune_plan.BASELINE_SHAPES[:1], one)[tune_plan.BASELINE_SHAPES[0]]["1"]
+            tuned = tune_plan.tune_shapes(be, db, pkey, tune_plan.HEADLINE_SHAPES[:1], one)[tune_plan.HEADLINE_SHAPES[0]]["1"]
             db.close()
             ro = ProfileDb(db_path, readonly=True)
-            ch = tune_plan.install(be, ro, pkey, tune_plan.BASELINE_SHAPES[:1], one)[0]
+            ch = tune_plan.install(be, ro, pkey, tune_plan.HEADLINE_SHAPES[:1], one)[0]
             ro.close()
         names = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}
         kernel_choice = {"source": ch.source, "variant": names.get(ch.variant), "strategy": "exhaustive",

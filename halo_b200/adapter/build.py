@@ -1,6 +1,6 @@
 """Builds libhalo_cuda_backend.so: the C++23 `halo::backend::Backend` implementation over the C ABI.
 
-It compiles against the reference's own headers where they lie (HALO_REF_ROOT, default /root/reference); nothing of the
+It compiles against the reference's own headers where they lie ($HALO_REF_ROOT, else a directory `reference` next to this repository); nothing of the
 reference is copied.  Without the reference tree (e.g. on the GPU box) the prebuilt library that travelled with the
 tree is used as is.  Symbols of HALO's backend-neutral code (op_name, Backend::run_op, ...) stay undefined in this
 library: the HALO build, or the test that loads it, provides them.
@@ -17,8 +17,11 @@ LIB = HERE / "libhalo_cuda_backend.so"
 
 
 def ref_root() -> Path | None:
-    root = Path(os.environ.get("HALO_REF_ROOT", "/root/reference"))
-    return root if (root / "include" / "halo" / "backend" / "backend.h").exists() else None
+    env = os.environ.get("HALO_REF_ROOT")
+    for root in ([Path(env)] if env else []) + [PKG.parent.parent / "reference"]:
+        if (root / "include" / "halo" / "backend" / "backend.h").exists():
+            return root
+    return None
 
 
 def build(force: bool = False) -> Path | None:

@@ -55,12 +55,12 @@ def main() -> None:
     gbps = measure_hbm_gbps(be)
     db.record_tier_bandwidth(key, tier="vram", processor="gpu", label="hbm3e device-to-device copy (measured)", threads=be.info().sm_count,
                              buffer_bytes=1 << 30, read_gbps=gbps, write_gbps=gbps, copy_gbps=gbps)
-    shapes = P.BASELINE_SHAPES if args.shapes == "all" else P.BASELINE_SHAPES[:1]
+    shapes = P.HEADLINE_SHAPES if args.shapes == "all" else P.HEADLINE_SHAPES[:1]
     opts = TuneOptions(strategy=args.strategy, heuristic_keep=args.heuristic_keep, random_budget=args.random_budget, seed=args.seed)
     if args.strategy == "heuristic":
         # per-SM throughput calibrated on this backend's own kernel: one tuned run of the headline shape
-        probe = P.tune_shapes(be, db, key, P.BASELINE_SHAPES[:1], (("1", 1, 1),), TuneOptions())[P.BASELINE_SHAPES[0]]["1"]
-        n, k = P.BASELINE_SHAPES[0][1], P.BASELINE_SHAPES[0][2]
+        probe = P.tune_shapes(be, db, key, P.HEADLINE_SHAPES[:1], (("1", 1, 1),), TuneOptions())[P.HEADLINE_SHAPES[0]]["1"]
+        n, k = P.HEADLINE_SHAPES[0][1], P.HEADLINE_SHAPES[0][2]
         gf = calibrate_gflops_per_thread(2.0 * n * k, probe.winner_median_ns or 1e4, be.info().sm_count)
         opts.cost_model = CostModel.from_measurements([{"tier": "vram", "threads": be.info().sm_count, "read_gbps": gbps}], gf, launch_ns=2500.0)
     results = P.tune_shapes(be, db, key, shapes, options=opts)

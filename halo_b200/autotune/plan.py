@@ -15,7 +15,7 @@ from .key import T_BUCKETS, OpKey, ProfileKey, b200_profile_key
 from .tuner import OpTuneResult, TuneOptions, decode_family_plan, select_kernel, tune
 
 # (weight type, N, K) of every decode-shaped matmul the benchmark configurations name
-BASELINE_SHAPES: tuple[tuple[int, int, int], ...] = (
+HEADLINE_SHAPES: tuple[tuple[int, int, int], ...] = (
     (synth.Q4_K, 17408, 5120),                                                      # FFN gate / up: the headline
     (synth.Q4_K, 10240, 5120), (synth.Q4_K, 6144, 5120), (synth.Q4_K, 5120, 6144),   # Gated-DeltaNet qkv, z, out
     (synth.Q4_K, 5120, 5120), (synth.Q4_K, 1024, 5120), (synth.Q4_K, 48, 5120),      # attention q / o, k, beta / alpha
@@ -38,7 +38,7 @@ def profile_key_of(be: hb.CudaBackend, workload: str = "synthetic matmul shapes,
     return b200_profile_key(be.info(), workload)
 
 
-def tune_shapes(be: hb.CudaBackend, db: ProfileDb, key: ProfileKey, shapes=BASELINE_SHAPES, buckets=T_BUCKETS, options: TuneOptions | None = None,
+def tune_shapes(be: hb.CudaBackend, db: ProfileDb, key: ProfileKey, shapes=HEADLINE_SHAPES, buckets=T_BUCKETS, options: TuneOptions | None = None,
                 launches_per_run: int = 48) -> dict[tuple[int, int, int], dict[str, OpTuneResult]]:
     """Tunes every (shape, batch bucket) and stores the winners.  A timed sample is `launches_per_run` back-to-back launches over
     distinct weight copies, so that a sample lasts hundreds of microseconds and the 5 % stability bar is meaningful."""
@@ -59,7 +59,7 @@ def family_of(be: hb.CudaBackend) -> dict[int, int]:
     return {i: fam for i, _, fam in be.variants(capi.OP_GEMV)}
 
 
-def install(be: hb.CudaBackend, db: ProfileDb, key: ProfileKey, shapes=BASELINE_SHAPES, buckets=T_BUCKETS) -> list[Choice]:
+def install(be: hb.CudaBackend, db: ProfileDb, key: ProfileKey, shapes=HEADLINE_SHAPES, buckets=T_BUCKETS) -> list[Choice]:
     """Looks every (shape, bucket) up and installs what the database holds.  The decode buckets of one shape must come from one
     numerics family (include/halo/backend/backend.h:300-304): the family is the one of the T = 1 choice, and a bucket whose stored
     winner belongs to another family is left to the backend's default of that family (source "default")."""

@@ -296,7 +296,7 @@ class CudaBackend:
         if a.gates_n_v != 0 and (op != "MATMUL" or not a.norm_w.empty()):
             raise HaloError(capi.E_UNSUPPORTED, f"{op}: the GDN gates epilogue (GemvArgs::gates) is for MATMUL without a fused norm")
         rb = C.c_uint64()
-        if a.variant_id == capi.GEMV_MMA_R:  # W is in the repacked row layout
+        if a.variant_id in capi.REPACKED_VARIANTS:  # W is in the repacked row layout
             _check(self.lib.halo_cuda_repacked_row_bytes(a.wtype, a.cols, C.byref(rb)))
         else:
             _check(self.lib.halo_cuda_row_bytes(a.wtype, a.cols, C.byref(rb)))

@@ -22,6 +22,7 @@ constexpr HaloCudaVariant kGemvVariants[] = {
     {HALO_CUDA_GEMV_MMA_M1, HALO_CUDA_OP_GEMV, 3, "gemv_mma_m1"},
     {HALO_CUDA_GEMV_MMA_R, HALO_CUDA_OP_GEMV, 5, "gemv_mma_r"},
     {HALO_CUDA_GEMV_MMA_I8X2, HALO_CUDA_OP_GEMV, 6, "gemv_mma_i8x2"},
+    {HALO_CUDA_GEMV_MMA_I8X2_R, HALO_CUDA_OP_GEMV, 6, "gemv_mma_i8x2_r"},
 };
 constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
 constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
@@ -80,6 +81,17 @@ int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, v
     return 0;
 }
 
+bool reads_repacked_rows(uint32_t variant_id) { return variant_id == HALO_CUDA_GEMV_MMA_R || variant_id == HALO_CUDA_GEMV_MMA_I8X2_R; }
+
+bool gemv_i8_r_supports(const GemvCall& c) {
+    switch (c.wtype) {
+        case HALO_CUDA_T_Q6_K: return gemv_i8_q6kr_supports(c);
+        case HALO_CUDA_T_Q8_0: return gemv_i8_q80r_supports(c);
+        case HALO_CUDA_T_Q4_0: return gemv_i8_q40r_supports(c);
+        default: return false;
+    }
+}
+
 bool note_smem_raised(HaloCudaCtx* ctx, const void* kernel) { return ctx->smem_raised.insert(kernel).second; }
 
 int allow_dynamic_smem(HaloCudaCtx* ctx, const void* kernel, uint32_t bytes) {
@@ -103,8 +115,8 @@ int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCa
     c->n_vec = a->n_vec;
     c->flags = a->flags;
     c->row_bytes = uint64_t{a->cols} / ti.block_elems * ti.block_bytes;
-    if (a->variant_id == HALO_CUDA_GEMV_MMA_R) {  // the W operand is in the repacked layout: its rows have another size
-        if (repacked_row_bytes(a->wtype, 256) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "%s: gemv_mma_r takes repacked Q4_0 / Q8_0 / Q6_K weights", op);
+    if (reads_repacked_rows(a->variant_id)) {  // the W operand is in the repacked layout: its rows have another size
+        if (repacked_row_bytes(a->wtype, 256) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "%s: variant %u takes repacked Q4_0 / Q8_0 / Q6_K weights", op, a->variant_id);
         if (a->cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "%s: %u elements is not a multiple of the repacked group size 256", op, a->cols);
         c->row_bytes = repacked_row_bytes(a->wtype, a->cols);
     }
@@ -220,6 +232,15 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
             if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH)
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_i8x2 uses context scratch");
             return launch_gemv_i8(ctx, c, s);
+        case HALO_CUDA_GEMV_MMA_I8X2_R:
+            if (!gemv_i8_r_supports(c))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_i8x2_r needs repacked 16-byte-aligned rows whose x records fit in shared memory, and 16-byte-aligned x");
+            if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_i8x2_r uses context scratch");
+            switch (c.wtype) {
+                case HALO_CUDA_T_Q6_K: return launch_gemv_i8_q6kr(ctx, c, s);
+                case HALO_CUDA_T_Q8_0: return launch_gemv_i8_q80r(ctx, c, s);
+                default: return launch_gemv_i8_q40r(ctx, c, s);
+            }
         case HALO_CUDA_GEMV_MMA_R:
             if (!gemv_mma_r_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemv_mma_r needs repacked 16-byte-aligned rows, cols %% 256 == 0 and 16-byte-aligned x");
@@ -579,8 +600,8 @@ int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t
     if (variant_id == 0 || variant_id > HALO_CUDA_GEMV_VARIANT_MAX)
         return fail(HALO_CUDA_E_CONFIG, "plan: unknown kernel variant id %u", variant_id);
     if (n_vec_lo > n_vec_hi) return fail(HALO_CUDA_E_API, "plan: empty n_vec range");
-    if (variant_id == HALO_CUDA_GEMV_MMA_R)
-        return fail(HALO_CUDA_E_CONFIG, "plan: gemv_mma_r reads another weight layout: the loader that repacks a tensor passes variant id %u with it",
+    if (reads_repacked_rows(variant_id))
+        return fail(HALO_CUDA_E_CONFIG, "plan: the repacked variants read another weight layout: the loader that repacks a tensor passes variant id %u with it",
                     variant_id);
     for (PlanEntry& p : ctx->plan) {
         if (p.wtype == wtype && p.rows == rows && p.cols == cols && p.n_vec_lo == n_vec_lo && p.n_vec_hi == n_vec_hi) {
@@ -662,8 +683,8 @@ int halo_cuda_gemv_normed(HaloCudaCtx* ctx, const HaloCudaGemv* args, const floa
     if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm belongs to the kernels that use context scratch");
     const uint32_t v = resolve_variant(ctx, c, args->variant_id);
     const bool has_it = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c)) ||
-                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c));
-    if (!has_it) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7, 8) have the fused input norm");
+                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c)) || (v == HALO_CUDA_GEMV_MMA_I8X2_R && gemv_i8_r_supports(c));
+    if (!has_it) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7, 8, 9) have the fused input norm");
     if (c.rows == 0) return 0;
     c.norm_w = norm_w;
     c.norm_eps = norm_eps;
@@ -730,8 +751,8 @@ int halo_cuda_gemv_reduce(HaloCudaCtx* ctx, const HaloCudaGemv* args, const Halo
     if (c.flags & HALO_CUDA_GEMV_FLAG_NO_SCRATCH) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the peer epilogue belongs to the kernels that use context scratch");
     const uint32_t v = resolve_variant(ctx, c, args->variant_id);
     const bool pushes = (v == HALO_CUDA_GEMV_MMA_F16X2 && gemv_mma_supports(c)) || (v == HALO_CUDA_GEMV_MMA_R && gemv_mma_r_supports(c)) ||
-                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c));
-    if (!pushes) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7) have the peer epilogue");
+                        (v == HALO_CUDA_GEMV_MMA_I8X2 && gemv_i8_supports(c)) || (v == HALO_CUDA_GEMV_MMA_I8X2_R && gemv_i8_r_supports(c));
+    if (!pushes) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: only the tensor-core skinny variants (3, 7, 8, 9) have the peer epilogue");
     c.peer = peers;
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (int rc = run_gemv(ctx, c, v, s)) return rc;

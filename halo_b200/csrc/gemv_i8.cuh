@@ -43,10 +43,16 @@ __device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uin
 // x records of NTOK rows, per super-block:
 //   digits  [sub-block 0..7][column 0..2 * NTOK - 1][32 B]   column 2 * tok = hi digits, 2 * tok + 1 = lo digits of row tok;
 //                                                            byte i of a column = element i of the sub-block
-//   meta    [row][48 B]                                      int32 pairs (X_p, X_{4+p}) for p = 0..3, then 1 / s as fp32
+//                                                            (formats whose weight words hold elements 4t .. 4t+3 and 16+4t .. of a
+//                                                            32-element block keep a column PERMUTED: element e at byte
+//                                                            8 * ((e % 16) / 4) + 4 * (e / 16) + e % 4, so that a lane's two B
+//                                                            registers are one 8-byte load)
+//   meta    [row][112 B]                                     int32 pairs (X_p, X_{4+p}) for p = 0..3 (sums of xq over 32 elements),
+//                                                            1 / s as fp32 at byte 32, and at byte 48 the sixteen sums over 16
+//                                                            elements as [t][T] = group 4 T + t
 // The digit area and the meta area are separate arrays (all super-blocks of one, then all of the other), in shared
 // memory as in the scratch the pre-staging kernel fills.
-constexpr uint32_t kDigitBytes = 512, kMetaBytes = 48;
+constexpr uint32_t kDigitBytes = 512, kMetaBytes = 112;
 inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
 inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * rec_bytes(n_tok); }
 
@@ -54,7 +60,7 @@ inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64
 /// 8 l .. 8 l + 7 in (v0, v1).  A super-block with a NaN or an infinity gets 1 / s = NaN, which poisons exactly the sums it
 /// enters (the reference's per-row NaN, src/backend/backend.cpp:91-96).
 __device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta, float4 v0, float4 v1, uint32_t sb, uint32_t n_tok, uint32_t tok,
-                                                 uint32_t lane) {
+                                                 uint32_t lane, bool perm = false) {
     float m = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                     fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
 #pragma unroll
@@ -83,32 +89,44 @@ __device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta,
     lo.x = prmt(prmt(q[0], q[1], 0x0040), prmt(q[2], q[3], 0x0040), 0x5410);
     lo.y = prmt(prmt(q[4], q[5], 0x0040), prmt(q[6], q[7], 0x0040), 0x5410);
     const uint32_t sub = lane >> 2, pos = (lane & 3u) * 8u;
-    uint8_t* d = digits + uint64_t{sb} * (kDigitBytes * n_tok) + sub * (64u * n_tok) + tok * 64u + pos;
-    *reinterpret_cast<uint2*>(d) = hi;
-    *reinterpret_cast<uint2*>(d + 32) = lo;
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    uint8_t* d = digits + uint64_t{sb} * (kDigitBytes * n_tok) + sub * (64u * n_tok) + tok * 64u;
+    if (!perm) {
+        *reinterpret_cast<uint2*>(d + pos) = hi;
+        *reinterpret_cast<uint2*>(d + pos + 32) = lo;
+    } else {  // elements 8 (l & 3) .. + 3 and .. + 4 .. + 7: k-step half (l & 3) >> 1, threads 2 (l & 1) and 2 (l & 1) + 1
+        const uint32_t at = 16u * (lane & 1u) + 4u * ((lane & 3u) >> 1);
+        *reinterpret_cast<uint32_t*>(d + at) = hi.x;
+        *reinterpret_cast<uint32_t*>(d + at + 8) = hi.y;
+        *reinterpret_cast<uint32_t*>(d + at + 32) = lo.x;
+        *reinterpret_cast<uint32_t*>(d + at + 40) = lo.y;
+    }
     uint8_t* mt = meta + uint64_t{sb} * (kMetaBytes * n_tok) + tok * kMetaBytes;
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if ((lane & 1u) == 0) reinterpret_cast<int*>(mt + 48)[((lane >> 1) & 3u) * 4u + (lane >> 3)] = sum;  // 16 elements: group lane / 2
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     if ((lane & 3u) == 0) reinterpret_cast<int*>(mt)[(sub & 3u) * 2u + (sub >> 2)] = sum;
     if (lane == 0) reinterpret_cast<float*>(mt)[8] = bad ? __int_as_float(0x7FC00000) : __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
 }
 
 /// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block of one row into the scratch records.
 static __global__ void __launch_bounds__(512) stage_x_i8_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch, uint32_t nb,
-                                                                uint32_t n_tok) {
+                                                                uint32_t n_tok, uint32_t perm) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t tk = blockIdx.x, sb = blockIdx.y * 16u + (threadIdx.x >> 5);
     if (sb >= nb) return;
     const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
     const uint32_t lane = threadIdx.x & 31u;
-    stage_superblock(scratch, scratch + uint64_t{nb} * kDigitBytes * n_tok, xr[sb * 64u + 2u * lane], xr[sb * 64u + 2u * lane + 1u], sb, n_tok, tk, lane);
+    stage_superblock(scratch, scratch + uint64_t{nb} * kDigitBytes * n_tok, xr[sb * 64u + 2u * lane], xr[sb * 64u + 2u * lane + 1u], sb, n_tok, tk, lane,
+                     perm != 0);
 }
 
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows (the extra 16 bytes keep the fragment reads conflict-free)
 struct Q4Ki {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1;
-    static constexpr bool kAllowSlices = true;
+    static constexpr bool kAllowSlices = true, kPermX = false;
+    static constexpr int kMaxTok = 16;  // x rows per launch (four MMA column groups); larger batches, or records that do not fit, run in tiles
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
     /// Lane constants of the single-row form.
     struct One {
@@ -244,6 +262,350 @@ struct Q4Ki {
     }
 };
 
+// ---- repacked Q8_0 / Q4_0 rows (layouts: gemv_mma_grouped.cu): eight 32-element blocks per 256-weight group, an fp16 scale each --------
+// One MMA (k = 32) per block: a lane's weight word holds elements 4t .. 4t+3 (k-step 0) or 16+4t .. (k-step 1), the x digits are
+// kept in the same order (permuted columns).  Per block b:  A_b = S_b - zero * X_b  (int32, exact),  and per phase p = 0..3
+//     u_p = fma(d_{4+p}, float(A_{4+p}), d_p * float(A_p)),   P_p = fma(1 / s, u_p, P_p),   y = (P_0 + P_1) + (P_2 + P_3).
+__device__ __forceinline__ void imma_ss(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma0_ss(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+template <class T>
+struct Blocks32 {
+    static constexpr bool kPermX = true;
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
+
+    template <bool FIRST>
+    __device__ static __forceinline__ void mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+        if constexpr (T::kSigned) {
+            if constexpr (FIRST) imma0_ss(c, a0, a1, a2, a3, b0, b1);
+            else imma_ss(c, a0, a1, a2, a3, b0, b1);
+        } else {
+            if constexpr (FIRST) imma0(c, a0, a1, a2, a3, b0, b1);
+            else imma(c, a0, a1, a2, a3, b0, b1);
+        }
+    }
+    /// fp16 number `idx` (compile time) of the eight in `d` as fp32
+    __device__ static __forceinline__ float scale(const uint4& d, int idx) {
+        const uint32_t w = (idx >> 1) == 0 ? d.x : (idx >> 1) == 1 ? d.y : (idx >> 1) == 2 ? d.z : d.w;
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(idx & 1 ? w >> 16 : w & 0xFFFFu)));
+    }
+
+    struct One {
+        const uint8_t* bp[4];
+        uint32_t bstep[4];
+        uint32_t sel;  // byte selector that moves fp16 number t of a word pair into the low half
+    };
+    __device__ static __forceinline__ One make_one(const uint8_t* digits, const uint8_t* zeros, uint32_t g, uint32_t t) {
+        One o;
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {
+            const bool real = (g >> 1) == static_cast<uint32_t>(ph);
+            o.bp[ph] = real ? digits + (g & 1u) * 32u + t * 8u : zeros + t * 8u;
+            o.bstep[ph] = real ? kDigitBytes : 0u;
+        }
+        o.sel = (2u * t) | ((2u * t + 1u) << 4);
+        return o;
+    }
+
+    template <class Release>
+    __device__ static __forceinline__ void item_one(const uint8_t* r0, uint32_t t, const One& o, uint32_t rec, const uint8_t* meta, float (&P)[2],
+                                                    Release&& release) {
+        const uint8_t* r1 = r0 + 8 * T::kPitch;
+        typename T::Frag f0, f1;
+        T::load(f0, r0, t);
+        T::load(f1, r1, t);
+        const uint4 d0 = *reinterpret_cast<const uint4*>(r0), d1 = *reinterpret_cast<const uint4*>(r1);
+        release();  // fragments and scales are in registers
+        const uint8_t* bq[4];
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) bq[ph] = o.bp[ph] + rec * o.bstep[ph];
+        int c[2][4];  // tile h: blocks 4h .. 4h + 3, one per column pair
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            uint32_t a0, a1, a2, a3;
+            T::regs(f0, b, a0, a2);
+            T::regs(f1, b, a1, a3);
+            const uint2 bx = *reinterpret_cast<const uint2*>(bq[b & 3] + b * 64);
+            if ((b & 3) == 0) mma<true>(c[b >> 2], a0, a1, a2, a3, bx.x, bx.y);
+            else mma<false>(c[b >> 2], a0, a1, a2, a3, bx.x, bx.y);
+        }
+        const uint8_t* mt = meta + rec * kMetaBytes;
+        const int2 X = *reinterpret_cast<const int2*>(mt + t * 8u);
+        const float inv = *reinterpret_cast<const float*>(mt + 32);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const uint4 d = rr ? d1 : d0;
+            const uint32_t lo = prmt(d.x, d.y, o.sel), hi = prmt(d.z, d.w, o.sel);  // scales of blocks t and 4 + t in the low halves
+            const float s0 = __low2float(*reinterpret_cast<const __half2*>(&lo)), s1 = __low2float(*reinterpret_cast<const __half2*>(&hi));
+            const int A0 = c[0][2 * rr] * 256 + c[0][2 * rr + 1] - T::kZero * X.x, A1 = c[1][2 * rr] * 256 + c[1][2 * rr + 1] - T::kZero * X.y;
+            const float u = __fmaf_rn(s1, __int2float_rn(A1), __fmul_rn(s0, __int2float_rn(A0)));
+            P[rr] = __fmaf_rn(inv, u, P[rr]);
+        }
+    }
+
+    template <int G, int NTOK, class Release>
+    __device__ static __forceinline__ void item_many(const uint8_t* r0, uint32_t t, uint32_t g, const uint8_t* dig, const uint8_t* meta, float (&P)[G][2][4],
+                                                     Release&& release) {
+        constexpr uint32_t kSub = 64u * NTOK;
+        const uint8_t* r1 = r0 + 8 * T::kPitch;
+        typename T::Frag f0, f1;
+        T::load(f0, r0, t);
+        T::load(f1, r1, t);
+        const uint4 dd[2] = {*reinterpret_cast<const uint4*>(r0), *reinterpret_cast<const uint4*>(r1)};
+        release();
+        uint32_t boff[G], moff[G];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            boff[gi] = min(8u * gi + g, 2u * NTOK - 1u) * 32u + t * 8u;
+            moff[gi] = min(4u * gi + t, static_cast<uint32_t>(NTOK - 1)) * kMetaBytes;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {  // phases p = 2 jj, 2 jj + 1: blocks p and p + 4
+            float U[G][2][2];
+            int4 X[G];
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) X[gi] = *reinterpret_cast<const int4*>(meta + moff[gi] + jj * 16);  // (X_p, X_{4+p}, X_{p+1}, X_{5+p})
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int b = 2 * jj + e + 4 * half;
+                    uint32_t a0, a1, a2, a3;
+                    T::regs(f0, b, a0, a2);
+                    T::regs(f1, b, a1, a3);
+#pragma unroll
+                    for (int gi = 0; gi < G; ++gi) {
+                        const uint2 bx = *reinterpret_cast<const uint2*>(dig + b * kSub + boff[gi]);
+                        int c[4];
+                        mma<true>(c, a0, a1, a2, a3, bx.x, bx.y);
+                        const int xs = e == 0 ? (half == 0 ? X[gi].x : X[gi].y) : (half == 0 ? X[gi].z : X[gi].w);
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const float fa = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1] - T::kZero * xs), sc = scale(dd[rr], b);
+                            U[gi][rr][e] = half == 0 ? __fmul_rn(sc, fa) : __fmaf_rn(sc, fa, U[gi][rr][e]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                const float inv = *reinterpret_cast<const float*>(meta + moff[gi] + 32);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    P[gi][rr][2 * jj] = __fmaf_rn(inv, U[gi][rr][0], P[gi][rr][2 * jj]);
+                    P[gi][rr][2 * jj + 1] = __fmaf_rn(inv, U[gi][rr][1], P[gi][rr][2 * jj + 1]);
+                }
+            }
+        }
+    }
+};
+
+struct Q80i : Blocks32<Q80i> {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 320, kItemCoord = 272 / 4, kBoxInner = 320 / 4, kMapElemBytes = 4;
+    static constexpr bool kAllowSlices = false, kSigned = true;  // 5 KB ring slots: two slices' worth of rings do not fit at every batch size
+    static constexpr int kZero = 0, kMaxTok = 8;
+    struct Frag {
+        uint4 q[4];  // chunk c: (block 2c, k-step 0), (block 2c, k-step 1), (block 2c + 1, k-step 0), (block 2c + 1, k-step 1)
+    };
+    __device__ static __forceinline__ void load(Frag& f, const uint8_t* row, uint32_t t) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) f.q[c] = *reinterpret_cast<const uint4*>(row + 16 + c * 64 + t * 16);
+    }
+    __device__ static __forceinline__ void regs(const Frag& f, int b, uint32_t& k0, uint32_t& k1) {
+        const uint4 c = f.q[b >> 1];
+        k0 = (b & 1) ? c.z : c.x, k1 = (b & 1) ? c.w : c.y;
+    }
+};
+
+struct Q40i : Blocks32<Q40i> {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kPitch = 192, kItemCoord = 144 / 4, kBoxInner = 192 / 4, kMapElemBytes = 4;
+    static constexpr bool kAllowSlices = true, kSigned = false;
+    static constexpr int kZero = 8, kMaxTok = 16;
+    struct Frag {
+        uint4 q[2];  // chunk c: the words of blocks 4c .. 4c + 3 (low nibbles: elements 4t .., high nibbles: elements 16 + 4t ..)
+    };
+    __device__ static __forceinline__ void load(Frag& f, const uint8_t* row, uint32_t t) {
+        f.q[0] = *reinterpret_cast<const uint4*>(row + 16 + t * 16);
+        f.q[1] = *reinterpret_cast<const uint4*>(row + 16 + 64 + t * 16);
+    }
+    __device__ static __forceinline__ void regs(const Frag& f, int b, uint32_t& k0, uint32_t& k1) {
+        const uint4 c = f.q[b >> 2];
+        const uint32_t w = (b & 3) == 0 ? c.x : (b & 3) == 1 ? c.y : (b & 3) == 2 ? c.z : c.w;
+        k0 = w & 0x0F0F0F0Fu, k1 = (w >> 4) & 0x0F0F0F0Fu;
+    }
+};
+
+// ---- repacked Q6_K rows (224 B per super-block): sixteen 16-element groups with an int8 scale each, one fp16 d per super-block ------
+// The 6-bit codes enter as unsigned bytes, the zero point leaves through the group's sum of xq:  A_g = S_g - 32 * X_g  (|A_g| < 2^24,
+// exact as fp32).  Per phase p = 0..3 (group g = 4 T + p, T = 0..3 ascending):
+//     u_p = sc_p * A_p,  u_p = fma(sc_{4T+p}, A_{4T+p}, u_p)   (fp32; sc and A converted exactly),   P_p = fma(1 / s, d * u_p, P_p)
+// A batch uses one m16n8k16 MMA per group.  A single row uses m16n8k32: a 32-element sub-block holds two groups, which land in
+// different column pairs because the B registers of the other half are masked to zero.
+__device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+struct Q6Ki {
+    static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kPitch = 224, kItemCoord = 224 / 4, kBoxInner = 224 / 4, kMapElemBytes = 4;
+    static constexpr bool kAllowSlices = true, kPermX = true;
+    static constexpr int kMaxTok = 8;
+    /// 224-byte slot rows put rows g and g + 1 on overlapping banks: fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return ((2u * g) & 7u) | (g >> 2); }
+
+    struct Frag {
+        uint4 ql[2];  // half n: words (b, lh) = (0,0), (0,1), (1,0), (1,1)
+        uint4 qh;     // words (n, lh) = (0,0), (0,1), (1,0), (1,1)
+    };
+    __device__ static __forceinline__ void load(Frag& f, const uint8_t* row, uint32_t t) {
+        f.ql[0] = *reinterpret_cast<const uint4*>(row + 32 + t * 16);
+        f.ql[1] = *reinterpret_cast<const uint4*>(row + 32 + 64 + t * 16);
+        f.qh = *reinterpret_cast<const uint4*>(row + 32 + 128 + t * 16);
+    }
+    /// The codes of sub-block sub = 4 n + quarter (elements 128 n + 32 quarter ..): k0 = elements 4t .. 4t+3, k1 = 16 + 4t ..
+    __device__ static __forceinline__ void regs(const Frag& f, int sub, uint32_t& k0, uint32_t& k1) {
+        const int n = sub >> 2, quarter = sub & 3, b = quarter & 1, nib = quarter >> 1;
+        const uint4 c = f.ql[n];
+        const uint32_t w0 = b ? c.z : c.x, w1 = b ? c.w : c.y;
+        const uint32_t h0 = n ? f.qh.z : f.qh.x, h1 = n ? f.qh.w : f.qh.y;
+        // nibble | two high bits << 4: byte j of h holds the high bits of element j for all four quarters, two bits each
+        auto code = [&](uint32_t w, uint32_t h) {
+            const uint32_t wn = nib ? w >> 4 : w;
+            const uint32_t hs = quarter == 0 ? h << 4 : quarter == 1 ? h << 2 : quarter == 2 ? h : h >> 2;
+            return (wn & 0x0F0F0F0Fu) | (hs & 0x30303030u);
+        };
+        k0 = code(w0, h0), k1 = code(w1, h1);
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+    struct One {
+        const uint8_t* bp[2];  // B base for the first / second sub-block of a tile: this lane's digits, or zeros
+        uint32_t bstep[2];
+        uint32_t m0, m1;       // which half of a sub-block this lane's column pair carries
+        uint32_t sel;          // sign-extending selector of scale byte t
+    };
+    __device__ static __forceinline__ One make_one(const uint8_t* digits, const uint8_t* zeros, uint32_t g, uint32_t t) {
+        One o;
+        const uint32_t ph = g >> 1;  // the column pair's group inside a tile of four
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const bool real = (ph >> 1) == static_cast<uint32_t>(e);
+            o.bp[e] = real ? digits + (g & 1u) * 32u + t * 8u : zeros + t * 8u;
+            o.bstep[e] = real ? kDigitBytes : 0u;
+        }
+        o.m0 = (ph & 1u) == 0 ? 0xFFFFFFFFu : 0u;
+        o.m1 = ~o.m0;
+        o.sel = t | ((8u | t) * 0x1110u);
+        return o;
+    }
+
+    template <class Release>
+    __device__ static __forceinline__ void item_one(const uint8_t* r0, uint32_t t, const One& o, uint32_t rec, const uint8_t* meta, float (&P)[2],
+                                                    Release&& release) {
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        Frag f0, f1;
+        load(f0, r0, t);
+        load(f1, r1, t);
+        const uint4 sw[2] = {*reinterpret_cast<const uint4*>(r0), *reinterpret_cast<const uint4*>(r1)};
+        const float d[2] = {__half2float(*reinterpret_cast<const __half*>(r0 + 16)), __half2float(*reinterpret_cast<const __half*>(r1 + 16))};
+        release();  // fragments and scales are in registers
+        const uint8_t* bq[2] = {o.bp[0] + rec * o.bstep[0], o.bp[1] + rec * o.bstep[1]};
+        int c[4][4];  // tile T: groups 4T .. 4T + 3, one per column pair
+#pragma unroll
+        for (int T = 0; T < 4; ++T) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int sub = 2 * T + e;
+                uint32_t a0, a1, a2, a3;
+                regs(f0, sub, a0, a2);
+                regs(f1, sub, a1, a3);
+                const uint2 v = *reinterpret_cast<const uint2*>(bq[e] + sub * 64);
+                if (e == 0) imma0(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
+                else imma(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
+            }
+        }
+        const uint8_t* mt = meta + rec * kMetaBytes;
+        const int4 X = *reinterpret_cast<const int4*>(mt + 48 + t * 16u);  // X of groups t, 4 + t, 8 + t, 12 + t
+        const float inv = *reinterpret_cast<const float*>(mt + 32);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            float u = 0.0f;
+#pragma unroll
+            for (int T = 0; T < 4; ++T) {
+                const int xs = T == 0 ? X.x : T == 1 ? X.y : T == 2 ? X.z : X.w;
+                const float a = __int2float_rn(c[T][2 * rr] * 256 + c[T][2 * rr + 1] - 32 * xs);
+                const float sc = __int2float_rn(static_cast<int>(prmt(word(sw[rr], T), 0u, o.sel)));
+                u = T == 0 ? __fmul_rn(sc, a) : __fmaf_rn(sc, a, u);
+            }
+            P[rr] = __fmaf_rn(inv, __fmul_rn(d[rr], u), P[rr]);
+        }
+    }
+
+    template <int G, int NTOK, class Release>
+    __device__ static __forceinline__ void item_many(const uint8_t* r0, uint32_t t, uint32_t g, const uint8_t* dig, const uint8_t* meta, float (&P)[G][2][4],
+                                                     Release&& release) {
+        constexpr uint32_t kSub = 64u * NTOK;
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        Frag f0, f1;
+        load(f0, r0, t);
+        load(f1, r1, t);
+        const uint4 sw[2] = {*reinterpret_cast<const uint4*>(r0), *reinterpret_cast<const uint4*>(r1)};
+        const float d[2] = {__half2float(*reinterpret_cast<const __half*>(r0 + 16)), __half2float(*reinterpret_cast<const __half*>(r1 + 16))};
+        release();
+        uint32_t boff[G], moff[G];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            boff[gi] = min(8u * gi + g, 2u * NTOK - 1u) * 32u + t * 8u;
+            moff[gi] = min(4u * gi + t, static_cast<uint32_t>(NTOK - 1)) * kMetaBytes;
+        }
+        float U[G][2][4];
+#pragma unroll
+        for (int T = 0; T < 4; ++T) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int sub = 2 * T + e;
+                uint32_t a0, a1, a2, a3;
+                regs(f0, sub, a0, a2);
+                regs(f1, sub, a1, a3);
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const uint2 bx = *reinterpret_cast<const uint2*>(dig + sub * kSub + boff[gi]);
+#pragma unroll
+                    for (int lh = 0; lh < 2; ++lh) {
+                        const int p = 2 * e + lh;  // group 4 T + p
+                        int c[4];
+                        imma_k16(c, lh ? a2 : a0, lh ? a3 : a1, lh ? bx.y : bx.x);
+                        const int xs = *reinterpret_cast<const int*>(meta + moff[gi] + 48 + (p * 4 + T) * 4);
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const float a = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1] - 32 * xs);
+                            const float sc = __int2float_rn(static_cast<int>(static_cast<int8_t>(word(sw[rr], T) >> (8 * p))));
+                            U[gi][rr][p] = T == 0 ? __fmul_rn(sc, a) : __fmaf_rn(sc, a, U[gi][rr][p]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            const float inv = *reinterpret_cast<const float*>(meta + moff[gi] + 32);
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+                for (int p = 0; p < 4; ++p) P[gi][rr][p] = __fmaf_rn(inv, __fmul_rn(d[rr], U[gi][rr][p]), P[gi][rr][p]);
+        }
+    }
+};
+
 // Shared-memory layout: header (mma_common.cuh) | weight ring | slice sums (KS > 1) | zeros (single row) | digits | meta
 template <class F, int NTOK, int NS, int KS>
 struct Layout {
@@ -255,15 +617,15 @@ struct Layout {
     // a single row's digits start 64 bytes off the zeros' 128-byte phase: the lanes of a half warp that read x and those that
     // read zeros then never meet on a bank
     static constexpr uint32_t kOffDigits = kOffZero + (NTOK == 1 ? 512u + 64u : 0u);
-    static constexpr uint32_t bytes(uint32_t nb) { return kOffDigits + nb * rec_bytes(NTOK); }
+    static constexpr uint32_t bytes(uint32_t n_rec) { return kOffDigits + n_rec * rec_bytes(NTOK); }
 };
 
 template <class F, int NTOK, int NS, int KS, bool PRE, bool NORM = false>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
-               float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, float* __restrict__ partials, uint32_t* __restrict__ counters,
-               uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage, const __grid_constant__ PeerPush peer,
-               const float* __restrict__ norm_w, float norm_eps) {
+               float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t n_rec, float* __restrict__ partials,
+               uint32_t* __restrict__ counters, uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage,
+               const __grid_constant__ PeerPush peer, const float* __restrict__ norm_w, float norm_eps) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     using L = Layout<F, NTOK, NS, KS>;
@@ -275,8 +637,10 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const uint32_t r = warp % R, ks = warp / R;
     const uint32_t n_rb = (rows + 15u) / 16u, cpu = tb.cols_per_unit;
     const uint32_t cta = blockIdx.x;  // the grid has exactly tb.parts CTAs
+    // n_rec x records are resident: all nb of them (record j = super-block j), or -- when every CTA of a one-slice partition walks
+    // fewer columns than a unit has -- only those of the CTA's own columns, record j = its j-th column (super-block (c0 + j) mod nb)
     uint8_t* digits = smem + L::kOffDigits;
-    uint8_t* meta = digits + nb * (kDigitBytes * NTOK);
+    uint8_t* meta = digits + n_rec * (kDigitBytes * NTOK);
 
     const uint32_t bars = smem_base + kOffBars + warp * NS * 8u;
     const uint32_t ring = smem_base + kOffRing + warp * NS * kSlot;
@@ -321,9 +685,24 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         if (tid == 0) {
             mbar_init(xbar, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            const uint32_t total = nb * rec_bytes(NTOK);  // digits, then meta: one contiguous run in the scratch as in shared memory
-            mbar_expect_tx(xbar, total);
-            for (uint32_t off = 0; off < total; off += 32768u) bulk_g2s(smem_base + L::kOffDigits + off, xstage + off, min(32768u, total - off), xbar);
+            // the records of this CTA's super-blocks: all of them, or the cyclic run of its columns (at most two contiguous pieces)
+            const uint32_t xc0 = tb.start[cta], xn = tb.start[cta + 1] - xc0;
+            const bool xpart = KS == 1 && n_rec < nb;
+            const uint32_t first = xpart ? xc0 % cpu : 0u, count = xpart ? xn : nb;
+            const uint32_t n1 = min(count, nb - first), n2 = count - n1;  // super-blocks [first, first + n1) then [0, n2)
+            constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
+            mbar_expect_tx(xbar, count * (kD + kM));
+            const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
+            const uint32_t smeta = smem_base + L::kOffDigits + n_rec * kD;
+            auto copy = [&](uint32_t dst, const uint8_t* src, uint32_t bytes) {
+                for (uint32_t off = 0; off < bytes; off += 32768u) bulk_g2s(dst + off, src + off, min(32768u, bytes - off), xbar);
+            };
+            copy(smem_base + L::kOffDigits, xstage + uint64_t{first} * kD, n1 * kD);
+            copy(smeta, gmeta + uint64_t{first} * kM, n1 * kM);
+            if (n2 != 0) {
+                copy(smem_base + L::kOffDigits + n1 * kD, xstage, n2 * kD);
+                copy(smeta + n1 * kM, gmeta, n2 * kM);
+            }
         }
         __syncthreads();
         if (!mbar_wait(xbar, 0)) {
@@ -335,7 +714,15 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // The row is converted in the kernel, one super-block per warp and round.  The first round (super-blocks 0 .. 15) is
         // what every warp's first tiles need: the block waits for it; the later rounds (their loads already in flight) finish
         // behind an mbarrier that only the tiles of super-block 16 and up wait for.
-        const uint32_t late_warps = nb > kSkWarps ? min(nb - kSkWarps, kSkWarps) : 0u;
+        // Under a partial residency the CTA converts only the super-blocks of its own columns, cyclically from where its range starts.
+        const uint32_t x_c0 = tb.start[cta], x_cols = tb.start[cta + 1] - x_c0;
+        const bool part = KS == 1 && n_rec < nb;
+        const uint32_t x_first = part ? x_c0 % cpu : 0u, x_count = part ? x_cols : nb;
+        auto x_sb = [&](uint32_t j) {  // the j-th super-block this CTA converts
+            const uint32_t sb = x_first + j;
+            return sb >= nb ? sb - nb : sb;  // (a one-slice partition has cpu == nb)
+        };
+        const uint32_t late_warps = x_count > kSkWarps ? min(x_count - kSkWarps, kSkWarps) : 0u;
         if (tid == 0 && late_warps != 0) {
             mbar_init(smem_base + kOffXBar + 8u, late_warps);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -358,24 +745,26 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             }
         };
         float4 v0[2], v1[2];
-        const bool first = warp < nb, second = warp + kSkWarps < nb;
-        if (first) fetch(warp, v0);
-        if (second) fetch(warp + kSkWarps, v1);
-        if (first) stage_superblock(digits, meta, v0[0], v0[1], warp, 1, 0, lane);
+        const bool first = warp < x_count, second = warp + kSkWarps < x_count;
+        if (first) fetch(x_sb(warp), v0);
+        if (second) fetch(x_sb(warp + kSkWarps), v1);
+        if (first) stage_superblock(digits, meta, v0[0], v0[1], warp, 1, 0, lane, F::kPermX);
         __syncthreads();
         if (second) {
-            stage_superblock(digits, meta, v1[0], v1[1], warp + kSkWarps, 1, 0, lane);
-            for (uint32_t sb = warp + 2 * kSkWarps; sb < nb; sb += kSkWarps) {
-                fetch(sb, v0);
-                stage_superblock(digits, meta, v0[0], v0[1], sb, 1, 0, lane);
+            stage_superblock(digits, meta, v1[0], v1[1], warp + kSkWarps, 1, 0, lane, F::kPermX);
+            for (uint32_t j = warp + 2 * kSkWarps; j < x_count; j += kSkWarps) {
+                fetch(x_sb(j), v0);
+                stage_superblock(digits, meta, v0[0], v0[1], j, 1, 0, lane, F::kPermX);
             }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_base + kOffXBar + 8u) : "memory");
         }
     }
     bool late_ready = false;  // this warp has seen the later rounds of the x conversion complete
+    // the record of a tile: its super-block, or (partial residency) its column's distance from the start of the CTA's range
+    const bool x_part = KS == 1 && n_rec < nb;
 
-    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + g * F::kPitch;
+    const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + F::slot_row(g) * F::kPitch;
     float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
     [[maybe_unused]] typename F::One one;
     if constexpr (NTOK == 1) one = F::make_one(digits, smem + L::kOffZero, g, t);
@@ -399,9 +788,9 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         if (unit * R + r >= n_rb) break;
         const uint32_t k_hi = min(kmax, c1 - unit * cpu);
         for (uint32_t k = k_lo; k < k_hi; ++k) {
-            const uint32_t sb = k * KS + ks;
+            const uint32_t sb = k * KS + ks, rec = x_part ? unit * cpu + k - c0 : sb;
             if constexpr (!PRE) {
-                if (sb >= kSkWarps && !late_ready) {
+                if (rec >= kSkWarps && !late_ready) {
                     if (!mbar_wait(smem_base + kOffXBar + 8u, 0)) {
                         if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
                         lost = true;
@@ -416,9 +805,9 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             if constexpr (NTOK == 1) {
                 float (&P1)[2] = *reinterpret_cast<float (*)[2]>(&P[0][0][0]);
                 static_assert(sizeof(P) == 2 * sizeof(float), "single-row accumulators");
-                F::item_one(slot0 + slot * kSlot, t, one, sb, meta, P1, release);
+                F::item_one(slot0 + slot * kSlot, t, one, rec, meta, P1, release);
             } else {
-                F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + sb * (kDigitBytes * NTOK), meta + sb * (kMetaBytes * NTOK), P, release);
+                F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + rec * (kDigitBytes * NTOK), meta + rec * (kMetaBytes * NTOK), P, release);
             }
         }
         // the row block, or this CTA's share of it, is done
@@ -439,7 +828,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
                 }
             }
-        sk::finish_block<G, NTOK, KS>(yacc, unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, g, peer);
+        sk::finish_block<G, NTOK, KS>(yacc, unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
     }
     if (lost) sk::linger_after_loss();
 }

@@ -1,0 +1,7 @@
+// gemv_mma_i8x2_r: the int8 tensor-core skinny kernels over repacked Q8_0 rows.
+#include "gemv_i8_launch.cuh"
+
+namespace halo_cuda {
+bool gemv_i8_q80r_supports(const GemvCall& c) { return i8::supports_format<i8::Q80i>(c); }
+int launch_gemv_i8_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) { return i8::launch_format<i8::Q80i>(ctx, c, s); }
+}  // namespace halo_cuda

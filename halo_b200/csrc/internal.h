@@ -136,6 +136,14 @@ int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, 
 int launch_gemv_mma_r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_i8(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_i8_supports(const GemvCall& c);
+int launch_gemv_i8_q6kr(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_i8_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+int launch_gemv_i8_q40r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
+bool gemv_i8_q6kr_supports(const GemvCall& c);
+bool gemv_i8_q80r_supports(const GemvCall& c);
+bool gemv_i8_q40r_supports(const GemvCall& c);
+bool gemv_i8_r_supports(const GemvCall& c);   // the three above by weight type
+bool reads_repacked_rows(uint32_t variant_id);  // the W operand of this variant is in the layout of halo_cuda_repack_rows
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout
 int launch_repack(uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride, uint32_t rows, uint32_t cols, cudaStream_t s);

@@ -60,7 +60,8 @@ extern "C" {
 #define HALO_CUDA_GEMV_MMA_R 7        /* tensor-core skinny kernel over REPACKED Q6_K / Q8_0 / Q4_0 rows (halo_cuda_repack_rows) */
 #define HALO_CUDA_GEMV_MMA_I8X2 8     /* tensor-core skinny kernel, x as two signed 8-bit digits per element (16-bit fixed point per
                                          256-element super-block), integer MMA; raw Q4_K rows */
-#define HALO_CUDA_GEMV_VARIANT_MAX 8
+#define HALO_CUDA_GEMV_MMA_I8X2_R 9   /* the same arithmetic over REPACKED Q6_K / Q8_0 / Q4_0 rows (halo_cuda_repack_rows) */
+#define HALO_CUDA_GEMV_VARIANT_MAX 9
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
 #define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch: the tensor-core variants then take their
@@ -197,13 +198,13 @@ int halo_cuda_variants(uint32_t op, HaloCudaVariant* out, uint32_t cap, uint32_t
 /* The variant id 0 resolves to for this call (what the shape heuristic, or an installed plan, picks). */
 int halo_cuda_gemv_resolve(HaloCudaCtx* ctx, const HaloCudaGemv* args, uint32_t* variant_id);
 /* Installs the autotuner's choice for one shape bucket: calls with variant_id 0, this wtype, rows, cols and
- * n_vec in [n_vec_lo, n_vec_hi] run `variant_id` (the "KernelPlan" join of ADR-001 5.6).  Variant 7 is refused (E_CONFIG): it
- * reads another weight layout, so it travels with the tensor a loader has repacked, not with a shape. */
+ * n_vec in [n_vec_lo, n_vec_hi] run `variant_id` (the "KernelPlan" join of ADR-001 5.6).  Variants 7 and 9 are refused (E_CONFIG): they
+ * read another weight layout, so they travel with the tensor a loader has repacked, not with a shape. */
 int halo_cuda_plan_set(HaloCudaCtx* ctx, uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec_lo, uint32_t n_vec_hi,
                        uint32_t variant_id);
 int halo_cuda_plan_clear(HaloCudaCtx* ctx);
 size_t halo_cuda_last_error(char* buf, size_t len);
-/* The repacked row layout of variant HALO_CUDA_GEMV_MMA_R: a byte permutation (plus padding for Q6_K) of every 256-weight
+/* The repacked row layout of the variants HALO_CUDA_GEMV_MMA_R and HALO_CUDA_GEMV_MMA_I8X2_R: a byte permutation (plus padding for Q6_K) of every 256-weight
  * group that makes the rows fetchable by the copy engine, the counterpart of tensor::gemv_repack
  * (include/halo/tensor/repack.h:11-36) and of the kGemvRepacked variant (backend.h:178-183).  cols must be a multiple
  * of 256.  halo_cuda_repacked_row_bytes gives the size of a repacked row (E_UNSUPPORTED for types without one);
@@ -257,7 +258,7 @@ int halo_cuda_get_rows(HaloCudaCtx* ctx, const HaloCudaGetRows* args, HaloCudaSt
  *   slots[p]: rank p's receive buffer as mapped on this rank (own: the local pointer), 2 * world * capacity * 8 bytes
  *   epoch, done: two zeroed words of this rank's own memory
  * rows * n_vec must not exceed capacity; the ranks must issue the same sequence of reductions.  Only the tensor-core
- * skinny variants (3, 7, 8) push; others: E_UNSUPPORTED. */
+ * skinny variants (3, 7, 8, 9) push; others: E_UNSUPPORTED. */
 #define HALO_CUDA_MAX_PEERS 8
 typedef struct HaloCudaPeerReduce {
     uint32_t world, rank, capacity, reserved;

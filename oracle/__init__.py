@@ -27,11 +27,20 @@ F32, Q4_0, Q8_0, Q4_K, Q6_K = 0, 2, 8, 12, 14
 _u8p = C.POINTER(C.c_uint8)
 
 
+def find_ref_root() -> Path | None:
+    """The reference source tree: $HALO_REF_ROOT, else a directory `reference` next to this repository; None when neither holds one."""
+    env = os.environ.get("HALO_REF_ROOT")
+    for root in ([Path(env)] if env else []) + [HERE.parent.parent / "reference"]:
+        if (root / "src" / "backend" / "cpu_backend.cpp").exists():
+            return root
+    return None
+
+
 def build(ref_root: str | None = None) -> None:
     """Compile the C restatement, and the reference library when the reference tree exists."""
     subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
-    root = ref_root or os.environ.get("HALO_REF_ROOT", "/root/reference")
-    if Path(root, "src", "backend", "cpu_backend.cpp").exists():
+    root = Path(ref_root) if ref_root else find_ref_root()
+    if root is not None and (root / "src" / "backend" / "cpu_backend.cpp").exists():
         subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"HALO_REF_ROOT={root}"], check=True)
 
 

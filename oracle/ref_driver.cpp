@@ -1,6 +1,6 @@
 // C entry points around the UNMODIFIED reference CPU backend.  TEST INFRASTRUCTURE ONLY.
 //
-// build_ref.sh compiles this file together with the reference's own sources (where they lie
+// The Makefile beside this file (target `ref`) compiles it together with the reference's own sources (where they lie
 // in the reference tree, never copied) into oracle/_ref/libhalo_ref.so.  The calls below go
 // through the reference's public interface exactly as its own tests do:
 // halo::backend::make_cpu_backend(&pool) -> import_host* -> Backend::gemv / lm_head

@@ -94,3 +94,23 @@ def summation_bound(checker_dequant, wtype, w, x, rows, cols, depth):
     wf = checker_dequant(wtype, w, rows * cols).reshape(rows, cols).astype(np.float64)
     s = np.abs(np.asarray(x, np.float64)) @ np.abs(wf).T
     return depth * 2.0**-24 * s
+
+
+def half_steps(x: np.ndarray) -> np.ndarray:
+    """Half a quantisation step of every element of x (rows of a multiple of 256 floats) in the int8 tensor-core family: the kernels
+    scale a super-block by the power of two s that puts its largest magnitude m in (2^14, 32639] and round x * s to an integer."""
+    x = np.asarray(x, np.float64)
+    blocks = np.abs(x).reshape(x.shape[0], -1, 256)
+    m = blocks.max(axis=2)
+    with np.errstate(divide="ignore"):
+        se = np.where(m > 0, 14 - np.floor(np.log2(np.where(m > 0, m, 1.0))), 0.0)
+    se = np.clip(se, -100, 100)
+    se = np.where(m * np.exp2(se) > 32639.0, se - 1, se)
+    return np.repeat(0.5 * np.exp2(-se), 256, axis=1)
+
+
+def rounded_operand_bound(checker, t, w, x, n, k):
+    """sum |w_i| * (half a quantisation step of x_i) plus the reordered-summation bound: what a kernel that rounds x to 16-bit fixed
+    point and then sums in its own order may differ from the CPU backend by."""
+    wf = checker.dequantize(t, w, n * k).reshape(n, k).astype(np.float64)
+    return half_steps(x) @ np.abs(wf).T + summation_bound(checker.dequantize, t, w, x, n, k, depth=2 * (k // 8 + 8))

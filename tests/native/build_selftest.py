@@ -1,5 +1,5 @@
 """Builds tests/native/libadapter_selftest.so: the C++ differential test of the cuda adapter against the reference CPU
-backend, both driven through the reference's Backend interface.  Needs the reference headers (HALO_REF_ROOT) and
+backend, both driven through the reference's Backend interface.  Needs the reference headers ($HALO_REF_ROOT, else a directory `reference` next to this repository) and
 oracle/_ref/libhalo_ref.so; where they are absent the prebuilt library that travelled with the tree is used."""
 from __future__ import annotations
 
@@ -14,7 +14,8 @@ LIB = HERE / "libadapter_selftest.so"
 
 
 def build(force: bool = False) -> Path | None:
-    ref = Path(os.environ.get("HALO_REF_ROOT", "/root/reference"))
+    env = os.environ.get("HALO_REF_ROOT")
+    ref = Path(env) if env else ROOT.parent / "reference"
     ref_so = ROOT / "oracle" / "_ref" / "libhalo_ref.so"
     adapter = ROOT / "halo_b200" / "adapter" / "libhalo_cuda_backend.so"
     if not (ref / "include" / "halo" / "backend" / "backend.h").exists() or not ref_so.exists() or not adapter.exists():

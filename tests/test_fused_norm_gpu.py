@@ -35,7 +35,7 @@ def cpu_rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
 
 def run(be, st, t, w, x, norm_w, rows, cols, eps, variant, fused=True):
     wb = be.import_host_readonly(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
-    if variant == capi.GEMV_MMA_R:
+    if variant in capi.REPACKED_VARIANTS:
         wb = be.repack(st, t, hb.TensorRef.of(wb), rows, cols)
     xb = be.import_host_readonly(np.ascontiguousarray(x, np.float32))
     nb = be.import_host_readonly(np.ascontiguousarray(norm_w, np.float32))
@@ -52,7 +52,8 @@ def run(be, st, t, w, x, norm_w, rows, cols, eps, variant, fused=True):
 
 CASES = [(synth.Q4_K, 70, 2560, 0), (synth.Q4_K, 17408, 5120, 0), (synth.Q4_K, 70, 2560, capi.GEMV_MMA_F16X2),
          (synth.Q4_K, 17408, 5120, capi.GEMV_MMA_F16X2), (synth.Q6_K, 37, 3072, capi.GEMV_MMA_R), (synth.Q6_K, 5120, 17408, capi.GEMV_MMA_R),
-         (synth.Q8_0, 50, 1536, capi.GEMV_MMA_R), (synth.Q4_0, 129, 2048, capi.GEMV_MMA_R)]
+         (synth.Q8_0, 50, 1536, capi.GEMV_MMA_R), (synth.Q4_0, 129, 2048, capi.GEMV_MMA_R), (synth.Q6_K, 37, 3072, capi.GEMV_MMA_I8X2_R),
+         (synth.Q6_K, 5120, 17408, capi.GEMV_MMA_I8X2_R), (synth.Q8_0, 50, 1536, capi.GEMV_MMA_I8X2_R), (synth.Q4_0, 129, 2048, capi.GEMV_MMA_I8X2_R)]
 
 
 @pytest.mark.parametrize("t,rows,cols,variant", CASES)
@@ -70,7 +71,7 @@ def test_fused_norm_matches_rms_norm_then_matmul(checker, t, rows, cols, variant
     scale = np.max(np.abs(want))
     # variant 0 on Q4_K is the int8 family: x becomes a 16-bit fixed-point number per super-block, and a last-bit difference in the
     # normalised row may move an element by one quantisation step
-    i8 = t == synth.Q4_K and variant == 0
+    i8 = (t == synth.Q4_K and variant == 0) or variant == capi.GEMV_MMA_I8X2_R
     assert np.max(np.abs(got - want)) <= (2e-4 if i8 else 1e-5) * scale     # against the CPU backend: rms_norm, then its own matmul
     assert np.max(np.abs(got - unfused)) <= (1e-4 if i8 else 2e-6) * scale  # against this backend's matmul over the CPU's normalised row
 

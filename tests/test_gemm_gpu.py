@@ -76,7 +76,7 @@ def test_gemm_gate_only_allow_gemm_takes_the_gemm(hz):
 
 
 def test_gemm_config2_full_size_against_the_skinny_kernel(hz):
-    # BASELINE config 2: Q4_K 17408 x 5120, M = 512; the tensor-core skinny kernel (near-fp32 accuracy, itself checked
+    # the prefill shape: Q4_K 17408 x 5120, M = 512; the tensor-core skinny kernel (near-fp32 accuracy, itself checked
     # against the oracle at this shape) is the yardstick, so the CPU does not have to run 9e10 multiply-adds
     n, k, m = 17408, 5120, 512
     w = synth.quant_weights(synth.Q4_K, n, k, 0, 1)

@@ -79,7 +79,7 @@ def test_exact_variant_bitwise_odd_strides_and_offsets(hz, checker, t):
 
 
 def test_exact_variant_bitwise_cfg0_full_size(hz, checker):
-    # BASELINE config 0: Q4_K 17408 x 5120, M = 1, seed 0
+    # the headline decode shape: Q4_K 17408 x 5120 (the 27B FFN gate / up projection), M = 1, seed 0
     n, k = 17408, 5120
     w = synth.quant_weights(synth.Q4_K, n, k, 0, 1)
     x = synth.activations(1, k, 0, 2)
@@ -89,7 +89,7 @@ def test_exact_variant_bitwise_cfg0_full_size(hz, checker):
 
 @pytest.mark.parametrize("t,m", [(synth.Q6_K, 1), (synth.Q6_K, 4), (synth.Q8_0, 8)])
 def test_exact_variant_bitwise_cfg1_full_size(hz, checker, t, m):
-    # BASELINE config 1: N = 5120, K = 17408, Q6_K and Q8_0
+    # the FFN down projection: N = 5120, K = 17408, Q6_K and Q8_0
     n, k = 5120, 17408
     w = synth.quant_weights(t, n, k, 0, 1)
     x = synth.activations(m, k, 0, 2)

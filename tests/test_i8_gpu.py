@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from conftest import bits
-from gpu_util import Harness, summation_bound
+from gpu_util import Harness, rounded_operand_bound
 from halo_b200 import backend as hb
 from halo_b200 import capi, synth
 
@@ -25,24 +25,6 @@ FAMILY_REL = 2e-4  # what the family states for itself: the largest error over t
 @pytest.fixture(scope="module")
 def hz():
     return Harness()
-
-
-def half_steps(x: np.ndarray) -> np.ndarray:
-    """Half a quantisation step of every element of x (rows of a multiple of 256 floats): the kernels scale a super-block by the
-    power of two s that puts its largest magnitude m in (2^14, 32639] and round x * s to an integer."""
-    x = np.asarray(x, np.float64)
-    blocks = np.abs(x).reshape(x.shape[0], -1, 256)
-    m = blocks.max(axis=2)
-    with np.errstate(divide="ignore"):
-        se = np.where(m > 0, 14 - np.floor(np.log2(np.where(m > 0, m, 1.0))), 0.0)
-    se = np.clip(se, -100, 100)
-    se = np.where(m * np.exp2(se) > 32639.0, se - 1, se)
-    return np.repeat(0.5 * np.exp2(-se), 256, axis=1)
-
-
-def rounded_operand_bound(checker, t, w, x, n, k):
-    wf = checker.dequantize(t, w, n * k).reshape(n, k).astype(np.float64)
-    return half_steps(x) @ np.abs(wf).T + summation_bound(checker.dequantize, t, w, x, n, k, depth=2 * (k // 8 + 8))
 
 
 @pytest.mark.parametrize("n,k,m", [(17408, 5120, 1), (37, 512, 3), (5120, 17408, 4), (1000, 5120, 16), (130, 256, 21), (5120, 17408, 13),
@@ -64,14 +46,15 @@ def test_i8_within_rounded_operand_bound(hz, checker, n, k, m):
         assert not np.array_equal(bits(y), bits(hz.gemv(t, w, x, n, k, variant=capi.GEMV_MMA_F16X2)))
 
 
-@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 9), (640, 6144, 17), (2176, 5120, 16)])
+@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 18), (640, 6144, 17), (2176, 5120, 33)])
 def test_i8_rows_do_not_depend_on_batch_size(hz, n, k, rows_of_x):
-    # token tiles of up to eight rows (fewer where K is long), pre-staged records for batches, in-kernel conversion for one row
+    # token tiles of up to sixteen rows (fewer where the x records of a tile would not fit), pre-staged records for batches,
+    # in-kernel conversion for one row
     t = synth.Q4_K
     w = synth.quant_weights(t, n, k, 3, 1)
     x = synth.activations(rows_of_x, k, 3, 2)
     y_all = hz.gemv(t, w, x, n, k, variant=V)
-    for m in (1, 2, 3, 4, 5, 7, 8, 9, 11, 16):
+    for m in (1, 2, 3, 4, 5, 7, 8, 9, 11, 12, 13, 15, 16, 17):
         if m > rows_of_x:
             continue
         ym = hz.gemv(t, w, x[:m], n, k, variant=V)
@@ -87,8 +70,9 @@ CASES = [
     (2176, 5120, 4, "even split, 17 CTAs per unit"),
     (9, 5120, 16, "fewer rows than a tile: 20 CTAs share one row block"),
     (40000, 256, 3, "one column per unit, several units per CTA"),
-    (5120, 6144, 17, "three token tiles (8 + 8 + 1)"),
-    (300, 17408, 8, "68 columns per unit, tiles of three rows"),
+    (5120, 6144, 17, "two token tiles (16 + 1)"),
+    (17408, 5120, 16, "all twenty super-blocks resident: two tiles of eight"),
+    (300, 17408, 8, "68 columns per unit: a CTA keeps only the records of its own columns"),
     (18992, 5120, 16, "vocabulary shard of the head"),
 ]
 
