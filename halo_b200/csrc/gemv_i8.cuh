@@ -124,7 +124,7 @@ static __global__ void __launch_bounds__(512) stage_x_i8_kernel(const float* __r
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows (the extra 16 bytes keep the fragment reads conflict-free)
 struct Q4Ki {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1;
-    static constexpr bool kAllowSlices = true, kPermX = false;
+    static constexpr bool kPermX = false;
     static constexpr int kMaxTok = 16;  // x rows per launch (four MMA column groups); larger batches, or records that do not fit, run in tiles
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
@@ -410,7 +410,7 @@ struct Blocks32 {
 
 struct Q80i : Blocks32<Q80i> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 320, kItemCoord = 272 / 4, kBoxInner = 320 / 4, kMapElemBytes = 4;
-    static constexpr bool kAllowSlices = false, kSigned = true;  // 5 KB ring slots: two slices' worth of rings do not fit at every batch size
+    static constexpr bool kSigned = true;
     static constexpr int kZero = 0, kMaxTok = 8;
     struct Frag {
         uint4 q[4];  // chunk c: (block 2c, k-step 0), (block 2c, k-step 1), (block 2c + 1, k-step 0), (block 2c + 1, k-step 1)
@@ -427,7 +427,7 @@ struct Q80i : Blocks32<Q80i> {
 
 struct Q40i : Blocks32<Q40i> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kPitch = 192, kItemCoord = 144 / 4, kBoxInner = 192 / 4, kMapElemBytes = 4;
-    static constexpr bool kAllowSlices = true, kSigned = false;
+    static constexpr bool kSigned = false;
     static constexpr int kZero = 8, kMaxTok = 16;
     struct Frag {
         uint4 q[2];  // chunk c: the words of blocks 4c .. 4c + 3 (low nibbles: elements 4t .., high nibbles: elements 16 + 4t ..)
@@ -457,7 +457,7 @@ __device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, 
 
 struct Q6Ki {
     static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kPitch = 224, kItemCoord = 224 / 4, kBoxInner = 224 / 4, kMapElemBytes = 4;
-    static constexpr bool kAllowSlices = true, kPermX = true;
+    static constexpr bool kPermX = true;
     static constexpr int kMaxTok = 8;
     /// 224-byte slot rows put rows g and g + 1 on overlapping banks: fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return ((2u * g) & 7u) | (g >> 2); }
@@ -607,39 +607,72 @@ struct Q6Ki {
 };
 
 // Shared-memory layout: header (mma_common.cuh) | weight ring | slice sums (KS > 1) | zeros (single row) | digits | meta
-template <class F, int NTOK, int NS, int KS>
+// KS (1, 2, 4, 8 or 16 in-CTA K slices; R = 16 / KS row blocks per unit) is a launch parameter: one kernel per format and batch size.
+template <class F, int NTOK, int NS>
 struct Layout {
     static constexpr int G = (NTOK + 3) / 4;
     static constexpr uint32_t kSlot = 16 * F::kPitch;
     static constexpr uint32_t kOffSlices = kOffRing + kSkWarps * NS * kSlot;
-    static constexpr uint32_t kRedBytes = KS > 1 ? (kSkWarps / KS) * (KS - 1) * 32 * 2 * G * 4 : 0;
-    static constexpr uint32_t kOffZero = (kOffSlices + kRedBytes + 127u) & ~127u;
+    /// slice sums: [r][ks - 1][lane][2 G] floats = (16 - R) warps' worth; ks_shift = log2 of the slice count
+    __host__ __device__ static constexpr uint32_t red_bytes(uint32_t ks_shift) { return (kSkWarps - (kSkWarps >> ks_shift)) * 32u * 2u * G * 4u; }
+    __host__ __device__ static constexpr uint32_t off_zero(uint32_t ks_shift) { return (kOffSlices + red_bytes(ks_shift) + 127u) & ~127u; }
     // a single row's digits start 64 bytes off the zeros' 128-byte phase: the lanes of a half warp that read x and those that
     // read zeros then never meet on a bank
-    static constexpr uint32_t kOffDigits = kOffZero + (NTOK == 1 ? 512u + 64u : 0u);
-    static constexpr uint32_t bytes(uint32_t n_rec) { return kOffDigits + n_rec * rec_bytes(NTOK); }
+    __host__ __device__ static constexpr uint32_t off_digits(uint32_t ks_shift) { return off_zero(ks_shift) + (NTOK == 1 ? 512u + 64u : 0u); }
+    __host__ __device__ static constexpr uint32_t bytes(uint32_t n_rec, uint32_t ks_shift) { return off_digits(ks_shift) + n_rec * rec_bytes(NTOK); }
 };
 
-template <class F, int NTOK, int NS, int KS, bool PRE, bool NORM = false>
+/// End of a unit (or of the CTA's share of it): the KS slices of the row block are added in ks order through shared memory
+/// (`red`: [r][ks - 1][lane][2G] floats), then slice 0 hands the sums over (gemv_mma_sk.cuh's finish_block with KS at run time).
+template <int G, int NTOK>
+__device__ __forceinline__ void finish_slices(float (&yacc)[G][2], uint32_t unit, uint32_t r, uint32_t ks, uint32_t KS, uint32_t R, float* red, const SkTable& tb,
+                                              uint32_t cta, float* part, uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
+                                              uint32_t row, const PeerPush& peer) {
+    if (KS > 1) {
+        if (ks != 0) {
+            float2* mine = reinterpret_cast<float2*>(red) + ((r * (KS - 1) + (ks - 1)) * 32 + lane) * G;
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) mine[gi] = make_float2(yacc[gi][0], yacc[gi][1]);
+        }
+        sk::named_barrier(1 + r, KS * 32);
+        if (ks == 0) {
+            for (uint32_t k = 1; k < KS; ++k) {
+                const float2* p = reinterpret_cast<const float2*>(red) + ((r * (KS - 1) + (k - 1)) * 32 + lane) * G;
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) yacc[gi][0] = __fadd_rn(yacc[gi][0], p[gi].x), yacc[gi][1] = __fadd_rn(yacc[gi][1], p[gi].y);
+            }
+        }
+        sk::named_barrier(1 + r, KS * 32);  // the slices may overwrite `red` at their next block only after slice 0 has read it
+    }
+    if (ks == 0) sk_flush_r<G, NTOK>(yacc, unit, r, R, tb, cta, part, counters, y, y_stride, rows, lane, row, peer);
+}
+
+// KSC: the slice count where it is known at compile time (the two-slice partition of the large shapes, whose inner loop
+// is the one that runs at memory speed), 0: taken from ks_shift_arg.
+template <class F, int NTOK, int NS, int KSC, bool PRE, bool NORM = false>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
-               float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t n_rec, float* __restrict__ partials,
+               float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t n_rec, uint32_t ks_shift_arg, float* __restrict__ partials,
                uint32_t* __restrict__ counters, uint32_t* __restrict__ error_word, const uint8_t* __restrict__ xstage,
                const __grid_constant__ PeerPush peer, const float* __restrict__ norm_w, float norm_eps) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-    using L = Layout<F, NTOK, NS, KS>;
-    constexpr int G = L::G, R = kSkWarps / KS;
+    using L = Layout<F, NTOK, NS>;
+    constexpr int G = L::G;
     constexpr uint32_t kThreads = kSkWarps * 32, kSlot = L::kSlot;
-    static_assert(kSkWarps <= kMaxWarps && NS <= 6, "shared-memory header layout");
+    static_assert(KSC == 0 || KSC == 2, "compile-time slice counts");
+    const uint32_t ks_shift = KSC == 2 ? 1u : ks_shift_arg;
+    const uint32_t KS = 1u << ks_shift, R = kSkWarps >> ks_shift;  // K slices, row blocks per unit
+    static_assert(kSkWarps == 16 && kSkWarps <= kMaxWarps && NS <= 6, "shared-memory header layout; warp -> (r, ks) by shifts");
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t r = warp % R, ks = warp / R;
+    const uint32_t r = warp & (R - 1u), ks = warp >> (4u - ks_shift);
     const uint32_t n_rb = (rows + 15u) / 16u, cpu = tb.cols_per_unit;
     const uint32_t cta = blockIdx.x;  // the grid has exactly tb.parts CTAs
     // n_rec x records are resident: all nb of them (record j = super-block j), or -- when every CTA of a one-slice partition walks
     // fewer columns than a unit has -- only those of the CTA's own columns, record j = its j-th column (super-block (c0 + j) mod nb)
-    uint8_t* digits = smem + L::kOffDigits;
+    const uint32_t off_zero = L::off_zero(ks_shift), off_digits = L::off_digits(ks_shift);
+    uint8_t* digits = smem + off_digits;
     uint8_t* meta = digits + n_rec * (kDigitBytes * NTOK);
 
     const uint32_t bars = smem_base + kOffBars + warp * NS * 8u;
@@ -655,7 +688,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // that unit inside the range, as long as the row block and the super-block exist.  The producer (ring fill) and the
     // consumer walk them independently; later units have later row blocks, so the first row block past the matrix ends both.
     const uint32_t c0 = tb.start[cta], c1 = tb.start[cta + 1];
-    const uint32_t kmax = nb > ks ? min(cpu, (nb - ks + KS - 1) / KS) : 0u;  // this warp's columns in a whole unit
+    const uint32_t kmax = nb > ks ? min(cpu, (nb - ks + KS - 1u) >> ks_shift) : 0u;  // this warp's columns in a whole unit
     const uint32_t unit0 = c0 / cpu;
     auto seg_end = [&](uint32_t unit) { return unit * R + r < n_rb && unit * cpu < c1 ? min(kmax, c1 - unit * cpu) : 0u; };
     uint32_t p_unit = unit0, p_k = c0 - unit0 * cpu, p_end = seg_end(unit0), fill_slot = 0;
@@ -679,7 +712,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
     bool lost = false;
     if constexpr (NTOK == 1)
-        for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + L::kOffZero)[i] = 0u;
+        for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + off_zero)[i] = 0u;
     if constexpr (PRE) {
         const uint32_t xbar = smem_base + kOffXBar;
         if (tid == 0) {
@@ -693,14 +726,14 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
             mbar_expect_tx(xbar, count * (kD + kM));
             const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
-            const uint32_t smeta = smem_base + L::kOffDigits + n_rec * kD;
+            const uint32_t smeta = smem_base + off_digits + n_rec * kD;
             auto copy = [&](uint32_t dst, const uint8_t* src, uint32_t bytes) {
                 for (uint32_t off = 0; off < bytes; off += 32768u) bulk_g2s(dst + off, src + off, min(32768u, bytes - off), xbar);
             };
-            copy(smem_base + L::kOffDigits, xstage + uint64_t{first} * kD, n1 * kD);
+            copy(smem_base + off_digits, xstage + uint64_t{first} * kD, n1 * kD);
             copy(smeta, gmeta + uint64_t{first} * kM, n1 * kM);
             if (n2 != 0) {
-                copy(smem_base + L::kOffDigits + n1 * kD, xstage, n2 * kD);
+                copy(smem_base + off_digits + n1 * kD, xstage, n2 * kD);
                 copy(smeta + n1 * kM, gmeta, n2 * kM);
             }
         }
@@ -767,7 +800,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const uint8_t* slot0 = smem + kOffRing + warp * NS * kSlot + F::slot_row(g) * F::kPitch;
     float* red = reinterpret_cast<float*>(smem + L::kOffSlices);
     [[maybe_unused]] typename F::One one;
-    if constexpr (NTOK == 1) one = F::make_one(digits, smem + L::kOffZero, g, t);
+    if constexpr (NTOK == 1) one = F::make_one(digits, smem + off_zero, g, t);
     float P[G][2][NTOK == 1 ? 1 : 4];
 #pragma unroll
     for (int gi = 0; gi < G; ++gi)
@@ -828,7 +861,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
                 }
             }
-        sk::finish_block<G, NTOK, KS>(yacc, unit, r, ks, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
+        finish_slices<G, NTOK>(yacc, unit, r, ks, KS, R, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
     }
     if (lost) sk::linger_after_loss();
 }

@@ -1,5 +1,5 @@
-// Host side of the int8 tensor-core skinny kernels (gemv_i8.cuh): token tiles, scratch, launch.  Included by one .cu per
-// weight format so that the formats compile in parallel.
+// Host side of the int8 tensor-core skinny kernels (gemv_i8.cuh): partition, token tiles, scratch, launch.  Included by
+// one .cu per weight format so that the formats compile in parallel.
 #pragma once
 #include "gemv_i8.cuh"
 #include "gemv_mma_sk_launch.cuh"
@@ -7,13 +7,41 @@
 namespace halo_cuda {
 namespace i8 {
 
-constexpr int kRing = 2;    // stages of a warp's weight ring: deeper rings measured slower (more row segments in flight at a time)
+constexpr int kRing = 2;  // stages of a warp's weight ring: deeper rings measured slower (more row segments in flight at a time)
 
-template <class F, int NTOK, int KS>
+/// Shared memory of a launch with n_tok x rows, n_rec resident records and 2^ks_shift slices (Layout<F, n_tok, kRing>::bytes
+/// for a batch size known only at run time).
+template <class F>
+uint32_t smem_bytes(uint32_t n_tok, uint32_t n_rec, uint32_t ks_shift) {
+    const uint32_t G = (n_tok + 3) / 4, off_slices = kOffRing + kSkWarps * kRing * 16 * F::kPitch;
+    const uint32_t red = (kSkWarps - (kSkWarps >> ks_shift)) * 32u * 2u * G * 4u;
+    return ((off_slices + red + 127u) & ~127u) + (n_tok == 1 ? 576u : 0u) + n_rec * rec_bytes(n_tok);
+}
+
+inline uint32_t log2_of(uint32_t ks) {
+    uint32_t s = 0;
+    while ((1u << s) < ks) ++s;
+    return s;
+}
+
+/// In-CTA slices need every x record of a row resident; they are on offer where that holds for a tile of eight x rows.
+template <class F>
+bool slices_fit(uint32_t nb) {
+    return smem_bytes<F>(8, nb, 4) <= kSmemBudget;
+}
+
+/// The partition of a shape (a function of rows, cols and the SM count alone: every batch size gets the same one).
+template <class F>
+void plan(const HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry* g) {
+    g->nb = c.cols / 256u;
+    g->ks = plan_partition_i8(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), slices_fit<F>(g->nb), &g->table);
+}
+
+template <class F, int NTOK, int KSC>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;
-    using L = Layout<F, NTOK, kRing, KS>;
-    const uint32_t n_rec = sk::resident_records(g), smem_bytes = L::bytes(n_rec);
+    using L = Layout<F, NTOK, kRing>;
+    const uint32_t ks_shift = log2_of(g.ks), n_rec = sk::resident_records(g), smem_bytes = L::bytes(n_rec, ks_shift);
     if (smem_bytes > kSmemBudget) return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x records of %d rows do not fit in shared memory", n_rec, NTOK);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
@@ -33,18 +61,18 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     const cudaLaunchConfig_t cfg = sk::pdl_config(g.table.parts, smem_bytes, s, attr);
     if (c.norm_w != nullptr) {
         if constexpr (NTOK == 1) {
-            auto kern = gemv_i8_kernel<F, 1, kRing, KS, false, true>;
+            auto kern = gemv_i8_kernel<F, 1, kRing, KSC, false, true>;
             if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
-            HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, static_cast<float*>(g.partials),
+            HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                        static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), c.norm_w, c.norm_eps));
             return 0;
         } else {
             return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
         }
     }
-    auto kern = gemv_i8_kernel<F, NTOK, kRing, KS, PRE, false>;
+    auto kern = gemv_i8_kernel<F, NTOK, kRing, KSC, PRE, false>;
     if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
-    HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, static_cast<float*>(g.partials),
+    HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), static_cast<const float*>(nullptr),
                                0.0f));
     return 0;
@@ -52,27 +80,26 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
 
 /// n rows starting at tok0 (n <= the largest tile whose records fit in shared memory)
 template <class F, int NTOK>
-int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, uint32_t tok0, uint32_t n, cudaStream_t s) {
+int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry& g, uint32_t tok0, uint32_t n, cudaStream_t s) {
     if constexpr (NTOK > F::kMaxTok) {
         return fail(HALO_CUDA_E_KERNEL, "MATMUL: token tile of %u", n);
     } else {
-        if (n != NTOK) return launch_tokens<F, NTOK + 1>(ctx, c, tok0, n, s);
-        sk::Geometry g{};
-        if (int rc = sk::geometry<F, NTOK>(ctx, c, s, &g)) return rc;
-        if constexpr (F::kAllowSlices) {
-            if (g.ks == 2) return launch_tile<F, NTOK, 2>(ctx, c, g, tok0, s);
-        }
-        return launch_tile<F, NTOK, 1>(ctx, c, g, tok0, s);
+        if (n != NTOK) return launch_tokens<F, NTOK + 1>(ctx, c, g, tok0, n, s);
+        // scratch of the cross-CTA reduction: a zeroed counter per row block, two partial records per CTA and row-block slot
+        constexpr int G = (NTOK + 3) / 4;
+        const uint64_t n_rb = (uint64_t{c.rows} + 15) / 16;
+        if (int rc = workspace(ctx, 2, n_rb * 4, s, &g.counters, /*zeroed=*/true)) return rc;
+        if (int rc = workspace(ctx, 3, uint64_t{g.table.parts} * 2 * kSkWarps * 32 * 2 * G * 4, s, &g.partials)) return rc;
+        if (g.ks == 2) return launch_tile<F, NTOK, 2>(ctx, c, g, tok0, s);  // the partition of the large shapes: slice count folded into the code
+        return launch_tile<F, NTOK, 0>(ctx, c, g, tok0, s);
     }
 }
 
 /// The largest token tile (<= F::kMaxTok) whose x records (n_rec super-blocks resident) fit next to the ring; 0: not even one row.
 template <class F>
-uint32_t max_tile(uint32_t n_rec) {
-    // the one-slice layout (no slice sums) is the smaller one; the two-slice layout adds at most 4 KB
-    const uint64_t fixed = Layout<F, F::kMaxTok, kRing, 2>::kOffDigits + 1024;
+uint32_t max_tile(uint32_t n_rec, uint32_t ks_shift) {
     for (uint32_t n = F::kMaxTok; n >= 1; --n)
-        if (fixed + uint64_t{n_rec} * rec_bytes(n) <= kSmemBudget) return n;
+        if (smem_bytes<F>(n, n_rec, ks_shift) <= kSmemBudget) return n;
     return 0;
 }
 
@@ -82,21 +109,24 @@ bool supports_format(const GemvCall& c) {
     if (reinterpret_cast<uintptr_t>(c.w) % 16 != 0 || c.w_stride % 16 != 0) return false;  // tensor-map base and pitch
     if (c.w_stride >= (uint64_t{1} << 40) || c.row_bytes >= (uint64_t{1} << 32)) return false;
     if (reinterpret_cast<uintptr_t>(c.x) % 16 != 0 || c.x_stride % 16 != 0) return false;  // float4 reads of x
-    return max_tile<F>(c.cols / 256u) != 0;                                                 // one row's records must fit whatever the partition
+    if ((uint64_t{c.rows} + 15) / 16 * (c.cols / 256u) >= (1ull << 30)) return false;      // (16-row, 256-column) tiles
+    return max_tile<F>(c.cols / 256u, 0) != 0;  // one row's records must fit whatever the partition
 }
 
 template <class F>
 int launch_format(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
-    const uint32_t nb = c.cols / 256u;
-    if (max_tile<F>(nb) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the int8 kernels keep x in shared memory; %u columns do not fit", c.cols);
-    // The partition (a function of the shape alone) decides how many records a CTA holds, and that the token tile.
     sk::Geometry g{};
-    g.nb = nb;
-    g.ks = plan_partition(c.rows, nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), F::kAllowSlices, &g.table);
-    const uint32_t tile = max_tile<F>(sk::resident_records(g));
+    plan<F>(ctx, c, &g);
+    // The partition decides how many records a CTA holds, and that the token tile; a batch is cut into equal tiles
+    // (whole MMA column groups of four rows where that still fits).
+    const uint32_t cap = max_tile<F>(sk::resident_records(g), log2_of(g.ks));
+    if (cap == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the int8 kernels keep x in shared memory; %u columns do not fit", c.cols);
+    const uint32_t n_tiles = (c.n_vec + cap - 1) / cap;
+    uint32_t tile = (c.n_vec + n_tiles - 1) / std::max(n_tiles, 1u);
+    if ((tile + 3u) / 4u * 4u <= cap) tile = (tile + 3u) / 4u * 4u;
     for (uint32_t t0 = 0; t0 < c.n_vec; t0 += tile) {
         const uint32_t n = c.n_vec - t0 < tile ? c.n_vec - t0 : tile;
-        if (int rc = launch_tokens<F, 1>(ctx, c, t0, n, s)) return rc;
+        if (int rc = launch_tokens<F, 1>(ctx, c, g, t0, n, s)) return rc;
     }
     return 0;
 }

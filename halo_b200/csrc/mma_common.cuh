@@ -213,6 +213,40 @@ inline uint32_t plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool al
     return 1;
 }
 
+/// The partition of the int8 kernels, whose CTAs cut K into 1, 2, 4, 8 or 16 in-CTA slices (R = 16 / KS row blocks per unit).
+/// With whole units per CTA nothing crosses CTAs, and a launch lasts about as long as the tiles one warp walks:
+/// ceil(units / CTAs) * ceil(nb / KS).  The fewest tiles win, ties go to fewer slices (more rows per CTA share an x record).
+/// Slices need every x record of a row resident in shared memory (`slices_ok`: they fit for a tile of eight x rows); without
+/// them, and where it walks fewer tiles even with the cross-CTA reduction (about `kReducePenalty` tiles' time), the even
+/// split of plan_partition's candidate B.  Returns KS; a function of (rows, cols, SM count) alone.
+constexpr uint32_t kReducePenalty = 4;
+inline uint32_t plan_partition_i8(uint32_t rows, uint32_t nb, uint32_t sms, bool slices_ok, SkTable* table) {
+    const uint64_t n_rb = (uint64_t{rows} + 15) / 16;
+    sms = std::min(sms, kSkMaxCtas);
+    SkTable& t = *table;
+    const uint64_t units_b = (n_rb + 15) / 16, cols_b = units_b * nb, parts_b = std::max<uint64_t>(1, std::min<uint64_t>(sms, cols_b));
+    uint64_t best = (cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : kReducePenalty);
+    uint32_t best_ks = 1;
+    if (slices_ok) {
+        for (uint32_t ks = 2; ks <= kSkWarps && ks / 2 < std::max(nb, 1u); ks *= 2) {  // no more slices than the next power of two above nb
+            const uint64_t units = (n_rb + kSkWarps / ks - 1) / (kSkWarps / ks), parts = std::max<uint64_t>(1, std::min<uint64_t>(sms, units));
+            const uint64_t tiles = (units + parts - 1) / parts * ((nb + ks - 1) / ks);
+            if (tiles < best) best = tiles, best_ks = ks;
+        }
+    }
+    if (best_ks == 1) {
+        t.parts = static_cast<uint32_t>(parts_b);
+        t.cols_per_unit = nb;
+        for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * cols_b / parts_b);
+        return 1;
+    }
+    const uint64_t R = kSkWarps / best_ks, units = (n_rb + R - 1) / R, cpu = (nb + best_ks - 1) / best_ks, parts = std::max<uint64_t>(1, std::min<uint64_t>(sms, units));
+    t.parts = static_cast<uint32_t>(parts);
+    t.cols_per_unit = static_cast<uint32_t>(cpu);
+    for (uint32_t c = 0; c <= t.parts; ++c) t.start[c] = static_cast<uint32_t>(uint64_t{c} * units / parts * cpu);
+    return best_ks;
+}
+
 /// Row-split tensor parallelism: instead of storing a finished row block to y, push it into slot `rank` of every
 /// peer's receive buffer (peer-mapped memory, plain stores over NVLink).  Every element travels as one 8-byte word
 /// {value bits, number of the reduction}: the word is written and read atomically, so the receiver needs no flag
@@ -239,11 +273,11 @@ __device__ __forceinline__ void peer_store(unsigned long long* p, unsigned long 
 /// Sums of one row block (this lane: rows g and g + 8 for its G token columns) -> y: directly when this CTA covered
 /// all of the unit's columns, else through the partial store and the last-arriver reduction.  `part` holds 2 records
 /// per CTA and row-block slot r (record 0: the unit the CTA's range starts in, record 1: the unit it ends in) of
-/// 32 lanes x 2G floats; `counters` one zeroed word per row block, left zeroed.
-template <int G, int NTOK, int R>
-__device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
-                                         uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
-                                         uint32_t g /* the W row of the block (0..7, and + 8) this lane's sums belong to */, const PeerPush& peer) {
+/// 32 lanes x 2G floats; `counters` one zeroed word per row block, left zeroed.  R: row blocks per unit.
+template <int G, int NTOK>
+__device__ __forceinline__ void sk_flush_r(const float (&acc)[G][2], uint32_t unit, uint32_t r, uint32_t R, const SkTable& tb, uint32_t cta, float* part,
+                                           uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane,
+                                           uint32_t g /* the W row of the block (0..7, and + 8) this lane's sums belong to */, const PeerPush& peer) {
     const uint32_t t = lane & 3u, rb = unit * R + r;
     const uint32_t u_lo = unit * tb.cols_per_unit, u_hi = u_lo + tb.cols_per_unit;  // the unit's columns
     uint32_t c_lo = cta, c_hi = cta;
@@ -321,6 +355,13 @@ __device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit
             if (n1 < rows) yr[n1] = sum[gi][1];
         }
     }
+}
+
+template <int G, int NTOK, int R>
+__device__ __forceinline__ void sk_flush(const float (&acc)[G][2], uint32_t unit, uint32_t r, const SkTable& tb, uint32_t cta, float* part,
+                                         uint32_t* counters, float* y, uint64_t y_stride, uint32_t rows, uint32_t lane, uint32_t g,
+                                         const PeerPush& peer) {
+    sk_flush_r<G, NTOK>(acc, unit, r, static_cast<uint32_t>(R), tb, cta, part, counters, y, y_stride, rows, lane, g, peer);
 }
 
 }  // namespace mma
