@@ -388,11 +388,12 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
         raw = be.import_host_readonly(w.reshape(-1))
         packed = [be.repack(st, wtype, hb.TensorRef.of(raw), n, k) for _ in range(copies)]
         st.wait()
+        variant = be.repacked_variant(wtype, k)  # what a loader passes with a repacked tensor of this type and K
         for m in ms_list:
             x = synth.activations(m, k, 11 + rank, 2)
             xb = be.import_host_readonly(x)
             yb = be.allocate(m * n * 4)
-            structs = [be._gemv_struct(hb.GemvArgs(wtype, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, capi.GEMV_MMA_R),
+            structs = [be._gemv_struct(hb.GemvArgs(wtype, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, variant),
                                        "MATMUL", False) for b in packed]
             heads = []
             if gather:  # the LM head proper: the matmul over this rank's vocabulary shard, the argmax of its rows, the shard's row offset
@@ -443,7 +444,7 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
             st.wait()
             shards = world if gather else 1  # the FFN / down shapes are per-GPU work (weak), the head is one job split over the ranks
             gbs = shards * wbytes / (us * 1e-6) / 1e9
-            out.append({"shape": name, "wtype": synth.TYPE_NAMES[wtype], "rows_per_gpu": n, "cols": k, "m": m, "us_per_call": us,
+            out.append({"shape": name, "wtype": synth.TYPE_NAMES[wtype], "variant": variant, "rows_per_gpu": n, "cols": k, "m": m, "us_per_call": us,
                         "weight_gbs": gbs, "frac_of_hbm_per_gpu": gbs / shards / pk["hbm_gbs"], "all_gather": bool(full is not None),
                         "rel_err_vs_exact": float(np.max(np.abs(y - ye)) / np.max(np.abs(ye)))})
             xb.free()
@@ -469,12 +470,12 @@ def fused_norm_leg(be, st, reps: int = 20, copies: int = 8):
     lib.halo_cuda_event_create(ctx, C.byref(e0))
     lib.halo_cuda_event_create(ctx, C.byref(e1))
     out = []
-    for name, t, n, k, variant in (("cfg0 q4_k", synth.Q4_K, N_ROWS, K_COLS, 0), ("cfg1 q6_k down", synth.Q6_K, 5120, 17408, capi.GEMV_MMA_R)):
+    for name, t, n, k, variant in (("cfg0 q4_k", synth.Q4_K, N_ROWS, K_COLS, 0), ("cfg1 q6_k down", synth.Q6_K, 5120, 17408, be.repacked_variant(synth.Q6_K, 17408))):
         w = synth.quant_weights(t, n, k, 0, 1)
         bufs = []
         for _ in range(copies):
             b = be.import_host_readonly(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
-            if variant == capi.GEMV_MMA_R:
+            if variant in capi.REPACKED_VARIANTS:
                 p = be.repack(st, t, hb.TensorRef.of(b), n, k)
                 st.wait()
                 b.free()

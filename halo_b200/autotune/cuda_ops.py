@@ -31,7 +31,7 @@ class CudaGemvTunable:
             copies = max(1, min(16, int(3 * 126e6 // max(wbytes, 1)) + 1))
         self.launches = max(launches_per_run, copies)
         self.wb = [be.import_host_readonly(w.reshape(-1)) for _ in range(copies)]
-        self.wr = []  # the same matrices in the repacked layout, where the type has one (read by gemv_mma_r only)
+        self.wr = []  # the same matrices in the repacked layout, where the type has one (read by the repacked variants only)
         if wtype in (synth.Q6_K, synth.Q8_0, synth.Q4_0) and cols % 256 == 0:
             self.wr = [be.repack(self.st, wtype, hb.TensorRef.of(b), rows, cols) for b in self.wb]
         self.xb = be.import_host_readonly(synth.activations(n_vec, cols, seed, 2))
@@ -45,7 +45,7 @@ class CudaGemvTunable:
         self.family = {i: fam for i, _, fam in be.variants(capi.OP_GEMV)}
 
     def _args(self, i: int, ybuf, variant: int) -> hb.GemvArgs:
-        wbuf = self.wr[i] if variant == capi.GEMV_MMA_R else self.wb[i]
+        wbuf = self.wr[i] if variant in capi.REPACKED_VARIANTS else self.wb[i]
         return hb.GemvArgs(self.wtype, hb.TensorRef.of(wbuf), hb.TensorRef.of(self.xb), hb.TensorRef.of(ybuf), self.rows, self.cols,
                            self.n_vec, variant, allow_gemm=self.allow_gemm)
 
@@ -56,7 +56,7 @@ class CudaGemvTunable:
                 continue  # the fp16 GEMM numerics need the caller's consent (GemvArgs::allow_gemm)
             if name == "gemv_mma_m1" and self.n_vec > 4:
                 continue  # one launch per row: not a candidate for wide batches
-            if vid == capi.GEMV_MMA_R and not self.wr:
+            if vid in capi.REPACKED_VARIANTS and not self.wr:
                 continue  # no repacked layout for this type
             if self.only_family is not None and _fam != self.only_family:
                 continue

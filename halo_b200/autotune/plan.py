@@ -72,7 +72,7 @@ def install(be: hb.CudaBackend, db: ProfileDb, key: ProfileKey, shapes=HEADLINE_
             op = OpKey.matmul(bucket, cols, rows, synth.TYPE_NAMES[wtype])
             cand, source = select_kernel(db, key, op, "cuda", names)
             variant = cand.get("variant") if cand is not None else None
-            if variant is not None and variant != capi.GEMV_MMA_R:  # the repacked variant travels with the tensor, never with a plan
+            if variant is not None and variant not in capi.REPACKED_VARIANTS:  # a repacked variant travels with the tensor, never with a plan
                 if first_family is None:
                     first_family = fams.get(variant)
                 if fams.get(variant) == first_family:

@@ -368,6 +368,12 @@ class CudaBackend:
         _check(self.lib.halo_cuda_repacked_row_bytes(wtype, cols, C.byref(rb)))
         return rb.value
 
+    def repacked_variant(self, wtype: int, cols: int) -> int:
+        """The variant id a repacked tensor of this type and (largest local) K travels with."""
+        v = C.c_uint32()
+        _check(self.lib.halo_cuda_repacked_variant(wtype, cols, C.byref(v)))
+        return v.value
+
     def repack(self, s: Stream, wtype: int, src: TensorRef, rows: int, cols: int) -> Buffer:
         """Raw GGUF rows -> a new read-only buffer in the repacked layout gemv_mma_r reads (what a loader does once per
         weight, like tensor::gemv_repack for the reference's Vulkan backend)."""

@@ -92,6 +92,11 @@ bool gemv_i8_r_supports(const GemvCall& c) {
     }
 }
 
+uint32_t repacked_variant(uint32_t wtype, uint32_t cols) {
+    const bool i8 = wtype == HALO_CUDA_T_Q6_K ? gemv_i8_q6kr_fits(cols) : wtype == HALO_CUDA_T_Q8_0 ? gemv_i8_q80r_fits(cols) : wtype == HALO_CUDA_T_Q4_0 ? gemv_i8_q40r_fits(cols) : false;
+    return i8 ? HALO_CUDA_GEMV_MMA_I8X2_R : HALO_CUDA_GEMV_MMA_R;
+}
+
 bool note_smem_raised(HaloCudaCtx* ctx, const void* kernel) { return ctx->smem_raised.insert(kernel).second; }
 
 int allow_dynamic_smem(HaloCudaCtx* ctx, const void* kernel, uint32_t bytes) {
@@ -624,6 +629,15 @@ int halo_cuda_repacked_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes)
     if (repacked_row_bytes(wtype, 256) == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "weight type id %u has no repacked layout", wtype);
     if (cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "%llu elements is not a multiple of the repacked group size 256", (unsigned long long)cols);
     *bytes = repacked_row_bytes(wtype, cols);
+    return 0;
+}
+
+int halo_cuda_repacked_variant(uint32_t wtype, uint64_t cols, uint32_t* variant_id) {
+    if (variant_id == nullptr) return fail(HALO_CUDA_E_API, "null out pointer");
+    uint64_t bytes = 0;
+    if (int rc = halo_cuda_repacked_row_bytes(wtype, cols, &bytes)) return rc;
+    if (cols > UINT32_MAX) return fail(HALO_CUDA_E_UNSUPPORTED, "%llu columns exceed 32-bit extents", (unsigned long long)cols);
+    *variant_id = repacked_variant(wtype, static_cast<uint32_t>(cols));
     return 0;
 }
 

@@ -113,6 +113,12 @@ bool supports_format(const GemvCall& c) {
     return max_tile<F>(c.cols / 256u, 0) != 0;  // one row's records must fit whatever the partition
 }
 
+/// Whether rows of `cols` columns can run at all: one row's records next to the ring (a function of the format and K alone).
+template <class F>
+bool fits_format(uint32_t cols) {
+    return cols != 0 && cols % 256u == 0 && max_tile<F>(cols / 256u, 0) != 0;
+}
+
 template <class F>
 int launch_format(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
     sk::Geometry g{};

@@ -3,5 +3,6 @@
 
 namespace halo_cuda {
 bool gemv_i8_q80r_supports(const GemvCall& c) { return i8::supports_format<i8::Q80i>(c); }
+bool gemv_i8_q80r_fits(uint32_t cols) { return i8::fits_format<i8::Q80i>(cols); }
 int launch_gemv_i8_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) { return i8::launch_format<i8::Q80i>(ctx, c, s); }
 }  // namespace halo_cuda

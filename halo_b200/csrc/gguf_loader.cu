@@ -494,6 +494,7 @@ void even_part(uint64_t n, uint32_t parts, uint32_t i, uint64_t* begin, uint64_t
 }
 
 struct Share {
+    uint64_t max_cols;  // the largest local K over the ranks (decides the variant of a repacked tensor alike on every rank)
     uint64_t row0, rows, k0, cols;
     uint64_t byte0, row_bytes;  // of the share inside a source row
     uint64_t src_row_bytes;
@@ -510,7 +511,7 @@ int plan_share(uint32_t wtype, uint64_t rows, uint64_t cols, const HaloCudaUploa
     const uint32_t rank = how != nullptr && world > 1 ? how->rank : 0;
     if (split > HALO_CUDA_SPLIT_ROW) return fail(HALO_CUDA_E_API, "upload: unknown split mode %u", split);
     if (rank >= world) return fail(HALO_CUDA_E_API, "upload: rank %u of %u", rank, world);
-    *s = Share{0, rows, 0, cols, 0, 0, cols / ti.block_elems * ti.block_bytes, false};
+    *s = Share{cols, 0, rows, 0, cols, 0, 0, cols / ti.block_elems * ti.block_bytes, false};
     if (split == HALO_CUDA_SPLIT_COLUMN && world > 1) {
         uint64_t b, e;
         even_part(rows, world, rank, &b, &e);
@@ -522,6 +523,8 @@ int plan_share(uint32_t wtype, uint64_t rows, uint64_t cols, const HaloCudaUploa
         s->k0 = b * ti.block_elems;
         s->cols = (e - b) * ti.block_elems;
         s->byte0 = b * ti.block_bytes;
+        even_part(cols / ti.block_elems, world, 0, &b, &e);  // rank 0 holds a largest share
+        s->max_cols = (e - b) * ti.block_elems;
     }
     s->row_bytes = s->cols / ti.block_elems * ti.block_bytes;
     // The repacked layout selects the kernel variant, and with it whether a row split reduces through the peer epilogue or a
@@ -545,7 +548,7 @@ void fill_matrix(uint32_t wtype, const Share& s, HaloCudaMatrix* out) {
     out->cols = uint32_t(s.cols);
     out->row0 = uint32_t(s.row0);
     out->k0 = uint32_t(s.k0);
-    out->variant_id = s.repack ? HALO_CUDA_GEMV_MMA_R : HALO_CUDA_GEMV_DEFAULT;
+    out->variant_id = s.repack ? repacked_variant(wtype, uint32_t(s.max_cols)) : HALO_CUDA_GEMV_DEFAULT;
     out->w_stride = s.repack ? repacked_row_bytes(wtype, s.cols) : s.row_bytes;
     out->bytes = s.rows * out->w_stride;
 }

@@ -143,6 +143,12 @@ bool gemv_i8_q6kr_supports(const GemvCall& c);
 bool gemv_i8_q80r_supports(const GemvCall& c);
 bool gemv_i8_q40r_supports(const GemvCall& c);
 bool gemv_i8_r_supports(const GemvCall& c);   // the three above by weight type
+bool gemv_i8_q6kr_fits(uint32_t cols);
+bool gemv_i8_q80r_fits(uint32_t cols);
+bool gemv_i8_q40r_fits(uint32_t cols);
+/// The variant a repacked tensor of this type and (largest local) K travels with: the int8 family where its x records fit in
+/// shared memory, else the fp16 family's repacked kernel (which can stream x).
+uint32_t repacked_variant(uint32_t wtype, uint32_t cols);
 bool reads_repacked_rows(uint32_t variant_id);  // the W operand of this variant is in the layout of halo_cuda_repack_rows
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout

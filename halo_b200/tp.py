@@ -64,6 +64,13 @@ def repacks(wtype: int, rows: int, cols: int, mode: str, tp: int) -> bool:
     return cols % 256 == 0
 
 
+def largest_local_cols(wtype: int, cols: int, mode: str, tp: int) -> int:
+    """The largest K any rank multiplies: what decides the kernel variant of a repacked tensor, alike on every rank."""
+    if mode != "row":
+        return cols
+    return max(e - b for b, e in row_ranges(wtype, cols, tp))
+
+
 @dataclass
 class Shard:
     mode: str            # "column" | "row"

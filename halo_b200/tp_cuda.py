@@ -17,7 +17,7 @@ from . import capi, gguf, synth, tp
 
 def variant_pushes(wtype: int, variant: int) -> bool:
     """Whether the kernel a projection runs has the peer epilogue: the tensor-core skinny variants."""
-    return variant == capi.GEMV_MMA_R or (variant == 0 and wtype == synth.Q4_K)
+    return variant in capi.REPACKED_VARIANTS or (variant == 0 and wtype == synth.Q4_K)
 
 
 class CudaTp:
@@ -84,7 +84,7 @@ class CudaTp:
             packed = self.be.repack(st, wtype, hb.TensorRef.of(buf), shard.rows, shard.cols)
             torch.cuda.current_stream(self.device).synchronize()
             buf.free()
-            buf, variant = packed, capi.GEMV_MMA_R
+            buf, variant = packed, self.be.repacked_variant(wtype, tp.largest_local_cols(wtype, cols, mode, self.world))
         shard.weights = np.empty((0, 0), np.uint8)  # the host copy is not needed any more
         return self._projection(shard, buf, variant)
 
@@ -99,7 +99,7 @@ class CudaTp:
             packed = self.be.repack(st, wtype, hb.TensorRef.of(buf), shard.rows, shard.cols)
             torch.cuda.current_stream(self.device).synchronize()
             buf.free()
-            buf, variant = packed, capi.GEMV_MMA_R
+            buf, variant = packed, self.be.repacked_variant(wtype, cols)
         shard.weights = np.empty((0, 0), np.uint8)
         return self._projection(shard, buf, variant), where
 

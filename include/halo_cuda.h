@@ -210,6 +210,10 @@ size_t halo_cuda_last_error(char* buf, size_t len);
  * of 256.  halo_cuda_repacked_row_bytes gives the size of a repacked row (E_UNSUPPORTED for types without one);
  * halo_cuda_repack_rows converts `rows` raw GGUF rows (any alignment) into 16-byte aligned repacked rows on the device. */
 int halo_cuda_repacked_row_bytes(uint32_t wtype, uint64_t cols, uint64_t* bytes);
+/* The variant id a loader passes with a tensor it has repacked: HALO_CUDA_GEMV_MMA_I8X2_R where the x records of one row of
+ * `cols` columns fit in shared memory next to the weight ring, else HALO_CUDA_GEMV_MMA_R.  Under a row split (K cut over
+ * ranks) pass the LARGEST local K, so that every rank picks the same family and with it the same reduction. */
+int halo_cuda_repacked_variant(uint32_t wtype, uint64_t cols, uint32_t* variant_id);
 int halo_cuda_repack_rows(HaloCudaCtx* ctx, uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride,
                           uint32_t rows, uint32_t cols, HaloCudaStream stream);
 

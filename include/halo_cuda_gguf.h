@@ -83,7 +83,7 @@ int halo_gguf_tensor_data(const HaloGguf* g, uint64_t index, const void** data, 
 typedef struct HaloCudaUpload {
     uint32_t split;
     uint32_t rank, world; /* world 0 or 1 = the whole matrix */
-    uint32_t repack;      /* 1: store the rows in the layout of HALO_CUDA_GEMV_MMA_R when the type and the local K allow it */
+    uint32_t repack;      /* 1: store the rows in the repacked layout (halo_cuda_repack_rows) when the type and the local K allow it */
     uint64_t staging_bytes; /* size of each of the two pinned staging buffers; 0 = 32 MiB */
 } HaloCudaUpload;
 
@@ -93,7 +93,7 @@ typedef struct HaloCudaMatrix {
     uint64_t w_stride;
     uint64_t bytes;
     uint32_t wtype;
-    uint32_t variant_id; /* HALO_CUDA_GEMV_MMA_R when repacked, else HALO_CUDA_GEMV_DEFAULT */
+    uint32_t variant_id; /* when repacked: halo_cuda_repacked_variant of the largest local K; else HALO_CUDA_GEMV_DEFAULT */
     uint32_t rows, cols; /* local */
     uint32_t row0, k0;   /* first global row / K element of the share */
 } HaloCudaMatrix;

@@ -4,6 +4,7 @@ typed metadata, tensor geometry, alignment, and a typed error -- never a crash -
 """
 from __future__ import annotations
 
+import ctypes as C
 import struct
 
 import numpy as np
@@ -260,11 +261,22 @@ def test_share_extents_match_the_tensor_parallel_split():
                 assert (m.row0, m.rows, m.k0, m.cols) == (0, rows, k0, k1 - k0)
                 assert m.row_stride == (synth.row_bytes(wtype, k1 - k0) if k1 > k0 else 0)
     whole = matrix_share(Q6_K, 5120, 17408, repack=True)
-    assert whole.variant_id == capi.GEMV_MMA_R and whole.row_stride == 17408 // 256 * 224
+    assert whole.variant_id == capi.GEMV_MMA_I8X2_R and whole.row_stride == 17408 // 256 * 224  # 68 super-blocks of x fit next to the ring
     assert matrix_share(Q4_K, 64, 512, repack=True).variant_id == capi.GEMV_DEFAULT  # Q4_K has no repacked layout
     assert matrix_share(Q8_0, 64, 96, repack=True).variant_id == capi.GEMV_DEFAULT   # K is not a whole number of 256-element groups
     assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 4, repack=True).variant_id == capi.GEMV_DEFAULT  # 384 local columns: one and a half groups
-    assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 2, repack=True).variant_id == capi.GEMV_MMA_R
+    assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 2, repack=True).variant_id == capi.GEMV_MMA_I8X2_R
+    # K beyond what the int8 kernels keep resident: the fp16 family's repacked kernel, which streams x; both ranks of an uneven row
+    # split decide from the larger share
+    assert matrix_share(Q8_0, 8, 32768, repack=True).variant_id == capi.GEMV_MMA_R
+    lib = capi.load()
+    v = C.c_uint32()
+    assert lib.halo_cuda_repacked_variant(Q8_0, 24064, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_I8X2_R
+    assert lib.halo_cuda_repacked_variant(Q8_0, 24320, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_R
+    assert lib.halo_cuda_repacked_variant(Q6_K, 44288, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_I8X2_R
+    pair = {matrix_share(Q6_K, 8, 44544 + 44288, capi.SPLIT_ROW, r, 2, repack=True).variant_id for r in (0, 1)}  # 174 + 173 super-blocks
+    assert pair == {capi.GEMV_MMA_R}
+    assert lib.halo_cuda_repacked_variant(Q4_K, 5120, C.byref(v)) == capi.E_UNSUPPORTED
     for bad, status in (((Q5_K, 4, 256), capi.E_UNSUPPORTED), ((Q4_K, 4, 100), capi.E_MODEL)):
         with pytest.raises(HaloError) as e:
             matrix_share(*bad)

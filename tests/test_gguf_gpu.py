@@ -85,7 +85,7 @@ def test_repacking_upload_equals_repack_after_import(be, model, t):
         if want.cols % 256 != 0:
             assert m.variant_id == capi.GEMV_DEFAULT and np.array_equal(fetch(be, st, m).reshape(-1), want.weights.reshape(-1))
             continue
-        assert m.variant_id == capi.GEMV_MMA_R and m.row_stride == be.repacked_row_bytes(t, want.cols)
+        assert m.variant_id == capi.GEMV_MMA_I8X2_R and m.row_stride == be.repacked_row_bytes(t, want.cols)
         wb = be.import_host_readonly(want.weights.reshape(-1))
         pk = be.repack(st, t, hb.TensorRef.of(wb), want.rows, want.cols)
         ref = np.empty(want.rows * m.row_stride, np.uint8)

@@ -196,7 +196,7 @@ def test_every_rank_of_a_split_chooses_the_same_kernel_layout():
                     variants.add(m.variant_id)
             assert len(variants) <= 1, (wtype, rows, cols, world, mode)
             if variants:
-                assert (variants == {capi.GEMV_MMA_R}) == want, (wtype, rows, cols, world, mode)
+                assert (variants <= set(capi.REPACKED_VARIANTS)) == want, (wtype, rows, cols, world, mode)
     assert not tp.repacks(synth.Q8_0, 40, 544, "row", 2)       # 288 + 256 columns: one rank could repack, the other not
     assert tp.repacks(synth.Q8_0, 40, 1536, "row", 2) and not tp.repacks(synth.Q8_0, 40, 1536, "row", 4)
     assert tp.repacks(synth.Q6_K, 40, 5120, "row", 8)           # 3,3,3,3,2,2,2,2 super-blocks: all whole groups
