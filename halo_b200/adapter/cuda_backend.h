@@ -42,10 +42,10 @@ struct CudaPlanEntry {
 /// Throws Error(Device) when no sm_100 device is usable, Error(Config) for an unknown default variant.
 [[nodiscard]] std::unique_ptr<Backend> make_cuda_backend(const CudaBackendOptions& options = {});
 
-/// The load-time weight repack of the gemv_mma_r variant (id 7), the counterpart of tensor::gemv_repack for the
+/// The load-time weight repack of the variants gemv_mma_r (id 7) and gemv_mma_i8x2_r (id 9), the counterpart of tensor::gemv_repack for the
 /// reference's repacked Vulkan matvecs (include/halo/tensor/repack.h:11-36): `rows` raw GGUF rows of Q6_K / Q8_0 /
 /// Q4_0 (cols a multiple of 256) -> a new read-only device buffer in the repacked row layout, to be passed as
-/// GemvArgs::w together with KernelChoice{7}.  Error(Unsupported) for other types, Error(Api) for another backend.
+/// GemvArgs::w together with KernelChoice{7} or KernelChoice{9}.  Error(Unsupported) for other types, Error(Api) for another backend.
 [[nodiscard]] std::unique_ptr<Buffer> cuda_backend_repack(Backend& backend, Stream& stream, DType wtype, const TensorRef& src, std::uint32_t rows,
                                                           std::uint32_t cols);
 
@@ -54,11 +54,12 @@ struct CudaPlanEntry {
 struct CudaSplit {
     enum class Mode : std::uint32_t { None = 0, Column = 1, Row = 2 } mode = Mode::None;
     std::uint32_t rank = 0, world = 1;
-    bool repack = false;  ///< store Q6_K / Q8_0 / Q4_0 rows in the gemv_mma_r layout when the local K is a multiple of 256
+    bool repack = false;  ///< store Q6_K / Q8_0 / Q4_0 rows in the repacked layout when the local K is a multiple of 256
 };
 
 /// A device-resident matmul operand with what GemvArgs needs beside it: the counterpart of the model's Mat
-/// (src/models/qwen35.cpp:52-67).  `kernel` is KernelChoice{7} for repacked rows, else KernelChoice{}.
+/// (src/models/qwen35.cpp:52-67).  `kernel` is the repacked variant the loader chose (KernelChoice{9} where the int8 kernels hold the
+/// local K in shared memory, else KernelChoice{7}) for repacked rows, else KernelChoice{}.
 struct CudaMat {
     std::unique_ptr<Buffer> buf;  ///< null for an empty share
     DType type = DType::F32;

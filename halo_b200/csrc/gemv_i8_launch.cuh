@@ -37,10 +37,10 @@ void plan(const HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry* g) {
     g->ks = plan_partition_i8(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), slices_fit<F>(g->nb), &g->table);
 }
 
-template <class F, int NTOK, int KSC>
+template <class F, int NTOK, int KSC, int NS = kRing>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;
-    using L = Layout<F, NTOK, kRing>;
+    using L = Layout<F, NTOK, NS>;
     const uint32_t ks_shift = log2_of(g.ks), n_rec = sk::resident_records(g), smem_bytes = L::bytes(n_rec, ks_shift);
     if (smem_bytes > kSmemBudget) return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x records of %d rows do not fit in shared memory", n_rec, NTOK);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
@@ -61,7 +61,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     const cudaLaunchConfig_t cfg = sk::pdl_config(g.table.parts, smem_bytes, s, attr);
     if (c.norm_w != nullptr) {
         if constexpr (NTOK == 1) {
-            auto kern = gemv_i8_kernel<F, 1, kRing, KSC, false, true>;
+            auto kern = gemv_i8_kernel<F, 1, NS, KSC, false, true>;
             if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
             HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                        static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), c.norm_w, c.norm_eps));
@@ -70,7 +70,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
             return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
         }
     }
-    auto kern = gemv_i8_kernel<F, NTOK, kRing, KSC, PRE, false>;
+    auto kern = gemv_i8_kernel<F, NTOK, NS, KSC, PRE, false>;
     if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
     HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), static_cast<const float*>(nullptr),

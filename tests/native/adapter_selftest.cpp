@@ -156,7 +156,7 @@ void test_gemv_bitwise(Pair& p, Report& r) {
     }
 }
 
-/// The repacked-layout tensor-core variant through the adapter: repack once, KernelChoice{7}, rows of any batch size.
+/// The repacked-layout tensor-core variants through the adapter: repack once, KernelChoice{7} (fp16 family) and {9} (int8 family), rows of any batch size.
 void test_gemv_repacked(Pair& p, Report& r) {
     struct Case {
         DType t;
@@ -172,15 +172,17 @@ void test_gemv_repacked(Pair& p, Report& r) {
         const auto packed = hb::cuda_backend_repack(*p.gpu, *p.gst, c.t, hb::TensorRef::of(*raw), c.n, c.k);
         const auto xb = p.gpu->import_host_readonly(cbytes(x.data(), x.size() * 4));
         const auto yb = p.gpu->allocate(yg.size() * 4, hb::Tier::Vram);
-        p.gpu->gemv(*p.gst, {c.t, hb::TensorRef::of(*packed), hb::TensorRef::of(*xb), hb::TensorRef::of(*yb), c.n, c.k, c.m, {7}});
-        p.gpu->download(*p.gst, hb::TensorRef::of(*yb), wbytes(yg.data(), yg.size() * 4));
-        p.gst->wait();
-        float maxref = 0, maxerr = 0;
-        for (std::size_t i = 0; i < yc.size(); ++i) {
-            maxref = std::max(maxref, std::fabs(yc[i]));
-            maxerr = std::max(maxerr, std::fabs(yc[i] - yg[i]));
+        for (const std::uint32_t variant : {7u, 9u}) {
+            p.gpu->gemv(*p.gst, {c.t, hb::TensorRef::of(*packed), hb::TensorRef::of(*xb), hb::TensorRef::of(*yb), c.n, c.k, c.m, {variant}});
+            p.gpu->download(*p.gst, hb::TensorRef::of(*yb), wbytes(yg.data(), yg.size() * 4));
+            p.gst->wait();
+            float maxref = 0, maxerr = 0;
+            for (std::size_t i = 0; i < yc.size(); ++i) {
+                maxref = std::max(maxref, std::fabs(yc[i]));
+                maxerr = std::max(maxerr, std::fabs(yc[i] - yg[i]));
+            }
+            r.expect(maxerr <= 1e-3f * maxref, std::format("variant {} over repacked rows within 1e-3 of the CPU backend (type {}): {} vs {}", variant, static_cast<int>(c.t), maxerr, maxref));
         }
-        r.expect(maxerr <= 1e-3f * maxref, std::format("gemv_mma_r over repacked rows within 1e-3 of the CPU backend (type {}): {} vs {}", static_cast<int>(c.t), maxerr, maxref));
         // a raw-sized operand must not pass as a repacked one where the layouts differ in size
         if (c.t == DType::Q6_K) {
             bool thrown = false;
@@ -287,7 +289,7 @@ void test_load_mat(Pair& p, Report& r) {
         std::vector<double> sum(yc.size(), 0.0);
         for (std::uint32_t rank = 0; rank < 2; ++rank) {
             const hb::CudaMat part = hb::cuda_backend_load_mat(*p.gpu, *p.gst, file, e.name, {hb::CudaSplit::Mode::Row, rank, 2, true});
-            r.expect((part.kernel.variant_id == 7) == (e.t != DType::Q4_K), std::format("{}: row share {} repacked iff the type has the layout", e.name, rank));
+            r.expect((part.kernel.variant_id == 9) == (e.t != DType::Q4_K), std::format("{}: row share {} repacked (int8 family: its K fits) iff the type has the layout", e.name, rank));
             const auto xr = hb::TensorRef::of(*xb).shifted(std::uint64_t{part.k0} * 4).with_stride(std::uint64_t{e.k} * 4);
             const auto y = run(part, xr, part.kernel);
             for (std::size_t i = 0; i < y.size(); ++i) sum[i] += y[i];
