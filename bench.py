@@ -223,7 +223,7 @@ def time_token_pass(projs, xs_of, m: int, steps: int, world: int):
 
     def one_token():
         for p in projs:
-            p(xs[p.shard.cols])
+            p(xs[p.full_cols])  # the projection cuts its own K range out of a full-width x (row split)
 
     for _ in range(3):
         one_token()
@@ -293,13 +293,17 @@ def tp_sweep(local_rank: int, rank: int, world: int, steps: int, n_layers: int =
                 proj, _ = rt.load_group(wtype, ws, k)
             else:
                 proj = rt.load(wtype, ws[0][0], ws[0][1], k, "row")
-            loaded.append((proj.shard, proj.buf, proj.variant))
+            loaded.append((proj.shard, proj.buf, proj.variant, k))
             total_bytes += sum(n * synth.row_bytes(wtype, k) for _, n in members)
             launches += 1
 
     def projections(fused: bool):
         keep, rt.peers = rt.peers, (rt.peers if fused else None)
-        out = [rt._projection(sh, buf, variant) for sh, buf, variant in loaded]
+        out = []
+        for sh, buf, variant, k in loaded:
+            p = rt._projection(sh, buf, variant)
+            p.full_cols = k
+            out.append(p)
         rt.peers = keep
         return out
 
@@ -353,7 +357,7 @@ def tp_sweep(local_rank: int, rank: int, world: int, steps: int, n_layers: int =
     out["workload"] = (f"cfg3: {n_layers} layers ({n_layers - n_layers // 4} GDN + {n_layers // 4} GQA), {total_bytes / 1e9:.2f} GB of Q4_K / Q6_K "
                        f"weights per token, tp={world}: column split of the grouped qkv / gate|up operands, row split + reduction out / o / down")
     out["scaling"] = "strong"
-    for _, buf, _ in loaded:
+    for _, buf, _, _ in loaded:
         buf.free()
     rt.close()
     return out

@@ -53,3 +53,30 @@ def test_two_streams_do_not_share_scratch():
     for (ya, yb), y in zip(got, want):
         assert np.array_equal(bits(ya), bits(y)) and np.array_equal(bits(yb), bits(y))
     assert be.scratch_bytes() > 0
+
+
+def test_two_devices_in_one_process_each_raise_their_own_kernel_attributes():
+    """A kernel's opt-in to large dynamic shared memory is a per-device attribute: a second context on another device must set it
+    again for itself (a process-wide "already done" flag would leave the second device's launches refused)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    t, n, k = synth.Q4_K, 2176, 5120
+    w = synth.quant_weights(t, n, k, 60, 1)
+    x = synth.activations(20, k, 60, 2)
+    ys = []
+    for dev in (0, 1):
+        be = hb.CudaBackend(dev)
+        st = be.create_stream()
+        wb, xb = be.import_host_readonly(w.reshape(-1)), be.import_host_readonly(x)
+        got = []
+        for m, variant, gemm in ((1, 0, False), (5, 0, False), (3, capi.GEMV_MMA_F16X2, False), (20, capi.GEMM_TCGEN05_F16, True)):
+            yb = be.allocate(m * n * 4)
+            be.gemv(st, hb.GemvArgs(t, hb.TensorRef.of(wb), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, variant, allow_gemm=gemm))
+            y = np.empty((m, n), np.float32)
+            be.download(st, hb.TensorRef.of(yb), y)
+            st.wait()
+            got.append(y)
+        ys.append(got)
+    for a, b in zip(*ys):
+        assert np.array_equal(bits(a), bits(b)), "the two devices run the same kernels on the same bytes"
