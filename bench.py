@@ -506,6 +506,35 @@ def fused_norm_leg(be, st, reps: int = 20, copies: int = 8):
             ns = C.c_uint64()
             lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
             row[key] = ns.value / 1e3 / (reps * copies)
+        # what the fusion replaces: a separate RMS-norm kernel in front of the plain matmul, on the same stream (the norm is
+        # torch's own rms_norm kernel, a library stand-in for the operator this backend does not have)
+        import torch
+        import torch.nn.functional as F
+        ts = torch.cuda.ExternalStream(st.handle)
+        with torch.cuda.stream(ts):
+            xt = torch.from_numpy(synth.activations(1, k, 0, 2)).to("cuda")
+            wt = torch.full((k,), 1.25, device="cuda", dtype=torch.float32)
+            structs = [be._gemv_struct(hb.GemvArgs(t, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, 1, variant), "MATMUL", False)
+                       for b in bufs]
+
+            def unfused():
+                for g in structs:
+                    xn = F.rms_norm(xt, (k,), wt, 1e-6)
+                    g.x = xn.data_ptr()
+                    rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+                    if rc != 0:
+                        raise hb.HaloError(rc, capi.last_error())
+
+            unfused()
+            st.wait()
+            lib.halo_cuda_event_record(ctx, e0, st.handle)
+            for _ in range(reps):
+                unfused()
+            lib.halo_cuda_event_record(ctx, e1, st.handle)
+            st.wait()
+        ns = C.c_uint64()
+        lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+        row["us_rms_norm_kernel_then_plain"] = ns.value / 1e3 / (reps * copies)
         out.append(row)
         for b in bufs + [xb, nw, yb]:
             b.free()

@@ -71,13 +71,16 @@ __device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta,
     se = max(-100, min(100, se));
     float s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
     if (m * s > 32639.0f) se -= 1, s = __uint_as_float(static_cast<uint32_t>(127 + se) << 23);
+    // |f * s| <= 32639 for every element by the choice of s (a power of two: the product is exact), so the conversion needs no
+    // clamp.  A super-block with an infinity is multiplied by 0 instead: inf * 0 and NaN * anything are NaN, which converts to 0.
+    const float mul = finite ? s : 0.0f;
     const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     int q[8], h[8], sum = 0;
     bool bad = !finite;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         bad |= f[i] != f[i];
-        q[i] = __float2int_rn(fminf(fmaxf(f[i] * s, -32639.0f), 32639.0f));
+        q[i] = __float2int_rn(f[i] * mul);
         h[i] = (q[i] + 128) >> 8;
         sum += q[i];
     }
@@ -702,7 +705,8 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             mbar_expect_tx(bars + fill_slot * 8u, kSlot);
             sk::tma_item_g2s<F>(ring + fill_slot * kSlot, &wmap, p_k * KS + ks, (p_unit * R + r) * 16u, bars + fill_slot * 8u);
         }
-        fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
+        if constexpr (NS == 2) fill_slot ^= 1u;
+        else fill_slot = fill_slot + 1 == NS ? 0 : fill_slot + 1;
         if (++p_k >= p_end) settle();
     };
 #pragma unroll
@@ -809,11 +813,16 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
             for (int p = 0; p < (NTOK == 1 ? 1 : 4); ++p) P[gi][rr][p] = 0.0f;
 
-    uint32_t slot = 0, parity = 0;
+    uint32_t slot = 0, parity = 0, taken = 0;  // tiles this warp has consumed: slot = taken mod NS, parity = (taken / NS) mod 2
     auto release = [&]() {
         __syncwarp();
-        slot = slot + 1 == NS ? 0 : slot + 1;
-        parity ^= (slot == 0);
+        ++taken;
+        if constexpr (NS == 2) {
+            slot = taken & 1u, parity = (taken >> 1) & 1u;
+        } else {
+            slot = slot + 1 == NS ? 0 : slot + 1;
+            parity ^= (slot == 0);
+        }
         refill();
     };
     // A warp that lost a copy keeps walking (its sums are garbage, the error word says so): its siblings wait for it at the barriers.
