@@ -20,6 +20,11 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
                                                           const unsigned long long* __restrict__ slots, uint32_t* epoch, uint32_t* blocks_done,
                                                           uint32_t world, uint32_t capacity, uint32_t* error_word,
                                                           uint32_t polls /* reads of one word (~0.2 us apart once sleeping) before its sender is declared lost */) {
+    // Launched as a programmatic dependent of the matmul that pushes: resident (and past its launch latency) while that kernel
+    // still runs; the kernel behind this one may fill its weight ring meanwhile.  The wait orders this kernel behind everything
+    // earlier in the stream: the previous reduction's epoch, earlier readers of y.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t next = *epoch + 1u, set = next & 1u;
     const uint64_t count = uint64_t{rows} * n_vec;
     const unsigned long long* base = slots + uint64_t{set} * world * capacity;
@@ -62,9 +67,17 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
 int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, cudaStream_t s) {
     const uint64_t count = uint64_t{rows} * n_vec;
     const uint32_t grid = static_cast<uint32_t>(count / 1024 < 1 ? 1 : count / 1024 > 64 ? 64 : count / 1024);
-    peer_finish_kernel<<<grid, 256, 0, s>>>(y, y_stride, rows, n_vec, static_cast<const unsigned long long*>(p.slots[p.rank]), p.epoch, p.done,
-                                            p.world, p.capacity, ctx->error_word_dev, ctx->peer_wait_polls);
-    HC_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HC_CUDA(cudaLaunchKernelEx(&cfg, peer_finish_kernel, y, y_stride, rows, n_vec, static_cast<const unsigned long long*>(p.slots[p.rank]), p.epoch, p.done,
+                               p.world, p.capacity, ctx->error_word_dev, ctx->peer_wait_polls));
     return 0;
 }
 
