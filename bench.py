@@ -541,6 +541,62 @@ def fused_norm_leg(be, st, reps: int = 20, copies: int = 8):
     return out
 
 
+def prefill_repacked_leg(be, st, reps: int = 5):
+    """The prefill GEMM over repacked Q6_K / Q8_0 / Q4_0 rows at M = 2048: the FFN down shape of config 1 in Q6_K and Q8_0, the
+    gate / up shape of config 4 in Q4_0.  A call names the tensor's decode variant and sets allow_gemm, as a model would; each
+    result carries its error against the oracle on a 64-row slice of N.  CUDA events on the launching stream."""
+    import numpy as np
+
+    import oracle
+    from halo_b200 import backend as hb
+    from halo_b200 import capi, synth
+
+    lib, ctx = be.lib, be.ctx
+    pk = peaks()
+    names = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.halo_cuda_event_create(ctx, C.byref(e0))
+    lib.halo_cuda_event_create(ctx, C.byref(e1))
+    chk = oracle.best_checker()
+    m, out = 2048, []
+    for name, t, n, k in (("cfg1 q6_k down", synth.Q6_K, 5120, 17408), ("cfg1 q8_0 down", synth.Q8_0, 5120, 17408),
+                          ("cfg4 q4_0 ffn gate / up", synth.Q4_0, 17408, 5120)):
+        w = synth.quant_weights(t, n, k, 21, 1)
+        x = synth.activations(m, k, 21, 2)
+        raw = be.import_host_readonly(w.reshape(-1))
+        pkd = be.repack(st, t, hb.TensorRef.of(raw), n, k)
+        xb = be.import_host_readonly(x)
+        yb = be.allocate(m * n * 4, zero=False)
+        a = hb.GemvArgs(t, hb.TensorRef.of(pkd), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, be.repacked_variant(t, k), allow_gemm=True)
+        g = be._gemv_struct(a, "MATMUL", False)
+        ran = be.resolve_variant(a)
+        for _ in range(2):
+            if lib.halo_cuda_gemv(ctx, C.byref(g), st.handle) != 0:
+                raise hb.HaloError(-1, capi.last_error())
+        st.wait()
+        lib.halo_cuda_event_record(ctx, e0, st.handle)
+        for _ in range(reps):
+            lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+        lib.halo_cuda_event_record(ctx, e1, st.handle)
+        st.wait()
+        ns = C.c_uint64()
+        lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+        ms = ns.value / 1e6 / reps
+        y = np.empty((m, n), np.float32)
+        be.download(st, hb.TensorRef.of(yb), y)
+        st.wait()
+        n_slice = 64
+        ref = chk.gemv(t, w.reshape(n, -1)[:n_slice], x, n_slice, k)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out.append({"shape": name, "wtype": synth.TYPE_NAMES[t], "rows": n, "cols": k, "m": m, "variant": names.get(ran, str(ran)), "ms_per_call": ms,
+                    "tflops": tf, "frac_of_bf16_burst": tf / pk["bf16_tflops"],
+                    "rel_err_vs_oracle": float(np.max(np.abs(y[:, :n_slice] - ref)) / np.max(np.abs(ref))),
+                    "oracle_sample": f"all {m} x rows on the first {n_slice} of {n} W rows"})
+        for b in (raw, pkd, xb, yb):
+            b.free()
+    return out
+
+
 def loader_leg(be, st, rank: int, world: int, reps: int = 3):
     """File -> device: this rank's column share of the config-4 LM head (Q4_0, 151936 x 5120, 437.6 MB in all) brought from a GGUF
     file in the page cache into HBM by the loader (pinned double-buffered staging, repack on the device), beside the plain
@@ -834,7 +890,7 @@ def run_ours(args) -> None:
             sms = timed(split_pass, psteps) / psteps
             prefill["column_split"] = {"rows_per_gpu": n_split, "ms_per_call": sms, "tflops": flops / (sms * 1e-3) / 1e12, "scaling": "strong"}
 
-    sweep = shapes = loader = fused_norm = None
+    sweep = shapes = loader = fused_norm = prefill_r = None
     if not args.profile:
         for b in wbufs[1:] + ybufs[1:]:
             b.free()
@@ -842,6 +898,7 @@ def run_ours(args) -> None:
         sweep = tp_sweep(local_rank, rank, world, max(3, min(args.steps, 20)))
         loader = loader_leg(be, st, rank, world)
         fused_norm = fused_norm_leg(be, st) if rank == 0 else None
+        prefill_r = prefill_repacked_leg(be, st) if rank == 0 else None
     clocks = sampler.stop() if rank == 0 else None
 
     launches_per_step = COPIES
@@ -868,6 +925,9 @@ def run_ours(args) -> None:
                                           "m2048_frac_of_bf16_burst": r3(prefill["roofline"]["frac"]),
                                           "by_m": [{"m": r["m"], "ms": r3(r["ms_per_call"]), "tflops_per_gpu": r3(r["tflops_per_gpu"])} for r in prefill["by_m"]],
                                           "column_split": prefill.get("column_split"), "rel_err_vs_oracle": prefill.get("rel_err_vs_oracle")}
+    if prefill_r is not None:
+        summary["prefill_repacked_tcgen05_m2048"] = [{"shape": r["shape"], "tflops": r3(r["tflops"]), "ms": r3(r["ms_per_call"]),
+                                                      "rel_err_vs_oracle": r["rel_err_vs_oracle"]} for r in prefill_r]
     if shapes is not None:
         summary["decode_shapes"] = [{"shape": r["shape"], "m": r["m"], "us": r3(r["us_per_call"]), "frac_of_hbm": r3(r["frac_of_hbm_per_gpu"]),
                                      "rel_err": r["rel_err_vs_exact"]} for r in shapes]
@@ -890,6 +950,7 @@ def run_ours(args) -> None:
                 "ms_per_step": e2e_s / args.steps * 1e3},
         "gpu_launches": total_launches,
         "prefill": prefill,
+        "prefill_repacked": prefill_r,
         "decode_shapes": shapes,
         "tp_sweep": sweep,
         "loader": loader,

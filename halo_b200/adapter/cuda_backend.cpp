@@ -386,7 +386,9 @@ private:
         g.wtype = static_cast<std::uint32_t>(a.wtype);
         g.variant_id = a.kernel.variant_id != 0 ? a.kernel.variant_id : options_.default_gemv_variant;
         std::uint64_t rb = 0;
-        if (g.variant_id == HALO_CUDA_GEMV_MMA_R || g.variant_id == HALO_CUDA_GEMV_MMA_I8X2_R) check(halo_cuda_repacked_row_bytes(g.wtype, a.cols, &rb));  // W is in the variant's layout
+        if (g.variant_id == HALO_CUDA_GEMV_MMA_R || g.variant_id == HALO_CUDA_GEMV_MMA_I8X2_R || g.variant_id == HALO_CUDA_GEMM_TCGEN05_F16_R ||
+            g.variant_id == HALO_CUDA_GEMM_TCGEN05_BF16_R)
+            check(halo_cuda_repacked_row_bytes(g.wtype, a.cols, &rb));  // W is in the variant's layout
         else check(halo_cuda_row_bytes(g.wtype, a.cols, &rb));
         g.w = resolve(a.w, extent(a.rows, rb, a.w.row_stride, op, "w"), Access::Read, op, "w");
         g.w_stride = a.w.row_stride;

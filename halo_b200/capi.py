@@ -21,7 +21,8 @@ OP_GET_ROWS, OP_GEMV, OP_LM_HEAD = 0, 3, 14
 GEMV_DEFAULT, GEMV_EXACT8, GEMV_WARP_F32, GEMV_MMA_F16X2, GEMM_TCGEN05_F16, GEMM_TCGEN05_BF16, GEMV_MMA_M1, GEMV_MMA_R = 0, 1, 2, 3, 4, 5, 6, 7
 GEMV_MMA_I8X2 = 8
 GEMV_MMA_I8X2_R = 9
-REPACKED_VARIANTS = (GEMV_MMA_R, GEMV_MMA_I8X2_R)  # W is in the layout of halo_cuda_repack_rows
+GEMM_TCGEN05_F16_R, GEMM_TCGEN05_BF16_R = 10, 11
+REPACKED_VARIANTS = (GEMV_MMA_R, GEMV_MMA_I8X2_R, GEMM_TCGEN05_F16_R, GEMM_TCGEN05_BF16_R)  # W is in the layout of halo_cuda_repack_rows
 FLAG_ALLOW_GEMM = 1
 FLAG_NO_SCRATCH = 0x80000000
 

@@ -23,6 +23,8 @@ constexpr HaloCudaVariant kGemvVariants[] = {
     {HALO_CUDA_GEMV_MMA_R, HALO_CUDA_OP_GEMV, 5, "gemv_mma_r"},
     {HALO_CUDA_GEMV_MMA_I8X2, HALO_CUDA_OP_GEMV, 6, "gemv_mma_i8x2"},
     {HALO_CUDA_GEMV_MMA_I8X2_R, HALO_CUDA_OP_GEMV, 6, "gemv_mma_i8x2_r"},
+    {HALO_CUDA_GEMM_TCGEN05_F16_R, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_f16_r"},
+    {HALO_CUDA_GEMM_TCGEN05_BF16_R, HALO_CUDA_OP_GEMV, 4, "gemm_tcgen05_bf16_r"},
 };
 constexpr HaloCudaVariant kLmHeadVariants[] = {{1, HALO_CUDA_OP_LM_HEAD, 1, "lm_head_gemv_argmax2"}};
 constexpr HaloCudaVariant kGetRowsVariants[] = {{1, HALO_CUDA_OP_GET_ROWS, 0, "get_rows_exact"}};
@@ -81,7 +83,10 @@ int workspace(HaloCudaCtx* ctx, int slot, uint64_t bytes, cudaStream_t stream, v
     return 0;
 }
 
-bool reads_repacked_rows(uint32_t variant_id) { return variant_id == HALO_CUDA_GEMV_MMA_R || variant_id == HALO_CUDA_GEMV_MMA_I8X2_R; }
+bool reads_repacked_rows(uint32_t variant_id) {
+    return variant_id == HALO_CUDA_GEMV_MMA_R || variant_id == HALO_CUDA_GEMV_MMA_I8X2_R || variant_id == HALO_CUDA_GEMM_TCGEN05_F16_R ||
+           variant_id == HALO_CUDA_GEMM_TCGEN05_BF16_R;
+}
 
 bool gemv_i8_r_supports(const GemvCall& c) {
     switch (c.wtype) {
@@ -168,6 +173,11 @@ int validate_gemv(const HaloCudaGemv* a, const char* op, bool y_optional, GemvCa
 }
 
 uint32_t resolve_variant(const HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested) {
+    // A repacked tensor travels with its decode variant (7 or 9); a prefill-sized batch whose caller accepts the GEMM's numerics
+    // runs the GEMM over the same repacked rows.
+    if ((requested == HALO_CUDA_GEMV_MMA_R || requested == HALO_CUDA_GEMV_MMA_I8X2_R) && (c.flags & HALO_CUDA_GEMV_FLAG_ALLOW_GEMM) != 0 &&
+        c.n_vec >= 64 && gemm_tcgen05_supports(c, true))
+        return HALO_CUDA_GEMM_TCGEN05_F16_R;
     if (requested != HALO_CUDA_GEMV_DEFAULT) return requested;
     if (c.cols == 0) return HALO_CUDA_GEMV_EXACT8;
     const bool gemm_ok = (c.flags & HALO_CUDA_GEMV_FLAG_ALLOW_GEMM) != 0;
@@ -254,7 +264,12 @@ int run_gemv(HaloCudaCtx* ctx, const GemvCall& c, uint32_t requested, cudaStream
         case HALO_CUDA_GEMM_TCGEN05_BF16:
             if (!gemm_tcgen05_supports(c))
                 return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemm_tcgen05 needs Q4_K weights in 16-byte-aligned rows and cols %% 256 == 0");
-            return launch_gemm_tcgen05(ctx, c, v == HALO_CUDA_GEMM_TCGEN05_BF16, s);
+            return launch_gemm_tcgen05(ctx, c, v == HALO_CUDA_GEMM_TCGEN05_BF16, false, s);
+        case HALO_CUDA_GEMM_TCGEN05_F16_R:
+        case HALO_CUDA_GEMM_TCGEN05_BF16_R:
+            if (!gemm_tcgen05_supports(c, true))
+                return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: gemm_tcgen05_*_r needs repacked Q6_K / Q8_0 / Q4_0 rows, 16-byte aligned, and 16-byte-aligned x");
+            return launch_gemm_tcgen05(ctx, c, v == HALO_CUDA_GEMM_TCGEN05_BF16_R, true, s);
         default: return fail(HALO_CUDA_E_CONFIG, "MATMUL: unknown kernel variant id %u on the cuda backend", v);
     }
 }

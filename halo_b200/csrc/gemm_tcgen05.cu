@@ -1,9 +1,11 @@
-// gemm_tcgen05_{f16,bf16}: the prefill GEMM, Y[M x N] = X[M x K] * dequant(W)[N x K]^T for Q4_K weights, M >= 64.
+// gemm_tcgen05_{f16,bf16}[_r]: the prefill GEMM, Y[M x N] = X[M x K] * dequant(W)[N x K]^T, M >= 64, for raw Q4_K rows and
+// (the _r variants) for Q6_K / Q8_0 / Q4_0 rows in the repacked layout of halo_cuda_repack_rows (gemv_mma_grouped.cu).
 //
 // The reference's own GEMM path rounds x and dequant(W) to fp16 and accumulates in fp32
 // (backends/vulkan/shaders/common/matmul_cm_main.glsl:1-6); a caller opts in with GemvArgs::allow_gemm
 // (include/halo/backend/backend.h:300-304).  Same numerics here: W is dequantized in fp32 exactly as
-// tensor::dequantize_row does ((d*sc)*q - dmin*m, src/tensor/quant.cpp:247-269) and rounded ONCE to the 16-bit type.
+// tensor::dequantize_row does ((d*sc)*q - dmin*m, src/tensor/quant.cpp:247-269; (d*s)*(q-32), :302-327; d*q, :143-151;
+// d*(q-8), :79-90) and rounded ONCE to the 16-bit type.
 //
 // Structure (one 256-token x 256-row output tile per CTA, 576 threads):
 //   warp 0      TMA producer: two 128 x 64 boxes of the 16-bit copy of X per stage (128-byte swizzle)
@@ -138,9 +140,171 @@ __device__ __forceinline__ uint32_t deq_pair(uint32_t masked, float scale, float
     return pack2<BF16>(fmaf(scale, f.x, -minv), fmaf(scale, f.y, -minv));
 }
 
+// ---- what a dequant thread does per K block of 64 weights, by weight format -------------------------------------------------------
+// Thread (row r, half hf) of the B tile owns 32 of the row's 64 weights of the block and writes four 16-byte chunks (8 values
+// each) of the row's 128 bytes; chunk position p holds weights 8p .. 8p+7 of the block in the order (0,2,1,3,4,6,5,7), which is
+// how byte pairs (0,2) and (1,3) fall out of a masked 32-bit word.  fetch() requests the bytes one K block ahead.
+__device__ __forceinline__ void store_chunk(uint8_t* dst, uint32_t pos, uint32_t sw, const uint4& v) {
+    *reinterpret_cast<uint4*>(dst + ((pos ^ sw) << 4)) = v;
+}
+
+struct GemmQ4K {  // raw rows of 144-byte super-blocks: K block j of a super-block = sub-blocks 2j (low nibbles) and 2j + 1 (high)
+    struct Regs {
+        uint4 h, q;
+    };
+    __device__ static __forceinline__ void fetch(Regs& r, const uint8_t* row, uint32_t kb, uint32_t hf) {
+        const uint8_t* blk = row + (kb >> 2) * 144u;
+        r.h = *reinterpret_cast<const uint4*>(blk);
+        r.q = *reinterpret_cast<const uint4*>(blk + 16 + (kb & 3u) * 32 + hf * 16);
+    }
+    template <bool BF16>
+    __device__ static __forceinline__ void emit(const Regs& r, uint32_t kb, uint32_t hf, uint8_t* dst, uint32_t sw) {
+        const uint32_t j = kb & 3u;
+        // 6-bit codes of sub-blocks 2j (low nibbles) and 2j+1 (high nibbles), src/tensor/quant.cpp:236-244
+        const uint32_t s0 = r.h.y, s1 = r.h.z, s2 = r.h.w;
+        uint32_t sc0, mn0, sc1, mn1;
+        if (j < 2) {
+            sc0 = (s0 >> (16 * j)) & 63u;       mn0 = (s1 >> (16 * j)) & 63u;
+            sc1 = (s0 >> (16 * j + 8)) & 63u;   mn1 = (s1 >> (16 * j + 8)) & 63u;
+        } else {
+            const uint32_t sh = 16 * (j - 2);
+            sc0 = ((s2 >> sh) & 0x0Fu) | (((s0 >> (sh + 6)) & 3u) << 4);
+            mn0 = ((s2 >> (sh + 4)) & 0x0Fu) | (((s1 >> (sh + 6)) & 3u) << 4);
+            sc1 = ((s2 >> (sh + 8)) & 0x0Fu) | (((s0 >> (sh + 14)) & 3u) << 4);
+            mn1 = ((s2 >> (sh + 12)) & 0x0Fu) | (((s1 >> (sh + 14)) & 3u) << 4);
+        }
+        const __half2 dd = *reinterpret_cast<const __half2*>(&r.h.x);
+        const float d = __low2float(dd), dmin = __high2float(dd);
+        const float d1 = d * static_cast<float>(sc0), m1 = dmin * static_cast<float>(mn0);
+        const float d2 = d * static_cast<float>(sc1) * 0.0625f, m2 = dmin * static_cast<float>(mn1);
+        const uint32_t q[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {  // 16-byte chunk c: elements 8c..8c+7 of the low-nibble sub-block, c+4: of the high one
+            const uint32_t c = 2 * hf + cc;
+            const uint32_t u0 = q[2 * cc], u1 = q[2 * cc + 1];
+            uint4 lo, hi;
+            lo.x = deq_pair<BF16>(u0 & 0x000F000Fu, d1, m1);
+            lo.y = deq_pair<BF16>((u0 >> 8) & 0x000F000Fu, d1, m1);
+            lo.z = deq_pair<BF16>(u1 & 0x000F000Fu, d1, m1);
+            lo.w = deq_pair<BF16>((u1 >> 8) & 0x000F000Fu, d1, m1);
+            hi.x = deq_pair<BF16>(u0 & 0x00F000F0u, d2, m2);
+            hi.y = deq_pair<BF16>((u0 >> 8) & 0x00F000F0u, d2, m2);
+            hi.z = deq_pair<BF16>(u1 & 0x00F000F0u, d2, m2);
+            hi.w = deq_pair<BF16>((u1 >> 8) & 0x00F000F0u, d2, m2);
+            store_chunk(dst, c, sw, lo);
+            store_chunk(dst, c + 4, sw, hi);
+        }
+    }
+};
+
+/// One 8-value chunk from two words whose bytes are the unsigned codes of weights 0..3 and 4..7 (each < 1024 as a 16-bit lane).
 template <bool BF16>
+__device__ __forceinline__ uint4 chunk_of_bytes(uint32_t w0, uint32_t w1, float scale, float minv) {
+    uint4 v;
+    v.x = deq_pair<BF16>(w0 & 0x00FF00FFu, scale, minv);
+    v.y = deq_pair<BF16>((w0 >> 8) & 0x00FF00FFu, scale, minv);
+    v.z = deq_pair<BF16>(w1 & 0x00FF00FFu, scale, minv);
+    v.w = deq_pair<BF16>((w1 >> 8) & 0x00FF00FFu, scale, minv);
+    return v;
+}
+
+struct GemmQ80R {  // repacked groups of 272 B: d[8] fp16 | chunk c < 4, thread t < 4: words (block 2c, step 0/1), (block 2c+1, step 0/1)
+    struct Regs {
+        uint2 w[4];  // thread t: the words (step 0, step 1) of this thread's block
+        float d;
+    };
+    __device__ static __forceinline__ void fetch(Regs& r, const uint8_t* row, uint32_t kb, uint32_t hf) {
+        const uint8_t* grp = row + (kb >> 2) * 272u;
+        const uint8_t* chunk = grp + 16 + (kb & 3u) * 64 + hf * 8;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) r.w[t] = *reinterpret_cast<const uint2*>(chunk + t * 16);
+        r.d = __half2float(*reinterpret_cast<const __half*>(grp + 2 * (2 * (kb & 3u) + hf)));
+    }
+    template <bool BF16>
+    __device__ static __forceinline__ void emit(const Regs& r, uint32_t kb, uint32_t hf, uint8_t* dst, uint32_t sw) {
+        const float minv = 128.0f * r.d;  // int8 + 128 as an unsigned byte; d * (u - 128) = fma(d, u, -128 d), rounded once
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {     // weights 8g .. 8g+7 of the block: step g / 2, threads 2 (g % 2) and + 1
+            const int t0 = 2 * (g & 1);
+            const uint32_t w0 = (g >> 1 ? r.w[t0].y : r.w[t0].x) ^ 0x80808080u, w1 = (g >> 1 ? r.w[t0 + 1].y : r.w[t0 + 1].x) ^ 0x80808080u;
+            store_chunk(dst, 4 * hf + g, sw, chunk_of_bytes<BF16>(w0, w1, r.d, minv));
+        }
+    }
+};
+
+struct GemmQ40R {  // repacked groups of 144 B: d[8] fp16 | chunk c < 2, thread t < 4: the quant word (bytes 4t..4t+3) of blocks 4c..4c+3
+    struct Regs {
+        uint32_t w[4];  // thread t's word of this thread's block: low nibbles = weights 4t.., high nibbles = weights 16 + 4t..
+        float d;
+    };
+    __device__ static __forceinline__ void fetch(Regs& r, const uint8_t* row, uint32_t kb, uint32_t hf) {
+        const uint8_t* grp = row + (kb >> 2) * 144u;
+        const uint32_t b = 2 * (kb & 3u) + hf;  // block of the group
+        const uint8_t* at = grp + 16 + (b >> 2) * 64 + (b & 3u) * 4;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) r.w[t] = *reinterpret_cast<const uint32_t*>(at + t * 16);
+        r.d = __half2float(*reinterpret_cast<const __half*>(grp + 2 * b));
+    }
+    template <bool BF16>
+    __device__ static __forceinline__ void emit(const Regs& r, uint32_t kb, uint32_t hf, uint8_t* dst, uint32_t sw) {
+        const float minv = 8.0f * r.d, d16 = r.d * 0.0625f;  // a high nibble arrives as 16 q
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // weights 8g .. 8g+7: g < 2 the low nibbles of words 2g, 2g+1; else the high nibbles of words 2(g-2), +1
+            const uint32_t w0 = r.w[2 * (g & 1)], w1 = r.w[2 * (g & 1) + 1];
+            uint4 v;
+            if (g < 2) {
+                v.x = deq_pair<BF16>(w0 & 0x000F000Fu, r.d, minv);
+                v.y = deq_pair<BF16>((w0 >> 8) & 0x000F000Fu, r.d, minv);
+                v.z = deq_pair<BF16>(w1 & 0x000F000Fu, r.d, minv);
+                v.w = deq_pair<BF16>((w1 >> 8) & 0x000F000Fu, r.d, minv);
+            } else {
+                v.x = deq_pair<BF16>(w0 & 0x00F000F0u, d16, minv);
+                v.y = deq_pair<BF16>((w0 >> 8) & 0x00F000F0u, d16, minv);
+                v.z = deq_pair<BF16>(w1 & 0x00F000F0u, d16, minv);
+                v.w = deq_pair<BF16>((w1 >> 8) & 0x00F000F0u, d16, minv);
+            }
+            store_chunk(dst, 4 * hf + g, sw, v);
+        }
+    }
+};
+
+struct GemmQ6KR {  // repacked groups of 224 B: scales[16] int8 | d fp16, pad | half n < 2, thread t < 4: ql words (b, lh) | thread t: qh words (n, lh)
+    struct Regs {
+        uint2 ql[4], qh[4];  // thread t: the words (lh 0, lh 1) of this thread's quarter
+        float ds[2];         // d * scale of the quarter's two 16-weight groups
+    };
+    __device__ static __forceinline__ void fetch(Regs& r, const uint8_t* row, uint32_t kb, uint32_t hf) {
+        const uint8_t* grp = row + (kb >> 2) * 224u;
+        const uint32_t n = (kb >> 1) & 1u, quarter = 2 * (kb & 1u) + hf;  // weights 128 n + 32 quarter .. + 31
+        const uint8_t* ql = grp + 32 + n * 64 + (quarter & 1u) * 8, *qh = grp + 32 + 128 + n * 8;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            r.ql[t] = *reinterpret_cast<const uint2*>(ql + t * 16);
+            r.qh[t] = *reinterpret_cast<const uint2*>(qh + t * 16);
+        }
+        const float d = __half2float(*reinterpret_cast<const __half*>(grp + 16));
+        const char2 sc = *reinterpret_cast<const char2*>(grp + 8 * n + 2 * quarter);
+        r.ds[0] = d * static_cast<float>(sc.x), r.ds[1] = d * static_cast<float>(sc.y);
+    }
+    template <bool BF16>
+    __device__ static __forceinline__ void emit(const Regs& r, uint32_t kb, uint32_t hf, uint8_t* dst, uint32_t sw) {
+        const uint32_t quarter = 2 * (kb & 1u) + hf, nib = (quarter >> 1) * 4, hsh = 2 * quarter;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // weights 8g .. 8g+7 of the quarter: lh = g / 2, threads 2 (g % 2) and + 1
+            const int t0 = 2 * (g & 1), lh = g >> 1;
+            auto codes = [&](int t) {
+                const uint32_t l = lh ? r.ql[t].y : r.ql[t].x, h = lh ? r.qh[t].y : r.qh[t].x;
+                return ((l >> nib) & 0x0F0F0F0Fu) | (((h >> hsh) & 0x03030303u) << 4);
+            };
+            const float ds = r.ds[lh];
+            store_chunk(dst, 4 * hf + g, sw, chunk_of_bytes<BF16>(codes(t0), codes(t0 + 1), ds, 32.0f * ds));  // (d*s)*(q-32), rounded once
+        }
+    }
+};
+
+template <bool BF16, class F>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ w, uint64_t w_stride,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ w, uint64_t w_stride,
                         float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, uint32_t nkb,
                         uint32_t* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
@@ -226,19 +390,12 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
         bool ok = true;
         // the quants of the next K block are requested one iteration ahead, so that their latency hides behind the
         // unpacking of the current block and the wait for a free stage
-        uint4 h_next = make_uint4(0, 0, 0, 0), q_next = make_uint4(0, 0, 0, 0);
-        if (valid) {
-            h_next = *reinterpret_cast<const uint4*>(row);
-            q_next = *reinterpret_cast<const uint4*>(row + 16 + hf * 16);
-        }
+        typename F::Regs next{};
+        if (valid) F::fetch(next, row, 0, hf);
         for (uint32_t kb = 0; kb < nkb; ++kb) {
             const uint32_t s = kb % kStages, use = kb / kStages;
-            const uint4 h = h_next, qa = q_next;
-            if (valid && kb + 1 < nkb) {
-                const uint8_t* nblk = row + ((kb + 1) >> 2) * 144u;
-                h_next = *reinterpret_cast<const uint4*>(nblk);
-                q_next = *reinterpret_cast<const uint4*>(nblk + 16 + ((kb + 1) & 3u) * 32 + hf * 16);
-            }
+            const typename F::Regs cur = next;
+            if (valid && kb + 1 < nkb) F::fetch(next, row, kb + 1, hf);
             if (use > 0) {
                 ok = g_mbar_wait(empty(s), (use - 1) & 1u);
                 ok = __all_sync(0xFFFFFFFFu, ok);
@@ -246,41 +403,7 @@ gemm_q4k_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t*
             }
             uint8_t* dst = smem + s * kStageBytes + 2 * kTileA + r * 128u;
             if (valid) {
-                const uint32_t j = kb & 3u;
-                // 6-bit codes of sub-blocks 2j (low nibbles) and 2j+1 (high nibbles), src/tensor/quant.cpp:236-244
-                const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
-                uint32_t sc0, mn0, sc1, mn1;
-                if (j < 2) {
-                    sc0 = (s0 >> (16 * j)) & 63u;       mn0 = (s1 >> (16 * j)) & 63u;
-                    sc1 = (s0 >> (16 * j + 8)) & 63u;   mn1 = (s1 >> (16 * j + 8)) & 63u;
-                } else {
-                    const uint32_t sh = 16 * (j - 2);
-                    sc0 = ((s2 >> sh) & 0x0Fu) | (((s0 >> (sh + 6)) & 3u) << 4);
-                    mn0 = ((s2 >> (sh + 4)) & 0x0Fu) | (((s1 >> (sh + 6)) & 3u) << 4);
-                    sc1 = ((s2 >> (sh + 8)) & 0x0Fu) | (((s0 >> (sh + 14)) & 3u) << 4);
-                    mn1 = ((s2 >> (sh + 12)) & 0x0Fu) | (((s1 >> (sh + 14)) & 3u) << 4);
-                }
-                const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
-                const float d = __low2float(dd), dmin = __high2float(dd);
-                const float d1 = d * static_cast<float>(sc0), m1 = dmin * static_cast<float>(mn0);
-                const float d2 = d * static_cast<float>(sc1) * 0.0625f, m2 = dmin * static_cast<float>(mn1);
-                const uint32_t q[4] = {qa.x, qa.y, qa.z, qa.w};
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {  // 16-byte chunk c: elements 8c..8c+7 of the low-nibble sub-block, c+4: of the high one
-                    const uint32_t c = 2 * hf + cc;
-                    const uint32_t u0 = q[2 * cc], u1 = q[2 * cc + 1];
-                    uint4 lo, hi;
-                    lo.x = deq_pair<BF16>(u0 & 0x000F000Fu, d1, m1);
-                    lo.y = deq_pair<BF16>((u0 >> 8) & 0x000F000Fu, d1, m1);
-                    lo.z = deq_pair<BF16>(u1 & 0x000F000Fu, d1, m1);
-                    lo.w = deq_pair<BF16>((u1 >> 8) & 0x000F000Fu, d1, m1);
-                    hi.x = deq_pair<BF16>(u0 & 0x00F000F0u, d2, m2);
-                    hi.y = deq_pair<BF16>((u0 >> 8) & 0x00F000F0u, d2, m2);
-                    hi.z = deq_pair<BF16>(u1 & 0x00F000F0u, d2, m2);
-                    hi.w = deq_pair<BF16>((u1 >> 8) & 0x00F000F0u, d2, m2);
-                    *reinterpret_cast<uint4*>(dst + ((c ^ sw) << 4)) = lo;
-                    *reinterpret_cast<uint4*>(dst + (((c + 4) ^ sw) << 4)) = hi;
-                }
+                F::template emit<BF16>(cur, kb, hf, dst, sw);
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + ((4 * hf + c) << 4)) = make_uint4(0, 0, 0, 0);
@@ -365,7 +488,7 @@ int x_map(void* x16, uint32_t n_vec, uint32_t cols, bool bf16, CUtensorMap* out)
     return 0;
 }
 
-template <bool BF16>
+template <bool BF16, class F>
 int launch_t(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
     void* ws = nullptr;
     if (int rc = workspace(ctx, 0, uint64_t{c.n_vec} * c.cols * 2, s, &ws)) return rc;
@@ -375,25 +498,38 @@ int launch_t(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
     HC_CUDA(cudaGetLastError());
     CUtensorMap xmap;
     if (int rc = x_map(ws, c.n_vec, c.cols, BF16, &xmap)) return rc;
-    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(gemm_q4k_tcgen05_kernel<BF16>), kGemmSmem)) return rc;
+    auto kern = gemm_tcgen05_kernel<BF16, F>;
+    if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kGemmSmem)) return rc;
     const dim3 grid((c.rows + kBN - 1) / kBN, (c.n_vec + kBM - 1) / kBM);
-    gemm_q4k_tcgen05_kernel<BF16><<<grid, kGemmThreads, kGemmSmem, s>>>(xmap, c.w, c.w_stride, c.y, c.y_stride, c.rows, c.n_vec, c.cols / kBK,
-                                                                          ctx->error_word_dev);
+    kern<<<grid, kGemmThreads, kGemmSmem, s>>>(xmap, c.w, c.w_stride, c.y, c.y_stride, c.rows, c.n_vec, c.cols / kBK, ctx->error_word_dev);
     HC_CUDA(cudaGetLastError());
     return 0;
 }
 
+template <class F>
+int launch_f(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s) {
+    return bf16 ? launch_t<true, F>(ctx, c, s) : launch_t<false, F>(ctx, c, s);
+}
+
 }  // namespace
 
-bool gemm_tcgen05_supports(const GemvCall& c) {
-    if (c.wtype != HALO_CUDA_T_Q4_K || c.cols == 0 || c.rows == 0) return false;
+/// repacked: W is in the layout of halo_cuda_repack_rows (Q6_K / Q8_0 / Q4_0); else raw Q4_K rows.
+bool gemm_tcgen05_supports(const GemvCall& c, bool repacked) {
+    const bool type_ok = repacked ? (c.wtype == HALO_CUDA_T_Q6_K || c.wtype == HALO_CUDA_T_Q8_0 || c.wtype == HALO_CUDA_T_Q4_0) : c.wtype == HALO_CUDA_T_Q4_K;
+    if (!type_ok || c.cols == 0 || c.rows == 0 || c.cols % 256u != 0) return false;
     if (reinterpret_cast<uintptr_t>(c.w) % 16 != 0 || c.w_stride % 16 != 0) return false;  // 16-byte block loads
     if (reinterpret_cast<uintptr_t>(c.x) % 16 != 0 || c.x_stride % 16 != 0) return false;  // float4 reads of x
     return (c.rows + kBN - 1) / kBN <= 0x7FFFFFFFu && (c.n_vec + kBM - 1) / kBM <= 65535u;
 }
 
-int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s) {
-    return bf16 ? launch_t<true>(ctx, c, s) : launch_t<false>(ctx, c, s);
+int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, bool repacked, cudaStream_t s) {
+    if (!repacked) return launch_f<GemmQ4K>(ctx, c, bf16, s);
+    switch (c.wtype) {
+        case HALO_CUDA_T_Q6_K: return launch_f<GemmQ6KR>(ctx, c, bf16, s);
+        case HALO_CUDA_T_Q8_0: return launch_f<GemmQ80R>(ctx, c, bf16, s);
+        case HALO_CUDA_T_Q4_0: return launch_f<GemmQ40R>(ctx, c, bf16, s);
+        default: return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: no repacked GEMM for weight type id %u", c.wtype);
+    }
 }
 
 }  // namespace halo_cuda

@@ -127,7 +127,7 @@ bool gemv_warp_f32_supports(const GemvCall& c);
 int launch_gemv_mma(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_mma_m1(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 bool gemv_mma_supports(const GemvCall& c);
-int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, cudaStream_t s);
+int launch_gemm_tcgen05(HaloCudaCtx* ctx, const GemvCall& c, bool bf16, bool repacked, cudaStream_t s);
 int launch_gemv_sk_q4k(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q40r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
 int launch_gemv_sk_q80r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s);
@@ -153,7 +153,7 @@ bool reads_repacked_rows(uint32_t variant_id);  // the W operand of this variant
 bool gemv_mma_r_supports(const GemvCall& c);
 uint64_t repacked_row_bytes(uint32_t wtype, uint64_t cols);  // 0 for a type without a repacked layout
 int launch_repack(uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride, uint32_t rows, uint32_t cols, cudaStream_t s);
-bool gemm_tcgen05_supports(const GemvCall& c);
+bool gemm_tcgen05_supports(const GemvCall& c, bool repacked = false);
 int launch_get_rows(const HaloCudaGetRows& a, uint64_t row_bytes, uint64_t table_stride, uint64_t out_stride, cudaStream_t s);
 int launch_argmax(const float* logits, uint64_t stride_elems, uint32_t n, uint32_t n_vec, uint32_t valid, uint32_t row_offset,
                   uint32_t* result, int32_t* ids, void* scratch, cudaStream_t s);

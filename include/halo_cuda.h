@@ -61,7 +61,10 @@ extern "C" {
 #define HALO_CUDA_GEMV_MMA_I8X2 8     /* tensor-core skinny kernel, x as two signed 8-bit digits per element (16-bit fixed point per
                                          256-element super-block), integer MMA; raw Q4_K rows */
 #define HALO_CUDA_GEMV_MMA_I8X2_R 9   /* the same arithmetic over REPACKED Q6_K / Q8_0 / Q4_0 rows (halo_cuda_repack_rows) */
-#define HALO_CUDA_GEMV_VARIANT_MAX 9
+#define HALO_CUDA_GEMM_TCGEN05_F16_R 10  /* the prefill GEMM over REPACKED Q6_K / Q8_0 / Q4_0 rows; also what a call with variant 7 or 9,
+                                            HALO_CUDA_GEMV_FLAG_ALLOW_GEMM and n_vec >= 64 runs */
+#define HALO_CUDA_GEMM_TCGEN05_BF16_R 11 /* same with bf16 operands */
+#define HALO_CUDA_GEMV_VARIANT_MAX 11
 
 #define HALO_CUDA_GEMV_FLAG_ALLOW_GEMM 1u /* GemvArgs::allow_gemm: the caller accepts fp16 GEMM numerics */
 #define HALO_CUDA_GEMV_FLAG_NO_SCRATCH 0x80000000u /* never touch context scratch: the tensor-core variants then take their

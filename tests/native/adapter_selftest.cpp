@@ -117,7 +117,7 @@ void test_registry(Pair& p, Report& r) {
     const auto v = p.gpu->variants(hb::OpId::Gemv);
     const char* names[] = {"gemv_exact8", "gemv_warp_f32", "gemv_mma_f16x2", "gemm_tcgen05_f16", "gemm_tcgen05_bf16", "gemv_mma_m1", "gemv_mma_r",
                            "gemv_mma_i8x2"};
-    r.expect(v.size() == 9, "MATMUL has nine registered variants");
+    r.expect(v.size() == 11, "MATMUL has eleven registered variants");
     for (std::size_t i = 0; i < v.size() && i < 8; ++i)
         r.expect(v[i].id == i + 1 && v[i].name == names[i] && v[i].op == hb::OpId::Gemv, std::format("variant id {} is {}", i + 1, names[i]));
     r.expect(code_of([&] { (void)p.gpu->variants(hb::OpId::RmsNorm); }) == static_cast<int>(ErrorCode::Unsupported), "variants(RMS_NORM) is Unsupported");

@@ -49,7 +49,7 @@ def test_geometry_and_registry_need_no_device():
     assert lib.halo_cuda_variants(capi.OP_GEMV, arr, 16, C.byref(n)) == 0
     got = {arr[i].id: arr[i].name.decode() for i in range(n.value)}
     assert got == {1: "gemv_exact8", 2: "gemv_warp_f32", 3: "gemv_mma_f16x2", 4: "gemm_tcgen05_f16", 5: "gemm_tcgen05_bf16",
-                   6: "gemv_mma_m1", 7: "gemv_mma_r", 8: "gemv_mma_i8x2", 9: "gemv_mma_i8x2_r"}
+                   6: "gemv_mma_m1", 7: "gemv_mma_r", 8: "gemv_mma_i8x2", 9: "gemv_mma_i8x2_r", 10: "gemm_tcgen05_f16_r", 11: "gemm_tcgen05_bf16_r"}
     assert lib.halo_cuda_variants(1, arr, 16, C.byref(n)) == capi.E_UNSUPPORTED  # RMS_NORM is not this backend's
 
 
