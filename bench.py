@@ -541,6 +541,52 @@ def fused_norm_leg(be, st, reps: int = 20, copies: int = 8):
     return out
 
 
+def raw_rows_leg(be, st, reps: int = 10):
+    """What plain Backend::gemv gives on RAW Q6_K / Q8_0 / Q4_0 rows (no repacking loader): variant 0 resolves to gemv_warp_f32
+    there.  The FFN down shape of config 1 at M = 1 and 8, the gate / up shape of config 4 at M = 16; >= 300 MB of weight copies
+    cycled, CUDA events on the launching stream."""
+    from halo_b200 import backend as hb
+    from halo_b200 import capi, synth
+
+    lib, ctx = be.lib, be.ctx
+    pk = peaks()
+    names = {i: n for i, n, _ in be.variants(capi.OP_GEMV)}
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.halo_cuda_event_create(ctx, C.byref(e0))
+    lib.halo_cuda_event_create(ctx, C.byref(e1))
+    out = []
+    for name, t, n, k, ms_list in (("cfg1 q6_k down", synth.Q6_K, 5120, 17408, (1, 8)), ("cfg1 q8_0 down", synth.Q8_0, 5120, 17408, (1, 8)),
+                                   ("cfg4 q4_0 ffn gate / up", synth.Q4_0, 17408, 5120, (16,))):
+        w = synth.quant_weights(t, n, k, 31, 1)
+        copies = max(2, -(-int(300e6) // w.nbytes))
+        bufs = [be.import_host_readonly(w.reshape(-1)) for _ in range(copies)]
+        for m in ms_list:
+            xb = be.import_host_readonly(synth.activations(m, k, 31, 2))
+            yb = be.allocate(m * n * 4)
+            args = [hb.GemvArgs(t, hb.TensorRef.of(b), hb.TensorRef.of(xb), hb.TensorRef.of(yb), n, k, m, 0) for b in bufs]
+            structs = [be._gemv_struct(a, "MATMUL", False) for a in args]
+            ran = be.resolve_variant(args[0])
+            for g in structs:
+                lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+            st.wait()
+            lib.halo_cuda_event_record(ctx, e0, st.handle)
+            for _ in range(reps):
+                for g in structs:
+                    lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+            lib.halo_cuda_event_record(ctx, e1, st.handle)
+            st.wait()
+            ns = C.c_uint64()
+            lib.halo_cuda_event_elapsed_ns(ctx, e0, e1, C.byref(ns))
+            us = ns.value / 1e3 / (reps * copies)
+            out.append({"shape": name, "m": m, "variant": names.get(ran, str(ran)), "us_per_call": us, "weight_gbs": w.nbytes / us / 1e3,
+                        "frac_of_hbm": w.nbytes / us / 1e3 / pk["hbm_gbs"]})
+            xb.free()
+            yb.free()
+        for b in bufs:
+            b.free()
+    return out
+
+
 def prefill_repacked_leg(be, st, reps: int = 5):
     """The prefill GEMM over repacked Q6_K / Q8_0 / Q4_0 rows at M = 2048: the FFN down shape of config 1 in Q6_K and Q8_0, the
     gate / up shape of config 4 in Q4_0.  A call names the tensor's decode variant and sets allow_gemm, as a model would; each
@@ -890,7 +936,7 @@ def run_ours(args) -> None:
             sms = timed(split_pass, psteps) / psteps
             prefill["column_split"] = {"rows_per_gpu": n_split, "ms_per_call": sms, "tflops": flops / (sms * 1e-3) / 1e12, "scaling": "strong"}
 
-    sweep = shapes = loader = fused_norm = prefill_r = None
+    sweep = shapes = loader = fused_norm = prefill_r = raw_rows = None
     if not args.profile:
         for b in wbufs[1:] + ybufs[1:]:
             b.free()
@@ -899,6 +945,7 @@ def run_ours(args) -> None:
         loader = loader_leg(be, st, rank, world)
         fused_norm = fused_norm_leg(be, st) if rank == 0 else None
         prefill_r = prefill_repacked_leg(be, st) if rank == 0 else None
+        raw_rows = raw_rows_leg(be, st) if rank == 0 else None
     clocks = sampler.stop() if rank == 0 else None
 
     launches_per_step = COPIES
@@ -931,6 +978,9 @@ def run_ours(args) -> None:
     if shapes is not None:
         summary["decode_shapes"] = [{"shape": r["shape"], "m": r["m"], "us": r3(r["us_per_call"]), "frac_of_hbm": r3(r["frac_of_hbm_per_gpu"]),
                                      "rel_err": r["rel_err_vs_exact"]} for r in shapes]
+    if raw_rows is not None:
+        summary["raw_rows_default_variant"] = [{"shape": r["shape"], "m": r["m"], "variant": r["variant"], "us": r3(r["us_per_call"]),
+                                                "frac_of_hbm": r3(r["frac_of_hbm"])} for r in raw_rows]
     if sweep is not None:
         summary["tp_sweep"] = {k: ({"ms": r3(v["ms_per_token"]), "gbs": r3(v["weight_gbs"]), "launches": v["launches_per_token"]} if k.startswith("m") else v)
                                for k, v in sweep.items() if k != "workload"}
@@ -952,6 +1002,7 @@ def run_ours(args) -> None:
         "prefill": prefill,
         "prefill_repacked": prefill_r,
         "decode_shapes": shapes,
+        "raw_rows_default_variant": raw_rows,
         "tp_sweep": sweep,
         "loader": loader,
         "fused_norm": fused_norm,
