@@ -30,21 +30,27 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
     const unsigned long long* base = slots + uint64_t{set} * world * capacity;
     bool lost = false;
     for (uint64_t i = uint64_t{blockIdx.x} * blockDim.x + threadIdx.x; i < count && !lost; i += uint64_t{gridDim.x} * blockDim.x) {
+        // every rank's word of this element is requested before any is looked at: one round trip when they have all arrived
+        unsigned long long w[mma::kMaxPeers];
+#pragma unroll
+        for (uint32_t p = 0; p < mma::kMaxPeers; ++p)
+            if (p < world) w[p] = ld_relaxed_sys(base + uint64_t{p} * capacity + i);
         float sum = 0.0f;
-        for (uint32_t p = 0; p < world; ++p) {
-            const unsigned long long* src = base + uint64_t{p} * capacity + i;
-            unsigned long long w = ld_relaxed_sys(src);
-            for (uint32_t n = 0; static_cast<uint32_t>(w >> 32) != next; ++n) {
-                if (n >= polls) {
-                    lost = true;
-                    break;
+#pragma unroll
+        for (uint32_t p = 0; p < mma::kMaxPeers; ++p) {
+            if (p < world && !lost) {
+                const unsigned long long* src = base + uint64_t{p} * capacity + i;
+                for (uint32_t n = 0; static_cast<uint32_t>(w[p] >> 32) != next; ++n) {
+                    if (n >= polls) {
+                        lost = true;
+                        break;
+                    }
+                    if (n > 64) __nanosleep(200);
+                    w[p] = ld_relaxed_sys(src);
                 }
-                if (n > 64) __nanosleep(200);
-                w = ld_relaxed_sys(src);
+                const float v = __uint_as_float(static_cast<uint32_t>(w[p]));
+                sum = p == 0 ? v : sum + v;  // rank order: every rank adds the same numbers in the same order
             }
-            if (lost) break;
-            const float v = __uint_as_float(static_cast<uint32_t>(w));
-            sum = p == 0 ? v : sum + v;
         }
         if (lost) break;
         const uint32_t tk = static_cast<uint32_t>(i / rows), n = static_cast<uint32_t>(i - uint64_t{tk} * rows);
@@ -66,7 +72,8 @@ __global__ void __launch_bounds__(256) peer_finish_kernel(float* __restrict__ y,
 
 int launch_peer_finish(HaloCudaCtx* ctx, const HaloCudaPeerReduce& p, float* y, uint64_t y_stride, uint32_t rows, uint32_t n_vec, cudaStream_t s) {
     const uint64_t count = uint64_t{rows} * n_vec;
-    const uint32_t grid = static_cast<uint32_t>(count / 1024 < 1 ? 1 : count / 1024 > 64 ? 64 : count / 1024);
+    const uint64_t blocks = (count + 255) / 256;  // one element per thread up to 296 blocks: the reads of an element's words overlap
+    const uint32_t grid = static_cast<uint32_t>(blocks < 1 ? 1 : blocks > 296 ? 296 : blocks);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
