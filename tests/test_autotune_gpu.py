@@ -23,12 +23,15 @@ def test_tune_persist_lookup_and_plan(tmp_path):
     db.record_tier_bandwidth(key, tier="vram", processor="gpu", label="hbm3e copy (measured)", threads=0, buffer_bytes=1 << 31,
                              read_gbps=6545.9, write_gbps=6545.9, copy_gbps=6545.9)
     results = {}
-    opts = TuneOptions()  # the reference's acceptance: cv <= 5 %; a timed sample is 48 launches long, not one
+    opts = TuneOptions()  # the reference's acceptance: cv <= 5 %; a timed sample is 96 launches long, not one
     for bucket, lo, hi in T_BUCKETS[:2]:
-        op = CudaGemvTunable(be, synth.Q4_K, rows, cols, hi, bucket, copies=8, launches_per_run=48)
+        op = CudaGemvTunable(be, synth.Q4_K, rows, cols, hi, bucket, copies=8, launches_per_run=96)
         names = {c.get("variant") for c in op.candidates()}
         assert {capi.GEMV_EXACT8, capi.GEMV_WARP_F32, capi.GEMV_MMA_F16X2, capi.GEMV_MMA_I8X2} <= names and capi.GEMM_TCGEN05_F16 not in names
-        results[bucket] = tune(db, key, [op], opts)[0]
+        for _attempt in range(3):  # a neighbour on a shared host can make one run noisy: tune again rather than loosen the 5 %
+            results[bucket] = tune(db, key, [op], opts)[0]
+            if all(c.stability == "stable" for c in results[bucket].candidates if c.measured):
+                break
         assert results[bucket].winner is not None
         assert all(c.valid for c in results[bucket].candidates), "every registered decode variant must pass validation on Q4_K"
         # the bit-exact variant is never the fastest: a tuner that picked it would point at a timing bug
