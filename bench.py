@@ -6,7 +6,8 @@ Metric (one JSON line on stdout): weight GB/s of the decode-shaped Q4_K matmul 1
 the `prefill` object the TFLOP/s of the same weights at M = 2048.  A step is one pass of Backend::gemv over
 COPIES distinct copies of the weight matrix (COPIES x 50 MB, several times the 126 MB L2, so every launch
 streams its weights from HBM).  `value` times launches on inputs resident in HBM; `e2e` times the same pass
-through the backend's public call with host buffers (pinned upload of each x, download of each y).
+through the backend's public calls with host buffers (every step copies its x rows up from pinned memory and its y
+rows down; two steps are in flight on two streams, so the copies of one overlap the matmuls of the other).
 `--impl reference` times the reference's own CPU backend on the same workload with all host threads.
 Under torchrun each rank owns one GPU and an equal column shard of an N-times-wider projection (weak scaling,
 no collective on the data path: a column split needs none).
@@ -801,35 +802,76 @@ def run_ours(args) -> None:
         sampler.start()
     ms = timed(one_pass, args.steps)
 
-    # ---- e2e: the same pass through the public calls with host buffers: the step's COPIES x rows go up from pinned memory in
-    # one copy, every matmul reads its own row and writes its own y, the step's COPIES y rows come down in one copy, one wait
-    hx, hy = C.c_void_p(), C.c_void_p()
-    lib.halo_cuda_host_alloc(ctx, COPIES * K_COLS * 4, C.byref(hx))
-    lib.halo_cuda_host_alloc(ctx, COPIES * N_ROWS * 4, C.byref(hy))
-    for i in range(COPIES):
-        C.memmove(hx.value + i * K_COLS * 4, x.ctypes.data, K_COLS * 4)
-    x_all = be.allocate(COPIES * K_COLS * 4)
-    y_all = be.allocate(COPIES * N_ROWS * 4)
-    e2e_structs = [be._gemv_struct(hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef(x_all, i * K_COLS * 4, K_COLS * 4),
-                                               hb.TensorRef(y_all, i * N_ROWS * 4, N_ROWS * 4), N_ROWS, K_COLS, 1, args.variant), "MATMUL", False)
-                   for i in range(COPIES)]
+    # The same resident pass with its 16 independent matmuls issued alternately on two streams (informative, not the headline:
+    # in a decode chain every matmul waits for the one before it).  The two streams fill each other's launch turnaround.
+    two_stream = None
+    if not args.profile:
+        st2 = be.create_stream()
+        ev0, ev1, ev2 = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        for e in (ev0, ev1, ev2):
+            lib.halo_cuda_event_create(ctx, C.byref(e))
 
-    def e2e_pass():
-        lib.halo_cuda_memcpy_h2d_async(ctx, C.c_void_p(x_all.ptr), hx, COPIES * K_COLS * 4, st.handle)
-        for g in e2e_structs:
-            rc = lib.halo_cuda_gemv(ctx, C.byref(g), st.handle)
+        def two_pass():
+            for i, g in enumerate(structs):
+                rc = lib.halo_cuda_gemv(ctx, C.byref(g), (st2 if i & 1 else st).handle)
+                if rc != 0:
+                    raise hb.HaloError(rc, capi.last_error())
+
+        for _ in range(3):
+            two_pass()
+        st.wait()
+        st2.wait()
+        t0 = time.perf_counter()
+        reps2 = max(1, args.steps // 2)
+        for _ in range(reps2):
+            two_pass()
+        st.wait()
+        st2.wait()
+        us2 = (time.perf_counter() - t0) * 1e6 / (reps2 * COPIES)
+        two_stream = {"us_per_launch": us2, "frac_of_hbm": (wbytes + 4 * K_COLS + 4 * N_ROWS) / us2 / 1e3 / peaks()["hbm_gbs"],
+                      "timing": "wall clock around the launches of both streams and their waits"}
+
+    # ---- e2e: the same pass through the public calls with host buffers: the step's COPIES x rows go up from pinned memory in
+    # one copy, every matmul reads its own row and writes its own y, the step's COPIES y rows come down in one copy.  As a host
+    # that wants throughput would, two steps are in flight: steps alternate between two streams (each with its own pinned and
+    # device buffers), and the host waits for step i - 2 before it issues step i, so the copies of one step overlap the matmuls of
+    # the other.  Every step still copies its own inputs up and its own results down inside the timed region.
+    lanes = []
+    for _ in range(2):
+        hx, hy = C.c_void_p(), C.c_void_p()
+        lib.halo_cuda_host_alloc(ctx, COPIES * K_COLS * 4, C.byref(hx))
+        lib.halo_cuda_host_alloc(ctx, COPIES * N_ROWS * 4, C.byref(hy))
+        for i in range(COPIES):
+            C.memmove(hx.value + i * K_COLS * 4, x.ctypes.data, K_COLS * 4)
+        x_all = be.allocate(COPIES * K_COLS * 4)
+        y_all = be.allocate(COPIES * N_ROWS * 4)
+        stream = be.create_stream()
+        structs_l = [be._gemv_struct(hb.GemvArgs(synth.Q4_K, hb.TensorRef.of(wbufs[i]), hb.TensorRef(x_all, i * K_COLS * 4, K_COLS * 4),
+                                                 hb.TensorRef(y_all, i * N_ROWS * 4, N_ROWS * 4), N_ROWS, K_COLS, 1, args.variant), "MATMUL", False)
+                     for i in range(COPIES)]
+        lanes.append((stream, hx, hy, x_all, y_all, structs_l))
+
+    def e2e_step(lane):
+        stream, hx, hy, x_all, y_all, structs_l = lane
+        stream.wait()  # the step issued two steps ago on this stream: its results are in host memory now
+        lib.halo_cuda_memcpy_h2d_async(ctx, C.c_void_p(x_all.ptr), hx, COPIES * K_COLS * 4, stream.handle)
+        for g in structs_l:
+            rc = lib.halo_cuda_gemv(ctx, C.byref(g), stream.handle)
             if rc != 0:
                 raise hb.HaloError(rc, capi.last_error())
-        lib.halo_cuda_memcpy_d2h_async(ctx, hy, C.c_void_p(y_all.ptr), COPIES * N_ROWS * 4, st.handle)
-        st.wait()
+        lib.halo_cuda_memcpy_d2h_async(ctx, hy, C.c_void_p(y_all.ptr), COPIES * N_ROWS * 4, stream.handle)
 
-    for _ in range(0 if args.profile else 3):
-        e2e_pass()
+    def e2e_run(steps):
+        for i in range(steps):
+            e2e_step(lanes[i & 1])
+        for lane in lanes:
+            lane[0].wait()
+
+    e2e_run(0 if args.profile else 6)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(1 if args.profile else args.steps):
-        e2e_pass()
-    e2e_s = (time.perf_counter() - t0) * (args.steps if args.profile else 1)
+    e2e_run(2 if args.profile else args.steps)
+    e2e_s = (time.perf_counter() - t0) * (args.steps / 2 if args.profile else 1)
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -990,14 +1032,15 @@ def run_ours(args) -> None:
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"cfg0: Q4_K mul_mat N={N_ROWS} K={K_COLS} M=1 per GPU, {COPIES} distinct weight copies per step",
                    "variant": vname, "l2": f"inputs larger than L2: {COPIES} x {wbytes / 1e6:.1f} MB of weights cycled",
-                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err, "kernel_choice": kernel_choice, **summary},
+                   "parallelism": f"column split x{world}, no collective", "rel_err_vs_exact": rel_err, "kernel_choice": kernel_choice,
+                   "two_streams_resident": two_stream, **summary},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of one launch of this kernel on this shape",
                      "peak_source": pk["source"], "kernel": vname, "launch_us": launch_us,
                      "algorithmic_bytes_per_launch": algo_bytes},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COPIES * K_COLS * 4, "d2h_bytes_per_step": COPIES * N_ROWS * 4,
-                "ms_per_step": e2e_s / args.steps * 1e3},
+                "ms_per_step": e2e_s / args.steps * 1e3, "pipelining": "two steps in flight on two streams; every step copies its own x up and y down"},
         "gpu_launches": total_launches,
         "prefill": prefill,
         "prefill_repacked": prefill_r,
