@@ -120,6 +120,7 @@ SYMBOLS = {
     "halo_cuda_get_rows": (C.c_int, [_P, C.POINTER(GetRows), _P]),
     "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_repacked_row_bytes": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "halo_cuda_gemv_plan_i8": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvPlan)]),
     "halo_cuda_repacked_variant": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint32)]),
     "halo_cuda_repack_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P]),
     "halo_cuda_gemv_plan": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvPlan)]),

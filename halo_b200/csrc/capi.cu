@@ -102,6 +102,15 @@ uint32_t repacked_variant(uint32_t wtype, uint32_t cols) {
     return i8 ? HALO_CUDA_GEMV_MMA_I8X2_R : HALO_CUDA_GEMV_MMA_R;
 }
 
+uint32_t gemv_i8_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table) {
+    switch (wtype) {
+        case HALO_CUDA_T_Q6_K: return gemv_i8_q6kr_plan(rows, cols, sm_count, table);
+        case HALO_CUDA_T_Q8_0: return gemv_i8_q80r_plan(rows, cols, sm_count, table);
+        case HALO_CUDA_T_Q4_0: return gemv_i8_q40r_plan(rows, cols, sm_count, table);
+        default: return gemv_i8_q4k_plan(rows, cols, sm_count, table);
+    }
+}
+
 bool note_smem_raised(HaloCudaCtx* ctx, const void* kernel) { return ctx->smem_raised.insert(kernel).second; }
 
 int allow_dynamic_smem(HaloCudaCtx* ctx, const void* kernel, uint32_t bytes) {
@@ -756,6 +765,21 @@ int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t s
     mma::SkTable t{};
     std::memset(plan, 0, sizeof *plan);
     plan->slices = mma::plan_partition(rows, cols / 256u, sm_count, mma::format_allows_slices(wtype), &t);
+    plan->ctas = t.parts;
+    plan->cols_per_unit = t.cols_per_unit;
+    for (uint32_t c = 0; c <= t.parts; ++c) plan->start[c] = t.start[c];
+    return 0;
+}
+
+int halo_cuda_gemv_plan_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan) {
+    if (plan == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    if (wtype != HALO_CUDA_T_Q4_K && repacked_row_bytes(wtype, 256) == 0)
+        return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: no tensor-core skinny kernel for weight type id %u", wtype);
+    if (cols == 0 || cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "MATMUL: %u elements is not a multiple of 256", cols);
+    if (rows == 0 || sm_count == 0) return fail(HALO_CUDA_E_KERNEL, "MATMUL: empty matrix or device");
+    mma::SkTable t{};
+    std::memset(plan, 0, sizeof *plan);
+    plan->slices = gemv_i8_plan(wtype, rows, cols, sm_count, &t);
     plan->ctas = t.parts;
     plan->cols_per_unit = t.cols_per_unit;
     for (uint32_t c = 0; c <= t.parts; ++c) plan->start[c] = t.start[c];

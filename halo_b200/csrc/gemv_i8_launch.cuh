@@ -37,6 +37,12 @@ void plan(const HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry* g) {
     g->ks = plan_partition_i8(c.rows, g->nb, static_cast<uint32_t>(ctx->prop.multiProcessorCount), slices_fit<F>(g->nb), &g->table);
 }
 
+/// The same plan for inspection: slice count and table for a device with `sm_count` SMs.
+template <class F>
+uint32_t plan_for(uint32_t rows, uint32_t cols, uint32_t sm_count, SkTable* table) {
+    return plan_partition_i8(rows, cols / 256u, sm_count, slices_fit<F>(cols / 256u), table);
+}
+
 template <class F, int NTOK, int KSC, int NS = kRing>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;

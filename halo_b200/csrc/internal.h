@@ -143,6 +143,14 @@ bool gemv_i8_q6kr_supports(const GemvCall& c);
 bool gemv_i8_q80r_supports(const GemvCall& c);
 bool gemv_i8_q40r_supports(const GemvCall& c);
 bool gemv_i8_r_supports(const GemvCall& c);   // the three above by weight type
+namespace mma {
+struct SkTable;
+}
+uint32_t gemv_i8_q4k_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
+uint32_t gemv_i8_q6kr_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
+uint32_t gemv_i8_q80r_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
+uint32_t gemv_i8_q40r_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
+uint32_t gemv_i8_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);  // by weight type
 bool gemv_i8_q6kr_fits(uint32_t cols);
 bool gemv_i8_q80r_fits(uint32_t cols);
 bool gemv_i8_q40r_fits(uint32_t cols);

@@ -220,7 +220,7 @@ int halo_cuda_repacked_variant(uint32_t wtype, uint64_t cols, uint32_t* variant_
 int halo_cuda_repack_rows(HaloCudaCtx* ctx, uint32_t wtype, const void* src, uint64_t src_stride, void* dst, uint64_t dst_stride,
                           uint32_t rows, uint32_t cols, HaloCudaStream stream);
 
-/* ---- the partition of the balanced skinny kernels (variants 3 and 7), for inspection and tests ----------------------
+/* ---- the partition of the balanced skinny kernels, for inspection and tests (halo_cuda_gemv_plan: variants 3 and 7) ----------------------
  * Pure host arithmetic, no device needed: how a rows x cols matmul of `wtype` is cut over a GPU with `sm_count` SMs.
  * A CTA is (16 / slices) row blocks of 16 W rows x `slices` interleaved K slices; a unit is that many row blocks, a
  * column one step of 256 * slices elements of K; CTA c walks columns [start[c], start[c + 1]) of the unit-major
@@ -231,6 +231,11 @@ typedef struct HaloCudaGemvPlan {
     uint32_t start[HALO_CUDA_PLAN_MAX_CTAS + 1];
 } HaloCudaGemvPlan;
 int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan);
+/* The same for the int8 family (variants 8 and 9), whose CTAs cut K into 1, 2, 4, 8 or 16 slices: whole units per CTA with the
+ * fewest tiles per warp, ceil(units / CTAs) * ceil(cols / 256 / slices), or -- where every x record of a row does not fit in
+ * shared memory for a tile of eight rows, or where it walks fewer tiles even with the cross-CTA reduction -- the even split of
+ * the columns with one slice.  A function of (wtype, rows, cols, sm_count) alone. */
+int halo_cuda_gemv_plan_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan);
 
 /* ---- the operators ------------------------------------------------------------------------------ */
 int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);

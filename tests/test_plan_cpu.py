@@ -79,3 +79,66 @@ def test_plan_rejects_what_the_kernels_do_not_take():
     assert lib.halo_cuda_gemv_plan(synth.Q4_K, 16, 1000, 148, C.byref(p)) == capi.E_MODEL
     assert lib.halo_cuda_gemv_plan(0, 16, 1024, 148, C.byref(p)) == capi.E_UNSUPPORTED
     assert lib.halo_cuda_gemv_plan(synth.Q4_K, 0, 1024, 148, C.byref(p)) == capi.E_KERNEL
+
+
+# ---- the int8 family's planner (halo_cuda_gemv_plan_i8): 1, 2, 4, 8 or 16 in-CTA slices ------------------------------------------
+def plan_i8(wtype: int, rows: int, cols: int, sms: int = 148):
+    lib = capi.load()
+    p = capi.GemvPlan()
+    rc = lib.halo_cuda_gemv_plan_i8(wtype, rows, cols, sms, C.byref(p))
+    assert rc == 0, capi.last_error()
+    return p.slices, p.ctas, p.cols_per_unit, list(p.start[: p.ctas + 1])
+
+
+def check_i8(wtype: int, rows: int, cols: int, sms: int = 148):
+    ks, ctas, cpu, start = plan_i8(wtype, rows, cols, sms)
+    nb, n_rb, r_blocks = cols // 256, (rows + 15) // 16, 16 // ks
+    assert ks in (1, 2, 4, 8, 16) and 1 <= ctas <= min(sms, 160) and cpu == (nb + ks - 1) // ks
+    assert start[0] == 0 and all(a < b for a, b in zip(start, start[1:])), "ranges must be contiguous and non-empty"
+    units = (n_rb + r_blocks - 1) // r_blocks
+    assert start[-1] == units * cpu, "the ranges must cover every column of every unit"
+    if ks > 1:  # slices come with whole units per CTA: nothing crosses CTAs
+        assert all(s % cpu == 0 for s in start)
+    owned = 0
+    for c in range(ctas):
+        for col in range(start[c], start[c + 1]):
+            unit, k = divmod(col, cpu)
+            rbs = min(r_blocks, n_rb - unit * r_blocks)
+            sbs = sum(1 for s in range(ks) if k * ks + s < nb)
+            owned += max(rbs, 0) * sbs
+    assert owned == n_rb * nb, "every (row block, super-block) tile exactly once"
+    return ks, ctas
+
+
+def test_i8_plan_of_the_benchmark_shapes():
+    assert check_i8(synth.Q4_K, 17408, 5120) == (2, 136)      # the headline: 136 whole units of 8 row blocks x 2 slices
+    assert check_i8(synth.Q4_K, 5120, 5120) == (4, 80)        # attention q / o: 5 tiles per warp, no cross-CTA reduction
+    assert check_i8(synth.Q4_K, 2176, 5120) == (16, 136)      # a tensor-parallel share of gate / up: one row block per CTA
+    assert check_i8(synth.Q4_K, 48, 5120) == (16, 3)          # beta | alpha
+    assert check_i8(synth.Q6_K, 5120, 17408) == (1, 148)      # 68 super-blocks of x do not fit for eight rows: even split
+    assert check_i8(synth.Q8_0, 5120, 17408) == (1, 148)
+    assert check_i8(synth.Q4_0, 151936, 5120) == (1, 148)     # the head: the even split walks fewer tiles than any whole-unit plan
+    assert check_i8(synth.Q4_K, 5120, 256) == (1, 20)         # one super-block: nothing to slice
+
+
+def test_i8_plan_is_a_function_of_shape_type_and_sm_count_only():
+    a = plan_i8(synth.Q4_K, 4096, 4096)
+    assert a == plan_i8(synth.Q4_K, 4096, 4096)
+    # the type matters only through what fits in shared memory: Q8_0's 5 KB ring slots leave room for fewer records
+    assert plan_i8(synth.Q8_0, 5120, 5120)[0] == 1 and plan_i8(synth.Q4_0, 5120, 5120)[0] == 4
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_i8_plan_covers_random_shapes(seed):
+    rng = random.Random(100 + seed)
+    for _ in range(80):
+        wtype = rng.choice([synth.Q4_K, synth.Q6_K, synth.Q8_0, synth.Q4_0])
+        check_i8(wtype, rng.randint(1, 40000), 256 * rng.randint(1, 70), rng.choice([148, 132, 8, 1, 160, 400]))
+
+
+def test_i8_plan_rejects_what_the_kernels_do_not_take():
+    lib = capi.load()
+    p = capi.GemvPlan()
+    assert lib.halo_cuda_gemv_plan_i8(synth.Q4_K, 16, 1000, 148, C.byref(p)) == capi.E_MODEL
+    assert lib.halo_cuda_gemv_plan_i8(0, 16, 1024, 148, C.byref(p)) == capi.E_UNSUPPORTED
+    assert lib.halo_cuda_gemv_plan_i8(synth.Q4_K, 0, 1024, 148, C.byref(p)) == capi.E_KERNEL
