@@ -1,5 +1,6 @@
-// The int8 tensor-core skinny kernels (variant gemv_mma_i8x2): x travels as two signed 8-bit digits per element, the
-// 4-bit codes go into the MMA as unsigned bytes, and every sum up to the per-sub-block scale is an exact integer.
+// The int8 tensor-core skinny kernels (variants gemv_mma_i8x2 over raw Q4_K rows and gemv_mma_i8x2_r over repacked Q6_K / Q8_0 /
+// Q4_0 rows): x travels as two signed 8-bit digits per element, the quant codes go into the MMA as bytes, and every sum up to
+// the per-group scale is an exact integer.  The Q4_K arithmetic is spelled out here; the other formats say theirs at their structs.
 //
 // x is quantised per super-block (256 elements, what one warp converts at a time): s = the power of two that puts the
 // super-block's largest magnitude in (2^14, 32639], xq = rint(x * s) = 256 * hi + lo with hi, lo in [-128, 127].  The
@@ -15,7 +16,8 @@
 // x sits in the column pair (2p, 2p + 1) of B for the sub-blocks s = p (mod 4) (hi digit, lo digit; the other columns
 // read zeros), so one accumulator tile carries four sub-blocks and lane t of a row finishes P_t; two shuffles add them.
 //
-// The partition, the per-warp TMA weight ring, the K slices and the cross-CTA reduction are those of gemv_mma_sk.cuh.
+// The per-warp TMA weight ring and the cross-CTA reduction are those of gemv_mma_sk.cuh; the partition (1 to 16 in-CTA K slices,
+// a launch parameter) is plan_partition_i8 of mma_common.cuh.
 #pragma once
 #include <cuda.h>
 

@@ -43,10 +43,10 @@ uint32_t plan_for(uint32_t rows, uint32_t cols, uint32_t sm_count, SkTable* tabl
     return plan_partition_i8(rows, cols / 256u, sm_count, slices_fit<F>(cols / 256u), table);
 }
 
-template <class F, int NTOK, int KSC, int NS = kRing>
+template <class F, int NTOK, int KSC>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;
-    using L = Layout<F, NTOK, NS>;
+    using L = Layout<F, NTOK, kRing>;
     const uint32_t ks_shift = log2_of(g.ks), n_rec = sk::resident_records(g), smem_bytes = L::bytes(n_rec, ks_shift);
     if (smem_bytes > kSmemBudget) return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x records of %d rows do not fit in shared memory", n_rec, NTOK);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
@@ -67,7 +67,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     const cudaLaunchConfig_t cfg = sk::pdl_config(g.table.parts, smem_bytes, s, attr);
     if (c.norm_w != nullptr) {
         if constexpr (NTOK == 1) {
-            auto kern = gemv_i8_kernel<F, 1, NS, KSC, false, true>;
+            auto kern = gemv_i8_kernel<F, 1, kRing, KSC, false, true>;
             if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
             HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                        static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), c.norm_w, c.norm_eps));
@@ -76,7 +76,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
             return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
         }
     }
-    auto kern = gemv_i8_kernel<F, NTOK, NS, KSC, PRE, false>;
+    auto kern = gemv_i8_kernel<F, NTOK, kRing, KSC, PRE, false>;
     if (int rc = allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kern), kSmemBudget)) return rc;
     HC_CUDA(cudaLaunchKernelEx(&cfg, kern, wmap, g.table, x, c.x_stride, y, c.y_stride, c.rows, g.nb, n_rec, ks_shift, static_cast<float*>(g.partials),
                                static_cast<uint32_t*>(g.counters), ctx->error_word_dev, xstage, sk::peer_push(c, tok0), static_cast<const float*>(nullptr),
