@@ -49,12 +49,11 @@ __device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uin
 //                                                            32-element block keep a column PERMUTED: element e at byte
 //                                                            8 * ((e % 16) / 4) + 4 * (e / 16) + e % 4, so that a lane's two B
 //                                                            registers are one 8-byte load)
-//   meta    [row][112 B]                                     int32 pairs (X_p, X_{4+p}) for p = 0..3 (sums of xq over 32 elements),
-//                                                            1 / s as fp32 at byte 32, and at byte 48 the sixteen sums over 16
-//                                                            elements as [t][T] = group 4 T + t
+//   meta    [row][48 B]                                      int32 pairs (X_p, X_{4+p}) for p = 0..3 (sums of xq over 32 elements: what
+//                                                            Q4_K's mins multiply), 1 / s as fp32 at byte 32
 // The digit area and the meta area are separate arrays (all super-blocks of one, then all of the other), in shared
 // memory as in the scratch the pre-staging kernel fills.
-constexpr uint32_t kDigitBytes = 512, kMetaBytes = 112;
+constexpr uint32_t kDigitBytes = 512, kMetaBytes = 48;
 inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
 inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * rec_bytes(n_tok); }
 
@@ -107,7 +106,6 @@ __device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta,
     }
     uint8_t* mt = meta + uint64_t{sb} * (kMetaBytes * n_tok) + tok * kMetaBytes;
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    if ((lane & 1u) == 0) reinterpret_cast<int*>(mt + 48)[((lane >> 1) & 3u) * 4u + (lane >> 3)] = sum;  // 16 elements: group lane / 2
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     if ((lane & 3u) == 0) reinterpret_cast<int*>(mt)[(sub & 3u) * 2u + (sub >> 2)] = sum;
     if (lane == 0) reinterpret_cast<float*>(mt)[8] = bad ? __int_as_float(0x7FC00000) : __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
@@ -269,8 +267,10 @@ struct Q4Ki {
 
 // ---- repacked Q8_0 / Q4_0 rows (layouts: gemv_mma_grouped.cu): eight 32-element blocks per 256-weight group, an fp16 scale each --------
 // One MMA (k = 32) per block: a lane's weight word holds elements 4t .. 4t+3 (k-step 0) or 16+4t .. (k-step 1), the x digits are
-// kept in the same order (permuted columns).  Per block b:  A_b = S_b - zero * X_b  (int32, exact),  and per phase p = 0..3
-//     u_p = fma(d_{4+p}, float(A_{4+p}), d_p * float(A_p)),   P_p = fma(1 / s, u_p, P_p),   y = (P_0 + P_1) + (P_2 + P_3).
+// kept in the same order (permuted columns).  The A operand is the SIGNED weight times 2^kShift as an s8 (Q8_0: the int8 itself;
+// Q4_0: ((nibble ^ 8) << 4) = 16 (q - 8), one or two operations per word), so no zero point is left for the epilogue.  Per block b:
+// A_b = sum 2^kShift (q - zero) xq (int32, exact), and per phase p = 0..3
+//     u_p = fma(d_{4+p}, float(A_{4+p}), d_p * float(A_p)),   P_p = fma(2^-kShift / s, u_p, P_p),   y = (P_0 + P_1) + (P_2 + P_3).
 __device__ __forceinline__ void imma_ss(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
@@ -289,14 +289,11 @@ struct Blocks32 {
 
     template <bool FIRST>
     __device__ static __forceinline__ void mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-        if constexpr (T::kSigned) {
-            if constexpr (FIRST) imma0_ss(c, a0, a1, a2, a3, b0, b1);
-            else imma_ss(c, a0, a1, a2, a3, b0, b1);
-        } else {
-            if constexpr (FIRST) imma0(c, a0, a1, a2, a3, b0, b1);
-            else imma(c, a0, a1, a2, a3, b0, b1);
-        }
+        if constexpr (FIRST) imma0_ss(c, a0, a1, a2, a3, b0, b1);
+        else imma_ss(c, a0, a1, a2, a3, b0, b1);
     }
+    /// 1 / s of the x record times the factor the A operand carries (both powers of two: exact)
+    __device__ static __forceinline__ float unscale(float inv) { return T::kShift == 0 ? inv : __fmul_rn(inv, 1.0f / static_cast<float>(1 << T::kShift)); }
     /// fp16 number `idx` (compile time) of the eight in `d` as fp32
     __device__ static __forceinline__ float scale(const uint4& d, int idx) {
         const uint32_t w = (idx >> 1) == 0 ? d.x : (idx >> 1) == 1 ? d.y : (idx >> 1) == 2 ? d.z : d.w;
@@ -342,15 +339,13 @@ struct Blocks32 {
             if ((b & 3) == 0) mma<true>(c[b >> 2], a0, a1, a2, a3, bx.x, bx.y);
             else mma<false>(c[b >> 2], a0, a1, a2, a3, bx.x, bx.y);
         }
-        const uint8_t* mt = meta + rec * kMetaBytes;
-        const int2 X = *reinterpret_cast<const int2*>(mt + t * 8u);
-        const float inv = *reinterpret_cast<const float*>(mt + 32);
+        const float inv = unscale(*reinterpret_cast<const float*>(meta + rec * kMetaBytes + 32));
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             const uint4 d = rr ? d1 : d0;
             const uint32_t lo = prmt(d.x, d.y, o.sel), hi = prmt(d.z, d.w, o.sel);  // scales of blocks t and 4 + t in the low halves
             const float s0 = __low2float(*reinterpret_cast<const __half2*>(&lo)), s1 = __low2float(*reinterpret_cast<const __half2*>(&hi));
-            const int A0 = c[0][2 * rr] * 256 + c[0][2 * rr + 1] - T::kZero * X.x, A1 = c[1][2 * rr] * 256 + c[1][2 * rr + 1] - T::kZero * X.y;
+            const int A0 = c[0][2 * rr] * 256 + c[0][2 * rr + 1], A1 = c[1][2 * rr] * 256 + c[1][2 * rr + 1];
             const float u = __fmaf_rn(s1, __int2float_rn(A1), __fmul_rn(s0, __int2float_rn(A0)));
             P[rr] = __fmaf_rn(inv, u, P[rr]);
         }
@@ -375,9 +370,6 @@ struct Blocks32 {
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {  // phases p = 2 jj, 2 jj + 1: blocks p and p + 4
             float U[G][2][2];
-            int4 X[G];
-#pragma unroll
-            for (int gi = 0; gi < G; ++gi) X[gi] = *reinterpret_cast<const int4*>(meta + moff[gi] + jj * 16);  // (X_p, X_{4+p}, X_{p+1}, X_{5+p})
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -391,10 +383,9 @@ struct Blocks32 {
                         const uint2 bx = *reinterpret_cast<const uint2*>(dig + b * kSub + boff[gi]);
                         int c[4];
                         mma<true>(c, a0, a1, a2, a3, bx.x, bx.y);
-                        const int xs = e == 0 ? (half == 0 ? X[gi].x : X[gi].y) : (half == 0 ? X[gi].z : X[gi].w);
 #pragma unroll
                         for (int rr = 0; rr < 2; ++rr) {
-                            const float fa = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1] - T::kZero * xs), sc = scale(dd[rr], b);
+                            const float fa = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1]), sc = scale(dd[rr], b);
                             U[gi][rr][e] = half == 0 ? __fmul_rn(sc, fa) : __fmaf_rn(sc, fa, U[gi][rr][e]);
                         }
                     }
@@ -402,7 +393,7 @@ struct Blocks32 {
             }
 #pragma unroll
             for (int gi = 0; gi < G; ++gi) {
-                const float inv = *reinterpret_cast<const float*>(meta + moff[gi] + 32);
+                const float inv = unscale(*reinterpret_cast<const float*>(meta + moff[gi] + 32));
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     P[gi][rr][2 * jj] = __fmaf_rn(inv, U[gi][rr][0], P[gi][rr][2 * jj]);
@@ -415,8 +406,7 @@ struct Blocks32 {
 
 struct Q80i : Blocks32<Q80i> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 320, kItemCoord = 272 / 4, kBoxInner = 320 / 4, kMapElemBytes = 4;
-    static constexpr bool kSigned = true;
-    static constexpr int kZero = 0, kMaxTok = 8;
+    static constexpr int kShift = 0, kMaxTok = 8;  // the int8 quants are the operand
     struct Frag {
         uint4 q[4];  // chunk c: (block 2c, k-step 0), (block 2c, k-step 1), (block 2c + 1, k-step 0), (block 2c + 1, k-step 1)
     };
@@ -432,8 +422,7 @@ struct Q80i : Blocks32<Q80i> {
 
 struct Q40i : Blocks32<Q40i> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kPitch = 192, kItemCoord = 144 / 4, kBoxInner = 192 / 4, kMapElemBytes = 4;
-    static constexpr bool kSigned = false;
-    static constexpr int kZero = 8, kMaxTok = 16;
+    static constexpr int kShift = 4, kMaxTok = 16;  // the operand is 16 (q - 8)
     struct Frag {
         uint4 q[2];  // chunk c: the words of blocks 4c .. 4c + 3 (low nibbles: elements 4t .., high nibbles: elements 16 + 4t ..)
     };
@@ -444,18 +433,20 @@ struct Q40i : Blocks32<Q40i> {
     __device__ static __forceinline__ void regs(const Frag& f, int b, uint32_t& k0, uint32_t& k1) {
         const uint4 c = f.q[b >> 2];
         const uint32_t w = (b & 3) == 0 ? c.x : (b & 3) == 1 ? c.y : (b & 3) == 2 ? c.z : c.w;
-        k0 = w & 0x0F0F0F0Fu, k1 = (w >> 4) & 0x0F0F0F0Fu;
+        // ((nibble ^ 8) << 4) as a signed byte is 16 (nibble - 8): the zero point rides in the operand
+        k0 = ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u, k1 = (w & 0xF0F0F0F0u) ^ 0x80808080u;
     }
 };
 
 // ---- repacked Q6_K rows (224 B per super-block): sixteen 16-element groups with an int8 scale each, one fp16 d per super-block ------
-// The 6-bit codes enter as unsigned bytes, the zero point leaves through the group's sum of xq:  A_g = S_g - 32 * X_g  (|A_g| < 2^24,
-// exact as fp32).  Per phase p = 0..3 (group g = 4 T + p, T = 0..3 ascending):
-//     u_p = sc_p * A_p,  u_p = fma(sc_{4T+p}, A_{4T+p}, u_p)   (fp32; sc and A converted exactly),   P_p = fma(1 / s, d * u_p, P_p)
+// The 6-bit codes enter as SIGNED bytes 4 (code - 32) = ((code << 2) ^ 0x80), built in the four operations per word it takes to put
+// nibble and high bits together, so no zero point is left for the epilogue:  A_g = 4 sum (q - 32) xq  (int32, exact).  Per phase
+// p = 0..3 (group g = 4 T + p, T = 0..3 ascending):
+//     u_p = sc_p * A_p,  u_p = fma(sc_{4T+p}, A_{4T+p}, u_p)   (fp32; sc converted exactly),   P_p = fma(1 / (4 s), d * u_p, P_p)
 // A batch uses one m16n8k16 MMA per group.  A single row uses m16n8k32: a 32-element sub-block holds two groups, which land in
 // different column pairs because the B registers of the other half are masked to zero.
 __device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
@@ -482,11 +473,12 @@ struct Q6Ki {
         const uint4 c = f.ql[n];
         const uint32_t w0 = b ? c.z : c.x, w1 = b ? c.w : c.y;
         const uint32_t h0 = n ? f.qh.z : f.qh.x, h1 = n ? f.qh.w : f.qh.y;
-        // nibble | two high bits << 4: byte j of h holds the high bits of element j for all four quarters, two bits each
+        // 4 code = nibble << 2 | two high bits << 6 (byte j of h holds the high bits of element j for all four quarters, two bits
+        // each); flipping bit 7 makes the byte, read as signed, 4 (code - 32)
         auto code = [&](uint32_t w, uint32_t h) {
-            const uint32_t wn = nib ? w >> 4 : w;
-            const uint32_t hs = quarter == 0 ? h << 4 : quarter == 1 ? h << 2 : quarter == 2 ? h : h >> 2;
-            return (wn & 0x0F0F0F0Fu) | (hs & 0x30303030u);
+            const uint32_t wn = nib ? w >> 2 : w << 2;
+            const uint32_t hs = quarter == 0 ? h << 6 : quarter == 1 ? h << 4 : quarter == 2 ? h << 2 : h;
+            return (wn & 0x3C3C3C3Cu) | ((hs & 0xC0C0C0C0u) ^ 0x80808080u);
         };
         k0 = code(w0, h0), k1 = code(w1, h1);
     }
@@ -534,20 +526,17 @@ struct Q6Ki {
                 regs(f0, sub, a0, a2);
                 regs(f1, sub, a1, a3);
                 const uint2 v = *reinterpret_cast<const uint2*>(bq[e] + sub * 64);
-                if (e == 0) imma0(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
-                else imma(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
+                if (e == 0) imma0_ss(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
+                else imma_ss(c[T], a0, a1, a2, a3, v.x & o.m0, v.y & o.m1);
             }
         }
-        const uint8_t* mt = meta + rec * kMetaBytes;
-        const int4 X = *reinterpret_cast<const int4*>(mt + 48 + t * 16u);  // X of groups t, 4 + t, 8 + t, 12 + t
-        const float inv = *reinterpret_cast<const float*>(mt + 32);
+        const float inv = __fmul_rn(*reinterpret_cast<const float*>(meta + rec * kMetaBytes + 32), 0.25f);  // the operand carries a factor 4
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             float u = 0.0f;
 #pragma unroll
             for (int T = 0; T < 4; ++T) {
-                const int xs = T == 0 ? X.x : T == 1 ? X.y : T == 2 ? X.z : X.w;
-                const float a = __int2float_rn(c[T][2 * rr] * 256 + c[T][2 * rr + 1] - 32 * xs);
+                const float a = __int2float_rn(c[T][2 * rr] * 256 + c[T][2 * rr + 1]);
                 const float sc = __int2float_rn(static_cast<int>(prmt(word(sw[rr], T), 0u, o.sel)));
                 u = T == 0 ? __fmul_rn(sc, a) : __fmaf_rn(sc, a, u);
             }
@@ -589,10 +578,9 @@ struct Q6Ki {
                         const int p = 2 * e + lh;  // group 4 T + p
                         int c[4];
                         imma_k16(c, lh ? a2 : a0, lh ? a3 : a1, lh ? bx.y : bx.x);
-                        const int xs = *reinterpret_cast<const int*>(meta + moff[gi] + 48 + (p * 4 + T) * 4);
 #pragma unroll
                         for (int rr = 0; rr < 2; ++rr) {
-                            const float a = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1] - 32 * xs);
+                            const float a = __int2float_rn(c[2 * rr] * 256 + c[2 * rr + 1]);
                             const float sc = __int2float_rn(static_cast<int>(static_cast<int8_t>(word(sw[rr], T) >> (8 * p))));
                             U[gi][rr][p] = T == 0 ? __fmul_rn(sc, a) : __fmaf_rn(sc, a, U[gi][rr][p]);
                         }
@@ -602,7 +590,7 @@ struct Q6Ki {
         }
 #pragma unroll
         for (int gi = 0; gi < G; ++gi) {
-            const float inv = *reinterpret_cast<const float*>(meta + moff[gi] + 32);
+            const float inv = __fmul_rn(*reinterpret_cast<const float*>(meta + moff[gi] + 32), 0.25f);
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr)
 #pragma unroll

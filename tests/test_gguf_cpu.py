@@ -268,13 +268,25 @@ def test_share_extents_match_the_tensor_parallel_split():
     assert matrix_share(Q8_0, 50, 1536, capi.SPLIT_ROW, 0, 2, repack=True).variant_id == capi.GEMV_MMA_I8X2_R
     # K beyond what the int8 kernels keep resident: the fp16 family's repacked kernel, which streams x; both ranks of an uneven row
     # split decide from the larger share
-    assert matrix_share(Q8_0, 8, 32768, repack=True).variant_id == capi.GEMV_MMA_R
+    assert matrix_share(Q8_0, 8, 65536, repack=True).variant_id == capi.GEMV_MMA_R
     lib = capi.load()
     v = C.c_uint32()
-    assert lib.halo_cuda_repacked_variant(Q8_0, 24064, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_I8X2_R
-    assert lib.halo_cuda_repacked_variant(Q8_0, 24320, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_R
-    assert lib.halo_cuda_repacked_variant(Q6_K, 44288, C.byref(v)) == 0 and v.value == capi.GEMV_MMA_I8X2_R
-    pair = {matrix_share(Q6_K, 8, 44544 + 44288, capi.SPLIT_ROW, r, 2, repack=True).variant_id for r in (0, 1)}  # 174 + 173 super-blocks
+
+    def variant(t, k):
+        assert lib.halo_cuda_repacked_variant(t, k, C.byref(v)) == 0
+        return v.value
+
+    first_r = {}  # per type: the smallest K (a multiple of 256) that no longer fits
+    for t in (Q8_0, Q6_K, Q4_0):
+        k = 256
+        while variant(t, k) == capi.GEMV_MMA_I8X2_R:
+            k += 256
+        first_r[t] = k
+        assert all(variant(t, kk) == capi.GEMV_MMA_R for kk in (k, k + 256, 4 * k))  # monotone: once too long, always too long
+    assert first_r[Q8_0] < first_r[Q6_K] < first_r[Q4_0]  # 5 KB, 3.5 KB and 3 KB ring slots leave less, more, most room for x
+    assert first_r[Q8_0] > 17408  # every K of the benchmark shapes runs the int8 family
+    k_hi, k_lo = first_r[Q6_K], first_r[Q6_K] - 256  # an uneven split into (k_hi, k_lo): rank 1 alone would fit, rank 0 does not
+    pair = {matrix_share(Q6_K, 8, k_hi + k_lo, capi.SPLIT_ROW, r, 2, repack=True).variant_id for r in (0, 1)}
     assert pair == {capi.GEMV_MMA_R}
     assert lib.halo_cuda_repacked_variant(Q4_K, 5120, C.byref(v)) == capi.E_UNSUPPORTED
     for bad, status in (((Q5_K, 4, 256), capi.E_UNSUPPORTED), ((Q4_K, 4, 100), capi.E_MODEL)):
