@@ -642,7 +642,11 @@ __device__ __forceinline__ void finish_slices(float (&yacc)[G][2], uint32_t unit
 
 // KSC: the slice count where it is known at compile time (the two-slice partition of the large shapes, whose inner loop
 // is the one that runs at memory speed), 0: taken from ks_shift_arg.
-template <class F, int NTOK, int NS, int KSC, bool PRE, bool NORM = false>
+// XC > 0 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of XC; the records of
+// a stretch (KS super-blocks per column, all NTOK rows) sit in one half of a double buffer, the next stretch's are copied into
+// the other half meanwhile, and a block barrier ends every stretch.  Same tiles, same order, same arithmetic as the resident
+// form: the bits do not change; the weights are read once whatever the batch.
+template <class F, int NTOK, int NS, int KSC, bool PRE, bool NORM = false, int XC = 0>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ SkTable tb, const float* __restrict__ x, uint64_t x_stride,
                float* __restrict__ y, uint64_t y_stride, uint32_t rows, uint32_t nb, uint32_t n_rec, uint32_t ks_shift_arg, float* __restrict__ partials,
@@ -707,7 +711,16 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     bool lost = false;
     if constexpr (NTOK == 1)
         for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + off_zero)[i] = 0u;
-    if constexpr (PRE) {
+    constexpr uint32_t kXFull = kOffRed + 160u;  // two mbarriers of the streamed form (the warp-sum floats before them end at kOffRed + 128)
+    if constexpr (XC > 0) {
+        static_assert(PRE && NTOK >= 2 && kXFull + 16u <= kOffBars, "streamed x: pre-staged batches");
+        if (tid == 0) {
+            mbar_init(smem_base + kXFull, 1);
+            mbar_init(smem_base + kXFull + 8u, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    } else if constexpr (PRE) {
         const uint32_t xbar = smem_base + kOffXBar;
         if (tid == 0) {
             mbar_init(xbar, 1);
@@ -815,6 +828,80 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         }
         refill();
     };
+    auto finish_unit = [&](uint32_t unit) {  // the row block, or this CTA's share of it, is done
+        float yacc[G][2];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                if constexpr (NTOK == 1) {
+                    float v = P[gi][rr][0];
+                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));  // (P_0 + P_1), (P_2 + P_3)
+                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
+                    yacc[gi][rr] = v;
+                    P[gi][rr][0] = 0.0f;
+                } else {
+                    yacc[gi][rr] = __fadd_rn(__fadd_rn(P[gi][rr][0], P[gi][rr][1]), __fadd_rn(P[gi][rr][2], P[gi][rr][3]));
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
+                }
+            }
+        finish_slices<G, NTOK>(yacc, unit, r, ks, KS, R, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
+    };
+    if constexpr (XC > 0) {
+        constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
+        const uint32_t col_bytes = KS * (kD + kM), half_bytes = XC * col_bytes;  // a column: KS super-blocks of digits, then KS of meta
+        const uint32_t n_str = (c1 - c0 + XC - 1u) / XC;
+        const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
+        auto issue = [&](uint32_t j) {  // thread 0: the records of stretch j into half j & 1
+            const uint32_t bar = smem_base + kXFull + (j & 1u) * 8u, dst0 = smem_base + off_digits + (j & 1u) * half_bytes;
+            uint32_t total = 0;
+            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+                const uint32_t sb0 = (col % cpu) * KS;
+                total += (sb0 < nb ? min(KS, nb - sb0) : 0u) * (kD + kM);
+            }
+            mbar_expect_tx(bar, total);
+            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+                const uint32_t sb0 = (col % cpu) * KS, cnt = sb0 < nb ? min(KS, nb - sb0) : 0u;
+                if (cnt == 0) continue;
+                bulk_g2s(dst0 + i * col_bytes, xstage + uint64_t{sb0} * kD, cnt * kD, bar);
+                bulk_g2s(dst0 + i * col_bytes + KS * kD, gmeta + uint64_t{sb0} * kM, cnt * kM, bar);
+            }
+        };
+        if (tid == 0) {
+            issue(0);
+            if (n_str > 1) issue(1);
+        }
+        uint32_t unit = unit0, kk = c0 - unit0 * cpu;
+        for (uint32_t j = 0; j < n_str; ++j) {
+            if (!mbar_wait(smem_base + kXFull + (j & 1u) * 8u, (j >> 1) & 1u)) {
+                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                lost = true;
+            }
+            const uint8_t* half = digits + (j & 1u) * half_bytes;
+            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+                const bool row_ok = unit * R + r < n_rb;
+                if (row_ok && kk < kmax) {
+                    if (!lost && !mbar_wait(bars + slot * 8u, parity)) {
+                        if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                        lost = true;
+                    }
+                    const uint8_t* colp = half + i * col_bytes;
+                    F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, colp + ks * kD, colp + KS * kD + ks * kM, P, release);
+                }
+                if (kk + 1u == cpu || col + 1u == c1) {
+                    if (row_ok) finish_unit(unit);
+                    kk = 0, ++unit;
+                } else {
+                    ++kk;
+                }
+            }
+            __syncthreads();  // every warp is done with this half: refill it two stretches ahead
+            if (tid == 0 && j + 2u < n_str) issue(j + 2u);
+        }
+        if (lost) sk::linger_after_loss();
+        return;
+    }
     // A warp that lost a copy keeps walking (its sums are garbage, the error word says so): its siblings wait for it at the barriers.
     for (uint32_t unit = unit0, k_lo = c0 - unit0 * cpu; unit * cpu < c1; ++unit, k_lo = 0) {
         if (unit * R + r >= n_rb) break;
@@ -842,25 +929,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + rec * (kDigitBytes * NTOK), meta + rec * (kMetaBytes * NTOK), P, release);
             }
         }
-        // the row block, or this CTA's share of it, is done
-        float yacc[G][2];
-#pragma unroll
-        for (int gi = 0; gi < G; ++gi)
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-                if constexpr (NTOK == 1) {
-                    float v = P[gi][rr][0];
-                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));  // (P_0 + P_1), (P_2 + P_3)
-                    v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
-                    yacc[gi][rr] = v;
-                    P[gi][rr][0] = 0.0f;
-                } else {
-                    yacc[gi][rr] = __fadd_rn(__fadd_rn(P[gi][rr][0], P[gi][rr][1]), __fadd_rn(P[gi][rr][2], P[gi][rr][3]));
-#pragma unroll
-                    for (int p = 0; p < 4; ++p) P[gi][rr][p] = 0.0f;
-                }
-            }
-        finish_slices<G, NTOK>(yacc, unit, r, ks, KS, R, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
+        finish_unit(unit);
     }
     if (lost) sk::linger_after_loss();
 }

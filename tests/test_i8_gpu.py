@@ -46,10 +46,11 @@ def test_i8_within_rounded_operand_bound(hz, checker, n, k, m):
         assert not np.array_equal(bits(y), bits(hz.gemv(t, w, x, n, k, variant=capi.GEMV_MMA_F16X2)))
 
 
-@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 18), (640, 6144, 17), (2176, 5120, 33)])
+@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 18), (640, 6144, 17), (2176, 5120, 33), (17408, 5120, 17)])
 def test_i8_rows_do_not_depend_on_batch_size(hz, n, k, rows_of_x):
     # token tiles of up to sixteen rows (fewer where the x records of a tile would not fit), pre-staged records for batches,
-    # in-kernel conversion for one row
+    # in-kernel conversion for one row; the last shape walks ten columns per CTA, so its batches of nine rows and up stream x
+    # through the double buffer while the smaller ones keep it resident
     t = synth.Q4_K
     w = synth.quant_weights(t, n, k, 3, 1)
     x = synth.activations(rows_of_x, k, 3, 2)
@@ -71,7 +72,7 @@ CASES = [
     (9, 5120, 16, "fewer rows than a tile: 20 CTAs share one row block"),
     (40000, 256, 3, "one column per unit, several units per CTA"),
     (5120, 6144, 17, "two token tiles (16 + 1)"),
-    (17408, 5120, 16, "all twenty super-blocks resident: two tiles of eight"),
+    (17408, 5120, 16, "twenty super-blocks of sixteen rows do not fit: x is streamed, one tile"),
     (300, 17408, 8, "68 columns per unit: a CTA keeps only the records of its own columns"),
     (18992, 5120, 16, "vocabulary shard of the head"),
 ]

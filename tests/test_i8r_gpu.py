@@ -73,7 +73,7 @@ def test_i8r_within_rounded_operand_bound(be, checker, t, n, k, m):
 
 
 @pytest.mark.parametrize("t", TYPES)
-@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 18), (640, 6144, 17), (2176, 5120, 33)])
+@pytest.mark.parametrize("n,k,rows_of_x", [(96, 2560, 20), (48, 17408, 18), (640, 6144, 17), (2176, 5120, 33), (17408, 5120, 17)])
 def test_i8r_rows_do_not_depend_on_batch_size(be, t, n, k, rows_of_x):
     w = synth.quant_weights(t, n, k, 3, 1)
     x = synth.activations(rows_of_x, k, 3, 2)
