@@ -721,36 +721,66 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         }
         __syncthreads();
     } else if constexpr (PRE) {
-        const uint32_t xbar = smem_base + kOffXBar;
-        if (tid == 0) {
-            mbar_init(xbar, 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            // the records of this CTA's super-blocks: all of them, or the cyclic run of its columns (at most two contiguous pieces)
-            const uint32_t xc0 = tb.start[cta], xn = tb.start[cta + 1] - xc0;
-            const bool xpart = KS == 1 && n_rec < nb;
-            const uint32_t first = xpart ? xc0 % cpu : 0u, count = xpart ? xn : nb;
-            const uint32_t n1 = min(count, nb - first), n2 = count - n1;  // super-blocks [first, first + n1) then [0, n2)
-            constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
-            mbar_expect_tx(xbar, count * (kD + kM));
-            const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
-            const uint32_t smeta = smem_base + off_digits + n_rec * kD;
-            auto copy = [&](uint32_t dst, const uint8_t* src, uint32_t bytes) {
-                for (uint32_t off = 0; off < bytes; off += 32768u) bulk_g2s(dst + off, src + off, min(32768u, bytes - off), xbar);
-            };
-            copy(smem_base + off_digits, xstage + uint64_t{first} * kD, n1 * kD);
-            copy(smeta, gmeta + uint64_t{first} * kM, n1 * kM);
-            if (n2 != 0) {
-                copy(smem_base + off_digits + n1 * kD, xstage, n2 * kD);
-                copy(smeta + n1 * kM, gmeta, n2 * kM);
+        static_assert(!NORM, "the fused input norm takes one x row");
+        if (xstage != nullptr) {  // the records were written by the conversion kernel before this launch: copy this CTA's in
+            const uint32_t xbar = smem_base + kOffXBar;
+            if (tid == 0) {
+                mbar_init(xbar, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                // the records of this CTA's super-blocks: all of them, or the cyclic run of its columns (at most two contiguous pieces)
+                const uint32_t xc0 = tb.start[cta], xn = tb.start[cta + 1] - xc0;
+                const bool xpart = KS == 1 && n_rec < nb;
+                const uint32_t first = xpart ? xc0 % cpu : 0u, count = xpart ? xn : nb;
+                const uint32_t n1 = min(count, nb - first), n2 = count - n1;  // super-blocks [first, first + n1) then [0, n2)
+                constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
+                mbar_expect_tx(xbar, count * (kD + kM));
+                const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
+                const uint32_t smeta = smem_base + off_digits + n_rec * kD;
+                auto copy = [&](uint32_t dst, const uint8_t* src, uint32_t bytes) {
+                    for (uint32_t off = 0; off < bytes; off += 32768u) bulk_g2s(dst + off, src + off, min(32768u, bytes - off), xbar);
+                };
+                copy(smem_base + off_digits, xstage + uint64_t{first} * kD, n1 * kD);
+                copy(smeta, gmeta + uint64_t{first} * kM, n1 * kM);
+                if (n2 != 0) {
+                    copy(smem_base + off_digits + n1 * kD, xstage, n2 * kD);
+                    copy(smeta + n1 * kM, gmeta, n2 * kM);
+                }
             }
-        }
-        __syncthreads();
-        if (!mbar_wait(xbar, 0)) {
-            if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
-            lost = true;
+            __syncthreads();
+            if (!mbar_wait(xbar, 0)) {
+                if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                lost = true;
+            }
+        } else {
+            // No conversion launch (the host leaves it out where a CTA has few records to make): the rows are converted here, a
+            // (record, row) pair per warp at a time, record-major, the loads of kAhead pairs in flight together.  Under a partial
+            // residency these are the super-blocks of the CTA's own columns only; under in-CTA slices every CTA converts all of x.
+            const uint32_t x_c0 = tb.start[cta], x_cols = tb.start[cta + 1] - x_c0;
+            const bool part = KS == 1 && n_rec < nb;
+            const uint32_t x_first = part ? x_c0 % cpu : 0u, n_items = (part ? x_cols : nb) * NTOK;
+            constexpr uint32_t kAhead = 4;  // (eight measured the same or slower)
+            for (uint32_t i0 = warp; i0 < n_items; i0 += kAhead * kSkWarps) {
+                float4 v[kAhead][2];
+#pragma unroll
+                for (uint32_t u = 0; u < kAhead; ++u) {
+                    const uint32_t i = i0 + u * kSkWarps;
+                    if (i < n_items) {
+                        const uint32_t j = i / NTOK, tok = i - j * NTOK;
+                        const uint32_t sb = x_first + j >= nb ? x_first + j - nb : x_first + j;  // (a one-slice partition has cpu == nb)
+                        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tok} * x_stride);
+                        v[u][0] = xr[sb * 64u + 2u * lane], v[u][1] = xr[sb * 64u + 2u * lane + 1u];
+                    }
+                }
+#pragma unroll
+                for (uint32_t u = 0; u < kAhead; ++u) {
+                    const uint32_t i = i0 + u * kSkWarps;
+                    if (i < n_items) stage_superblock(digits, meta, v[u][0], v[u][1], i / NTOK, NTOK, i % NTOK, lane, F::kPermX);
+                }
+            }
+            __syncthreads();
         }
     } else {
-        static_assert(NTOK == 1, "batches arrive pre-staged");
+        static_assert(NTOK == 1, "batches arrive through the branch above");
         // The row is converted in the kernel, one super-block per warp and round.  The first round (super-blocks 0 .. 15) is
         // what every warp's first tiles need: the block waits for it; the later rounds (their loads already in flight) finish
         // behind an mbarrier that only the tiles of super-block 16 and up wait for.

@@ -52,6 +52,15 @@ uint32_t plan_for(uint32_t rows, uint32_t cols, uint32_t sm_count, SkTable* tabl
     return plan_partition_i8(rows, cols / 256u, sm_count, slices_fit<F>(cols / 256u), table);
 }
 
+/// Whether a resident launch of n_tok (>= 2) x rows converts them itself instead of reading the records a conversion launch wrote.
+/// The conversion launch costs a dependent launch on the chain (about 3 us); converting in the kernel costs every CTA its
+/// n_rec * n_tok (record, row) pairs before its first tile.  Measured break-even: near 96 pairs where the CTAs read different
+/// columns of x (partial residency: 5120 x 17408 at 8 rows is 80 pairs, 24.5 us against 26.4), near 48 where all of them read
+/// all of x (K = 5120 at 2 rows is 40 pairs, 12.3 us against 13.4; at 4 rows the two forms tie, at 8 the launch wins by 3 us).
+inline bool converts_in_kernel(const sk::Geometry& g, uint32_t n_rec, uint32_t n_tok) {
+    return n_rec * n_tok <= (n_rec < g.nb ? 96u : 48u);
+}
+
 template <class F, int NTOK, int KSC, int XC = 0>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;
@@ -64,7 +73,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     CUtensorMap wmap;
     if (int rc = sk::weight_map<F>(c, &wmap)) return rc;
     const uint8_t* xstage = nullptr;
-    if constexpr (PRE) {
+    if (PRE && (XC > 0 || !converts_in_kernel(g, n_rec, NTOK))) {
         void* ws = nullptr;
         if (int rc = workspace(ctx, 0, stage_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
         cudaLaunchAttribute sattr[1];
