@@ -19,7 +19,8 @@ uint32_t smem_bytes(uint32_t n_tok, uint32_t n_rec, uint32_t ks_shift) {
 }
 
 constexpr int kStretch = 2;     // columns of x per half of the streamed form's double buffer
-constexpr int kStreamFrom = 9;  // the streamed form is compiled for tiles of 9 rows and up (smaller tiles' records fit resident)
+constexpr int kStreamFrom = 2;  // the streamed form takes any batch: a long K under a partition that keeps many records per CTA (a large N under
+                                // the even split, a long K under slices) leaves the resident form room for one or two rows only
 
 /// Shared memory of the streamed form: the double buffer of x records in place of the resident ones.
 template <class F>

@@ -133,6 +133,26 @@ def run_exact(be, t, raw, x, n, k):
     return y
 
 
+def test_i8r_small_batches_stream_x_where_a_cta_keeps_many_records(be):
+    """10240 x 17408 under the even split leaves a CTA nineteen columns: the records of eight rows do not fit beside the Q8_0 ring, and
+    the resident form would cut the batch into tiles that each read all weights.  The batch streams x instead (one pass); its rows
+    equal the single-row calls (resident form, checked against the bound above) bit for bit, and the exact kernel within the family's
+    tolerance."""
+    t, n, k, m = synth.Q8_0, 10240, 17408, 8
+    w = synth.quant_weights(t, n, k, 9, 1)
+    x = synth.activations(m, k, 9, 2)
+    y = run(be, t, w, x, n, k)
+    raw = be.import_host_readonly(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
+    ref = run_exact(be, t, raw, x, n, k)
+    raw.free()
+    assert np.max(np.abs(y - ref)) <= FAMILY_REL * np.max(np.abs(ref))
+    for r in (0, 3, 7):
+        y1 = run(be, t, w, x[r:r + 1], n, k)
+        assert np.array_equal(bits(y1[0]), bits(y[r])), f"row {r}"
+    y5 = run(be, t, w, x[:5], n, k)
+    assert np.array_equal(bits(y5), bits(y[:5]))
+
+
 @pytest.mark.parametrize("t", TYPES)
 def test_i8r_strided_operands(be, t):
     n, k, m = 77, 1024, 3
