@@ -126,9 +126,12 @@ static __global__ void __launch_bounds__(512) stage_x_i8_kernel(const float* __r
 
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows (the extra 16 bytes keep the fragment reads conflict-free)
 struct Q4Ki {
+    // (144-byte slot rows with permuted tile rows, as the repacked formats below have them, measured the same for one x row and 2 - 4 %
+    // slower for batches)
     static constexpr uint32_t kType = HALO_CUDA_T_Q4_K, kPitch = 160, kItemCoord = 144, kBoxInner = 160, kMapElemBytes = 1;
     static constexpr bool kPermX = false;
     static constexpr int kMaxTok = 16;  // x rows per launch (four MMA column groups); larger batches, or records that do not fit, run in tiles
+    static constexpr uint32_t kStretchMax = 8;  // columns per stretch of streamed x
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
     /// Lane constants of the single-row form.
@@ -285,7 +288,10 @@ __device__ __forceinline__ void imma0_ss(int (&c)[4], uint32_t a0, uint32_t a1, 
 template <class T>
 struct Blocks32 {
     static constexpr bool kPermX = true;
-    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
+    /// Slot rows are exactly one item wide (144 or 272 bytes: 16 mod 128), so the copy engine fetches no padding.  A quarter warp's
+    /// 16-byte fragment loads cover fragment rows g and g + 1: they take slot rows four apart (64 bytes mod 128), which keeps the
+    /// two 64-byte windows on different banks: fragment rows 0..7 read slot rows 0,4,1,5,2,6,3,7.
+    __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return (g >> 1) + 4u * (g & 1u); }
 
     template <bool FIRST>
     __device__ static __forceinline__ void mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -405,8 +411,9 @@ struct Blocks32 {
 };
 
 struct Q80i : Blocks32<Q80i> {
-    static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 320, kItemCoord = 272 / 4, kBoxInner = 320 / 4, kMapElemBytes = 4;
+    static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 272, kItemCoord = 272 / 4, kBoxInner = 272 / 4, kMapElemBytes = 4;
     static constexpr int kShift = 0, kMaxTok = 8;  // the int8 quants are the operand
+    static constexpr uint32_t kStretchMax = 3;
     struct Frag {
         uint4 q[4];  // chunk c: (block 2c, k-step 0), (block 2c, k-step 1), (block 2c + 1, k-step 0), (block 2c + 1, k-step 1)
     };
@@ -421,8 +428,9 @@ struct Q80i : Blocks32<Q80i> {
 };
 
 struct Q40i : Blocks32<Q40i> {
-    static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kPitch = 192, kItemCoord = 144 / 4, kBoxInner = 192 / 4, kMapElemBytes = 4;
+    static constexpr uint32_t kType = HALO_CUDA_T_Q4_0, kPitch = 144, kItemCoord = 144 / 4, kBoxInner = 144 / 4, kMapElemBytes = 4;
     static constexpr int kShift = 4, kMaxTok = 16;  // the operand is 16 (q - 8)
+    static constexpr uint32_t kStretchMax = 8;
     struct Frag {
         uint4 q[2];  // chunk c: the words of blocks 4c .. 4c + 3 (low nibbles: elements 4t .., high nibbles: elements 16 + 4t ..)
     };
@@ -455,6 +463,7 @@ struct Q6Ki {
     static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kPitch = 224, kItemCoord = 224 / 4, kBoxInner = 224 / 4, kMapElemBytes = 4;
     static constexpr bool kPermX = true;
     static constexpr int kMaxTok = 8;
+    static constexpr uint32_t kStretchMax = 8;
     /// 224-byte slot rows put rows g and g + 1 on overlapping banks: fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return ((2u * g) & 7u) | (g >> 2); }
 
@@ -642,7 +651,8 @@ __device__ __forceinline__ void finish_slices(float (&yacc)[G][2], uint32_t unit
 
 // KSC: the slice count where it is known at compile time (the two-slice partition of the large shapes, whose inner loop
 // is the one that runs at memory speed), 0: taken from ks_shift_arg.
-// XC > 0 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of XC; the records of
+// XC > 0 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of n_rec columns (as many
+// as fit: fewer block barriers, more room for the warps to run ahead of one another); the records of
 // a stretch (KS super-blocks per column, all NTOK rows) sit in one half of a double buffer, the next stretch's are copied into
 // the other half meanwhile, and a block barrier ends every stretch.  Same tiles, same order, same arithmetic as the resident
 // form: the bits do not change; the weights are read once whatever the batch.
@@ -880,18 +890,19 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     };
     if constexpr (XC > 0) {
         constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
-        const uint32_t col_bytes = KS * (kD + kM), half_bytes = XC * col_bytes;  // a column: KS super-blocks of digits, then KS of meta
-        const uint32_t n_str = (c1 - c0 + XC - 1u) / XC;
+        const uint32_t xc = n_rec;  // (streamed form: the parameter carries the columns per stretch)
+        const uint32_t col_bytes = KS * (kD + kM), half_bytes = xc * col_bytes;  // a column: KS super-blocks of digits, then KS of meta
+        const uint32_t n_str = (c1 - c0 + xc - 1u) / xc;
         const uint8_t* gmeta = xstage + uint64_t{nb} * kD;
         auto issue = [&](uint32_t j) {  // thread 0: the records of stretch j into half j & 1
             const uint32_t bar = smem_base + kXFull + (j & 1u) * 8u, dst0 = smem_base + off_digits + (j & 1u) * half_bytes;
             uint32_t total = 0;
-            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+            for (uint32_t i = 0, col = c0 + j * xc; i < xc && col < c1; ++i, ++col) {
                 const uint32_t sb0 = (col % cpu) * KS;
                 total += (sb0 < nb ? min(KS, nb - sb0) : 0u) * (kD + kM);
             }
             mbar_expect_tx(bar, total);
-            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+            for (uint32_t i = 0, col = c0 + j * xc; i < xc && col < c1; ++i, ++col) {
                 const uint32_t sb0 = (col % cpu) * KS, cnt = sb0 < nb ? min(KS, nb - sb0) : 0u;
                 if (cnt == 0) continue;
                 bulk_g2s(dst0 + i * col_bytes, xstage + uint64_t{sb0} * kD, cnt * kD, bar);
@@ -909,7 +920,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 lost = true;
             }
             const uint8_t* half = digits + (j & 1u) * half_bytes;
-            for (uint32_t i = 0, col = c0 + j * XC; i < XC && col < c1; ++i, ++col) {
+            for (uint32_t i = 0, col = c0 + j * xc; i < xc && col < c1; ++i, ++col) {
                 const bool row_ok = unit * R + r < n_rb;
                 if (row_ok && kk < kmax) {
                     if (!lost && !mbar_wait(bars + slot * 8u, parity)) {

@@ -18,14 +18,23 @@ uint32_t smem_bytes(uint32_t n_tok, uint32_t n_rec, uint32_t ks_shift) {
     return ((off_slices + red + 127u) & ~127u) + (n_tok == 1 ? 576u : 0u) + n_rec * rec_bytes(n_tok);
 }
 
-constexpr int kStretch = 2;     // columns of x per half of the streamed form's double buffer
 constexpr int kStreamFrom = 2;  // the streamed form takes any batch: a long K under a partition that keeps many records per CTA (a large N under
                                 // the even split, a long K under slices) leaves the resident form room for one or two rows only
 
-/// Shared memory of the streamed form: the double buffer of x records in place of the resident ones.
+/// Shared memory of the streamed form: the double buffer of x records (two halves of `stretch` columns) in place of the resident ones.
 template <class F>
-uint32_t smem_bytes_streamed(uint32_t n_tok, uint32_t ks_shift) {
-    return smem_bytes<F>(n_tok, 0, ks_shift) + 2u * kStretch * (1u << ks_shift) * rec_bytes(n_tok);
+uint32_t smem_bytes_streamed(uint32_t n_tok, uint32_t ks_shift, uint32_t stretch = 2) {
+    return smem_bytes<F>(n_tok, 0, ks_shift) + 2u * stretch * (1u << ks_shift) * rec_bytes(n_tok);
+}
+
+/// Columns per stretch of a streamed launch: the most that fit, from two (which always do where the form is chosen) to the format's
+/// kStretchMax.  Longer stretches mean fewer block barriers: 128256 x 8192 Q4_K at 8 rows 174 -> 161 us, 32768 x 28672 Q4_0 144 -> 129;
+/// Q8_0, whose streamed launches already run near the HBM rate, measured 3 - 5 % slower beyond three columns.
+template <class F>
+uint32_t stretch_columns(uint32_t n_tok, uint32_t ks_shift) {
+    uint32_t xc = 2;
+    while (xc < F::kStretchMax && smem_bytes_streamed<F>(n_tok, ks_shift, xc + 1) <= kSmemBudget) ++xc;
+    return xc;
 }
 
 inline uint32_t log2_of(uint32_t ks) {
@@ -66,8 +75,9 @@ template <class F, int NTOK, int KSC, int XC = 0>
 int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint32_t tok0, cudaStream_t s) {
     constexpr bool PRE = NTOK >= 2;
     using L = Layout<F, NTOK, kRing>;
-    const uint32_t ks_shift = log2_of(g.ks), n_rec = XC > 0 ? 0u : sk::resident_records(g);
-    const uint32_t smem_bytes = XC > 0 ? smem_bytes_streamed<F>(NTOK, ks_shift) : L::bytes(n_rec, ks_shift);
+    // n_rec: the resident records, or (streamed form) the columns per stretch
+    const uint32_t ks_shift = log2_of(g.ks), n_rec = XC > 0 ? stretch_columns<F>(NTOK, ks_shift) : sk::resident_records(g);
+    const uint32_t smem_bytes = XC > 0 ? smem_bytes_streamed<F>(NTOK, ks_shift, n_rec) : L::bytes(n_rec, ks_shift);
     if (smem_bytes > kSmemBudget) return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x records of %d rows do not fit in shared memory", n_rec, NTOK);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
@@ -119,8 +129,8 @@ int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry& g, uint32_t
         if constexpr (NTOK >= kStreamFrom) {
             if (streamed) {
                 if (c.norm_w != nullptr) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
-                if (g.ks == 2) return launch_tile<F, NTOK, 2, kStretch>(ctx, c, g, tok0, s);
-                return launch_tile<F, NTOK, 0, kStretch>(ctx, c, g, tok0, s);
+                if (g.ks == 2) return launch_tile<F, NTOK, 2, 1>(ctx, c, g, tok0, s);
+                return launch_tile<F, NTOK, 0, 1>(ctx, c, g, tok0, s);
             }
         }
         if (g.ks == 2) return launch_tile<F, NTOK, 2>(ctx, c, g, tok0, s);  // the partition of the large shapes: slice count folded into the code

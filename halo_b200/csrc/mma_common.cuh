@@ -216,6 +216,9 @@ inline uint32_t plan_partition(uint32_t rows, uint32_t nb, uint32_t sms, bool al
 /// The partition of the int8 kernels, whose CTAs cut K into 1, 2, 4, 8 or 16 in-CTA slices (R = 16 / KS row blocks per unit).
 /// With whole units per CTA nothing crosses CTAs, and a launch lasts about as long as the tiles one warp walks:
 /// ceil(units / CTAs) * ceil(nb / KS).  The fewest tiles win, ties go to fewer slices (more rows per CTA share an x record).
+/// Every unit of a sliced partition ends with the slices' sums meeting in shared memory (KS - 1 records added behind two named
+/// barriers), charged KS / 16 of a tile: with one or two tiles per unit that is what a launch spends its time on (128256 x 4096
+/// under sixteen slices, 55 tiles and 55 such meetings per warp, ran at 0.60 of the HBM rate; under two slices 56 tiles run at 0.9).
 /// Slices need every x record of a row resident in shared memory (`slices_ok`: they fit for a tile of eight x rows); without
 /// them, and where it walks fewer tiles even with the cross-CTA reduction (about `kReducePenalty` tiles' time), the even
 /// split of plan_partition's candidate B.  Returns KS; a function of (rows, cols, SM count) alone.
@@ -225,12 +228,13 @@ inline uint32_t plan_partition_i8(uint32_t rows, uint32_t nb, uint32_t sms, bool
     sms = std::min(sms, kSkMaxCtas);
     SkTable& t = *table;
     const uint64_t units_b = (n_rb + 15) / 16, cols_b = units_b * nb, parts_b = std::max<uint64_t>(1, std::min<uint64_t>(sms, cols_b));
-    uint64_t best = (cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : kReducePenalty);
+    // costs in sixteenths of a tile
+    uint64_t best = 16 * ((cols_b + parts_b - 1) / parts_b + (parts_b == units_b ? 0 : kReducePenalty));
     uint32_t best_ks = 1;
     if (slices_ok) {
         for (uint32_t ks = 2; ks <= kSkWarps && ks / 2 < std::max(nb, 1u); ks *= 2) {  // no more slices than the next power of two above nb
             const uint64_t units = (n_rb + kSkWarps / ks - 1) / (kSkWarps / ks), parts = std::max<uint64_t>(1, std::min<uint64_t>(sms, units));
-            const uint64_t tiles = (units + parts - 1) / parts * ((nb + ks - 1) / ks);
+            const uint64_t tiles = (units + parts - 1) / parts * (16 * ((nb + ks - 1) / ks) + ks);
             if (tiles < best) best = tiles, best_ks = ks;
         }
     }

@@ -119,6 +119,9 @@ def test_i8_plan_of_the_benchmark_shapes():
     assert check_i8(synth.Q8_0, 5120, 17408) == (1, 148)
     assert check_i8(synth.Q4_0, 151936, 5120) == (1, 148)     # the head: the even split walks fewer tiles than any whole-unit plan
     assert check_i8(synth.Q4_K, 5120, 256) == (1, 20)         # one super-block: nothing to slice
+    # a vocabulary-sized N with a short K: sixteen slices walk one tile fewer than two, but end every tile with the slices' meeting
+    assert check_i8(synth.Q4_K, 128256, 4096)[0] == 2
+    assert check_i8(synth.Q4_K, 32768, 2048)[0] == 2
 
 
 def test_i8_plan_is_a_function_of_shape_type_and_sm_count_only():
