@@ -54,7 +54,7 @@ __device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uin
 // The digit area and the meta area are separate arrays (all super-blocks of one, then all of the other), in shared
 // memory as in the scratch the pre-staging kernel fills.
 constexpr uint32_t kDigitBytes = 512, kMetaBytes = 48;
-inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
+__host__ __device__ inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
 inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * rec_bytes(n_tok); }
 
 /// One super-block (index sb) of x row `tok` into the records at `digits` / `meta`, by one warp: lane l holds elements
@@ -111,17 +111,20 @@ __device__ __forceinline__ void stage_superblock(uint8_t* digits, uint8_t* meta,
     if (lane == 0) reinterpret_cast<float*>(mt)[8] = bad ? __int_as_float(0x7FC00000) : __uint_as_float(static_cast<uint32_t>(127 - se) << 23);
 }
 
-/// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block of one row into the scratch records.
+/// grid (x rows, blocks of 16 super-blocks): every warp converts one super-block of one row into the scratch records.  The `total`
+/// rows are those of consecutive token tiles of `tile_rows` rows (the last one may be shorter); tile i's records start at
+/// scratch + i * nb * rec_bytes(tile_rows) and are laid out for that tile's own row count.
 static __global__ void __launch_bounds__(512) stage_x_i8_kernel(const float* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ scratch, uint32_t nb,
-                                                                uint32_t n_tok, uint32_t perm) {
+                                                                uint32_t tile_rows, uint32_t total, uint32_t perm) {
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t tk = blockIdx.x, sb = blockIdx.y * 16u + (threadIdx.x >> 5);
+    const uint32_t row = blockIdx.x, sb = blockIdx.y * 16u + (threadIdx.x >> 5);
     if (sb >= nb) return;
-    const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tk} * x_stride);
+    const uint32_t tile = row / tile_rows, tok = row - tile * tile_rows, n_tok = min(tile_rows, total - tile * tile_rows);
+    uint8_t* region = scratch + uint64_t{tile} * nb * rec_bytes(tile_rows);
+    const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{row} * x_stride);
     const uint32_t lane = threadIdx.x & 31u;
-    stage_superblock(scratch, scratch + uint64_t{nb} * kDigitBytes * n_tok, xr[sb * 64u + 2u * lane], xr[sb * 64u + 2u * lane + 1u], sb, n_tok, tk, lane,
-                     perm != 0);
+    stage_superblock(region, region + uint64_t{nb} * kDigitBytes * n_tok, xr[sb * 64u + 2u * lane], xr[sb * 64u + 2u * lane + 1u], sb, n_tok, tok, lane, perm != 0);
 }
 
 // ---- Q4_K: raw GGUF super-blocks (144 B), fetched as 160-byte slot rows (the extra 16 bytes keep the fragment reads conflict-free)

@@ -77,6 +77,10 @@ struct Geometry {
     uint32_t nb, ks;
     SkTable table;
     void *counters, *partials;
+    // int8 family, calls of several token tiles: the x records of ALL tiles, written by one conversion launch (tile i of
+    // `staged_tile` rows at staged + i * nb * rec_bytes(staged_tile)); null: every tile sees to its own
+    const uint8_t* staged = nullptr;
+    uint32_t staged_tile = 0;
 };
 
 /// x records a CTA of the resident kernels holds in shared memory: under a one-slice partition whose every CTA walks less
