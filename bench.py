@@ -381,6 +381,10 @@ def decode_shapes(be, st, rank: int, world: int, reps: int):
              ("cfg4 q4_0 eh_proj", synth.Q4_0, 5120, 10240, (16,), False), ("cfg4 q4_0 attn q / o", synth.Q4_0, 5120, 5120, (16,), False),
              ("cfg4 q4_0 attn k / v", synth.Q4_0, 1024, 5120, (16,), False), ("cfg4 q4_0 ffn gate / up", synth.Q4_0, 17408, 5120, (16,), False),
              ("cfg4 q4_0 ffn down", synth.Q4_0, 5120, 17408, (16,), False),
+             # the same layer with the projections that read one x held as ONE operand, as the reference's models hold them
+             # (src/models/qwen35.cpp:79-96, 220-253) and the decode sweep below loads them: one launch each
+             ("cfg4 q4_0 attn q|k|v as one operand", synth.Q4_0, 5120 + 1024 + 1024, 5120, (16,), False),
+             ("cfg4 q4_0 ffn gate|up as one operand", synth.Q4_0, 2 * 17408, 5120, (16,), False),
              ("cfg4 q4_0 lm_head (matmul + argmax), vocab split", synth.Q4_0, vocab // world, 5120, (16,), True)]
     out = []
     e0, e1 = C.c_void_p(), C.c_void_p()

@@ -71,7 +71,7 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 //   meta    [row][48 B]                                      int32 pairs (X_p, X_{4+p}) for p = 0..3 (sums of xq over 32 elements: what
 //                                                            Q4_K's mins multiply), 1 / s as fp32 at byte 32
 // The digit area and the meta area are separate arrays (all super-blocks of one, then all of the other), in shared
-// memory as in the scratch the pre-staging kernel fills.
+// memory as in the scratch the conversion kernel (stage_x_i8_kernel) fills.
 constexpr uint32_t kDigitBytes = 512, kMetaBytes = 48;
 __host__ __device__ inline constexpr uint32_t rec_bytes(uint32_t n_tok) { return (kDigitBytes + kMetaBytes) * n_tok; }
 inline uint64_t stage_scratch_bytes(uint32_t nb, uint32_t n_tok) { return uint64_t{nb} * rec_bytes(n_tok); }
@@ -692,6 +692,9 @@ __device__ __forceinline__ void finish_slices(float (&yacc)[G][2], uint32_t unit
 
 // KSC: the slice count where it is known at compile time (the two-slice partition of the large shapes, whose inner loop
 // is the one that runs at memory speed), 0: taken from ks_shift_arg.
+// PRE (every launch of two x rows and up): the x records come from `xstage`, where a conversion launch wrote them, or --
+// xstage == nullptr -- the kernel converts the rows itself (the host chooses: gemv_i8_launch.cuh).  A single row is always
+// converted in the kernel.
 // XC > 0 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of n_rec columns (as many
 // as fit: fewer block barriers, more room for the warps to run ahead of one another); the records of
 // a stretch (KS super-blocks per column, all NTOK rows) sit in one half of a double buffer, the next stretch's are copied into
@@ -764,7 +767,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + off_zero)[i] = 0u;
     constexpr uint32_t kXFull = kOffRed + 160u;  // two mbarriers of the streamed form (the warp-sum floats before them end at kOffRed + 128)
     if constexpr (XC > 0) {
-        static_assert(PRE && NTOK >= 2 && kXFull + 16u <= kOffBars, "streamed x: pre-staged batches");
+        static_assert(PRE && NTOK >= 2 && kXFull + 16u <= kOffBars, "streamed x: batches, records from the conversion launch");
         if (tid == 0) {
             mbar_init(smem_base + kXFull, 1);
             mbar_init(smem_base + kXFull + 8u, 1);
