@@ -48,6 +48,11 @@ class GemvPlan(C.Structure):
                 ("start", C.c_uint32 * 161)]
 
 
+class GemvTiles(C.Structure):
+    _fields_ = [("tile_rows", C.c_uint32), ("launches", C.c_uint32), ("conversions", C.c_uint32), ("streamed", C.c_uint32),
+                ("stretch_cols", C.c_uint32), ("resident_rows", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+
+
 class PeerReduce(C.Structure):
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("capacity", C.c_uint32), ("reserved", C.c_uint32),
                 ("slots", C.c_void_p * 8), ("epoch", C.c_void_p), ("done", C.c_void_p)]
@@ -121,6 +126,7 @@ SYMBOLS = {
     "halo_cuda_lm_head_noalloc": (C.c_int, [_P, C.POINTER(LmHead), _P]),
     "halo_cuda_repacked_row_bytes": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
     "halo_cuda_gemv_plan_i8": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvPlan)]),
+    "halo_cuda_gemv_tiles_i8": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvTiles)]),
     "halo_cuda_repacked_variant": (C.c_int, [C.c_uint32, C.c_uint64, C.POINTER(C.c_uint32)]),
     "halo_cuda_repack_rows": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64, _P, C.c_uint64, C.c_uint32, C.c_uint32, _P]),
     "halo_cuda_gemv_plan": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(GemvPlan)]),

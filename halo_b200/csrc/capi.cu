@@ -786,6 +786,22 @@ int halo_cuda_gemv_plan_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_
     return 0;
 }
 
+int halo_cuda_gemv_tiles_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* tiles) {
+    if (tiles == nullptr) return fail(HALO_CUDA_E_API, "null argument");
+    if (wtype != HALO_CUDA_T_Q4_K && repacked_row_bytes(wtype, 256) == 0)
+        return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: no tensor-core skinny kernel for weight type id %u", wtype);
+    if (cols == 0 || cols % 256u != 0) return fail(HALO_CUDA_E_MODEL, "MATMUL: %u elements is not a multiple of 256", cols);
+    if (rows == 0 || sm_count == 0) return fail(HALO_CUDA_E_KERNEL, "MATMUL: empty matrix or device");
+    switch (wtype) {
+        case HALO_CUDA_T_Q6_K: gemv_i8_q6kr_tiles(rows, cols, n_vec, sm_count, tiles); break;
+        case HALO_CUDA_T_Q8_0: gemv_i8_q80r_tiles(rows, cols, n_vec, sm_count, tiles); break;
+        case HALO_CUDA_T_Q4_0: gemv_i8_q40r_tiles(rows, cols, n_vec, sm_count, tiles); break;
+        default: gemv_i8_q4k_tiles(rows, cols, n_vec, sm_count, tiles); break;
+    }
+    if (tiles->resident_rows == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the int8 kernels keep x in shared memory; %u columns do not fit", cols);
+    return 0;
+}
+
 int halo_cuda_gemv_reduce(HaloCudaCtx* ctx, const HaloCudaGemv* args, const HaloCudaPeerReduce* peers, HaloCudaStream stream) {
     if (int rc = enter(ctx)) return rc;
     GemvCall c{};

@@ -175,56 +175,89 @@ bool fits_format(uint32_t cols) {
     return cols != 0 && cols % 256u == 0 && max_tile<F>(cols / 256u, 0) != 0;
 }
 
+/// How a call of n_vec x rows is cut into launches: a function of the partition and the format alone (host arithmetic).
+struct TilePlan {
+    uint32_t tile = 0;      // x rows of every launch but the last (0: not even one row's records fit)
+    uint32_t cap_res = 0;   // the most rows the resident form holds
+    bool streamed = false;  // tiles of two rows and up stream x
+    bool one_stage = false; // one conversion launch writes the records of every tile
+    uint32_t launches = 0, conversions = 0, stretch = 0;  // matmul launches, conversion launches, columns per stretch (streamed)
+};
+
 template <class F>
-int launch_format(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
-    sk::Geometry g{};
-    plan<F>(ctx, c, &g);
+TilePlan tile_plan(const sk::Geometry& g, uint32_t n_vec) {
+    TilePlan p;
     // The partition decides how many records a CTA holds, and that the token tile; a batch is cut into equal tiles
     // (whole MMA column groups of four rows where that still fits).
-    const uint32_t cap_res = max_tile<F>(sk::resident_records(g), log2_of(g.ks));
-    if (cap_res == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the int8 kernels keep x in shared memory; %u columns do not fit", c.cols);
+    const uint32_t ks_shift = log2_of(g.ks);
+    p.cap_res = max_tile<F>(sk::resident_records(g), ks_shift);
+    if (p.cap_res == 0 || n_vec == 0) return p;
     // A batch larger than the resident form holds in one tile streams x instead, where that makes the tile larger: the weights
     // are then read once (same tiles, same order, same bits).
-    uint32_t cap = cap_res;
-    bool streamed = false;
+    uint32_t cap = p.cap_res;
     // (only where a CTA walks at least eight columns: on short walks the stretch barriers cost more than the second pass over
     // weights that are still in L2 -- 5120 x 5120 at 16 rows measured 21.7 us streamed against 19.0 us in two resident tiles)
     uint32_t longest = 0;
     for (uint32_t cc = 0; cc < g.table.parts; ++cc) longest = std::max(longest, g.table.start[cc + 1] - g.table.start[cc]);
-    if (c.n_vec > cap_res && static_cast<uint32_t>(F::kMaxTok) > cap_res && longest >= 8) {
+    if (n_vec > p.cap_res && static_cast<uint32_t>(F::kMaxTok) > p.cap_res && longest >= 8) {
         uint32_t cap_s = 0;
         for (uint32_t n = F::kMaxTok; n >= static_cast<uint32_t>(kStreamFrom) && cap_s == 0; --n)
-            if (smem_bytes_streamed<F>(n, log2_of(g.ks)) <= kSmemBudget) cap_s = n;
-        if (cap_s > cap_res && c.n_vec >= static_cast<uint32_t>(kStreamFrom)) cap = cap_s, streamed = true;
+            if (smem_bytes_streamed<F>(n, ks_shift) <= kSmemBudget) cap_s = n;
+        if (cap_s > p.cap_res && n_vec >= static_cast<uint32_t>(kStreamFrom)) cap = cap_s, p.streamed = true;
     }
-    const uint32_t n_tiles = (c.n_vec + cap - 1) / cap;
-    uint32_t tile = (c.n_vec + n_tiles - 1) / std::max(n_tiles, 1u);
-    if ((tile + 3u) / 4u * 4u <= cap) tile = (tile + 3u) / 4u * 4u;
-    if (streamed && tile < static_cast<uint32_t>(kStreamFrom)) tile = std::min<uint32_t>(cap, kStreamFrom);
+    const uint32_t n_tiles = (n_vec + cap - 1) / cap;
+    p.tile = (n_vec + n_tiles - 1) / n_tiles;
+    if ((p.tile + 3u) / 4u * 4u <= cap) p.tile = (p.tile + 3u) / 4u * 4u;
+    if (p.streamed && p.tile < static_cast<uint32_t>(kStreamFrom)) p.tile = std::min<uint32_t>(cap, kStreamFrom);
+    p.tile = std::min(p.tile, n_vec);  // (a call of fewer rows than the rounded tile is one launch of its own size)
+    if (p.streamed) p.stretch = stretch_columns<F>(std::min(p.tile, n_vec), ks_shift);
+    // Every tile but the last has `tile` rows, so tile i starts at row i * tile; a last tile of one row is converted in its kernel.
+    uint32_t staged_tiles = 0;
+    for (uint32_t t0 = 0; t0 < n_vec; t0 += p.tile) {
+        const uint32_t left = n_vec - t0, n = std::min(left, p.tile);
+        ++p.launches;
+        if (tile_needs_stage(g, n, p.streamed && left >= static_cast<uint32_t>(kStreamFrom))) ++staged_tiles;
+    }
     // A call of several tiles converts all of its x rows in ONE launch where any tile wants the records made for it: every further
-    // conversion launch would be another dependent launch on the chain (two tiles of eight rows: 5120 x 5120 19.2 -> 17.0 us, 1024 x 5120 13.2 -> 11.2).
-    // Every tile but the last has `tile` rows, so tile i starts at row i * tile.
-    if (c.n_vec > tile) {
-        bool any = false;
-        for (uint32_t t0 = 0; t0 < c.n_vec; t0 += tile) {
-            const uint32_t left = c.n_vec - t0, n = std::min(left, tile);
-            any = any || tile_needs_stage(g, n, streamed && left >= static_cast<uint32_t>(kStreamFrom));
-        }
-        if (any) {
-            const uint32_t tiles_all = (c.n_vec + tile - 1) / tile;
-            void* ws = nullptr;
-            if (int rc = workspace(ctx, 0, uint64_t{tiles_all} * stage_scratch_bytes(g.nb, tile), s, &ws)) return rc;
-            if (int rc = launch_stage(c.x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, tile, c.n_vec, F::kPermX, s)) return rc;
-            g.staged = static_cast<const uint8_t*>(ws), g.staged_tile = tile;
-        }
+    // conversion launch would be another dependent launch on the chain (two tiles of eight rows: 5120 x 5120 19.2 -> 17.0 us,
+    // 1024 x 5120 13.2 -> 11.2).
+    p.one_stage = n_vec > p.tile && staged_tiles != 0;
+    p.conversions = p.one_stage ? 1u : staged_tiles;
+    return p;
+}
+
+/// The same for inspection: the plan of a rows x cols matmul at n_vec x rows on a device with `sm_count` SMs.
+template <class F>
+TilePlan tile_plan_for(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count) {
+    sk::Geometry g{};
+    g.nb = cols / 256u;
+    g.ks = plan_for<F>(rows, cols, sm_count, &g.table);
+    return tile_plan<F>(g, n_vec);
+}
+
+inline void fill_tiles(const TilePlan& p, HaloCudaGemvTiles* out) {
+    *out = HaloCudaGemvTiles{};
+    out->tile_rows = p.tile, out->launches = p.launches, out->conversions = p.conversions, out->streamed = p.streamed ? 1u : 0u;
+    out->stretch_cols = p.stretch, out->resident_rows = p.cap_res;
+}
+
+template <class F>
+int launch_format(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) {
+    sk::Geometry g{};
+    plan<F>(ctx, c, &g);
+    const TilePlan p = tile_plan<F>(g, c.n_vec);
+    if (p.cap_res == 0) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the int8 kernels keep x in shared memory; %u columns do not fit", c.cols);
+    if (p.one_stage) {
+        const uint32_t tiles_all = (c.n_vec + p.tile - 1) / p.tile;
+        void* ws = nullptr;
+        if (int rc = workspace(ctx, 0, uint64_t{tiles_all} * stage_scratch_bytes(g.nb, p.tile), s, &ws)) return rc;
+        if (int rc = launch_stage(c.x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, p.tile, c.n_vec, F::kPermX, s)) return rc;
+        g.staged = static_cast<const uint8_t*>(ws), g.staged_tile = p.tile;
     }
-    for (uint32_t t0 = 0; t0 < c.n_vec;) {
-        const uint32_t left = c.n_vec - t0;
-        // a remainder too small for the streamed form runs resident, in tiles the resident form holds
-        const bool stream_this = streamed && left >= static_cast<uint32_t>(kStreamFrom);
-        const uint32_t n = stream_this ? std::min(left, tile) : std::min(left, streamed ? cap_res : tile);
-        if (int rc = launch_tokens<F, 1>(ctx, c, g, t0, n, stream_this, s)) return rc;
-        t0 += n;
+    for (uint32_t t0 = 0; t0 < c.n_vec; t0 += p.tile) {
+        const uint32_t left = c.n_vec - t0, n = std::min(left, p.tile);
+        // (a last tile of one row runs the single-row kernel)
+        if (int rc = launch_tokens<F, 1>(ctx, c, g, t0, n, p.streamed && left >= static_cast<uint32_t>(kStreamFrom), s)) return rc;
     }
     return 0;
 }

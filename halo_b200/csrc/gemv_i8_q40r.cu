@@ -6,4 +6,7 @@ bool gemv_i8_q40r_supports(const GemvCall& c) { return i8::supports_format<i8::Q
 bool gemv_i8_q40r_fits(uint32_t cols) { return i8::fits_format<i8::Q40i>(cols); }
 int launch_gemv_i8_q40r(HaloCudaCtx* ctx, const GemvCall& c, cudaStream_t s) { return i8::launch_format<i8::Q40i>(ctx, c, s); }
 uint32_t gemv_i8_q40r_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table) { return i8::plan_for<i8::Q40i>(rows, cols, sm_count, table); }
+void gemv_i8_q40r_tiles(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* out) {
+    i8::fill_tiles(i8::tile_plan_for<i8::Q40i>(rows, cols, n_vec, sm_count), out);
+}
 }  // namespace halo_cuda

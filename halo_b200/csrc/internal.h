@@ -150,6 +150,10 @@ uint32_t gemv_i8_q4k_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::
 uint32_t gemv_i8_q6kr_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
 uint32_t gemv_i8_q80r_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
 uint32_t gemv_i8_q40r_plan(uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);
+void gemv_i8_q4k_tiles(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* out);
+void gemv_i8_q6kr_tiles(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* out);
+void gemv_i8_q80r_tiles(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* out);
+void gemv_i8_q40r_tiles(uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* out);
 uint32_t gemv_i8_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, mma::SkTable* table);  // by weight type
 bool gemv_i8_q6kr_fits(uint32_t cols);
 bool gemv_i8_q80r_fits(uint32_t cols);

@@ -4,7 +4,7 @@ Every (type, N, K) is loaded the way a loader of this backend loads it (Q4_K raw
 through `halo_cuda_gemv` with the variant the backend names for it, over enough distinct weight copies to exceed L2, back to back on one
 stream with CUDA events.  One line per shape: microseconds, the share of the measured HBM rate the weight bytes make, and the time relative
 to the first batch size -- a batch that costs much more than a single row, or a shape far below its neighbours, is a partition or tiling
-cliff (the planner and the token tiles are functions of the shape: halo_cuda_gemv_plan_i8)."""
+cliff (the partition and the token tiles are functions of the shape: halo_cuda_gemv_plan_i8, halo_cuda_gemv_tiles_i8)."""
 from __future__ import annotations
 
 import argparse

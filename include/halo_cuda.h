@@ -236,6 +236,21 @@ int halo_cuda_gemv_plan(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t s
  * shared memory for a tile of eight rows, or where it walks fewer tiles even with the cross-CTA reduction -- the even split of
  * the columns with one slice.  A function of (wtype, rows, cols, sm_count) alone. */
 int halo_cuda_gemv_plan_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t sm_count, HaloCudaGemvPlan* plan);
+/* How the int8 family cuts a call of n_vec x rows into launches (host arithmetic, like the plans above).  A launch holds the x
+ * records of its rows in shared memory next to the weight ring: all of them (resident, at most `resident_rows` rows), or -- a
+ * batch the resident form cannot hold in one launch, where a CTA walks at least eight columns -- a double buffer of `stretch_cols`
+ * columns at a time (streamed).  The records are made in the matmul kernel itself (one row; a batch whose CTAs have few to make)
+ * or by ONE conversion launch per call.  Whatever the cut, a row's bits are those of its single-row call. */
+typedef struct HaloCudaGemvTiles {
+    uint32_t tile_rows;     /* x rows of every matmul launch but the last */
+    uint32_t launches;      /* matmul launches: passes over the weights */
+    uint32_t conversions;   /* conversion launches ahead of them (0 or 1) */
+    uint32_t streamed;      /* 1: launches of two rows and up stream their x records */
+    uint32_t stretch_cols;  /* columns per stretch of a streamed launch, else 0 */
+    uint32_t resident_rows; /* the most rows the resident form holds for this shape */
+    uint32_t reserved[2];
+} HaloCudaGemvTiles;
+int halo_cuda_gemv_tiles_i8(uint32_t wtype, uint32_t rows, uint32_t cols, uint32_t n_vec, uint32_t sm_count, HaloCudaGemvTiles* tiles);
 
 /* ---- the operators ------------------------------------------------------------------------------ */
 int halo_cuda_gemv(HaloCudaCtx* ctx, const HaloCudaGemv* args, HaloCudaStream stream);

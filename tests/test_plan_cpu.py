@@ -145,3 +145,61 @@ def test_i8_plan_rejects_what_the_kernels_do_not_take():
     assert lib.halo_cuda_gemv_plan_i8(synth.Q4_K, 16, 1000, 148, C.byref(p)) == capi.E_MODEL
     assert lib.halo_cuda_gemv_plan_i8(0, 16, 1024, 148, C.byref(p)) == capi.E_UNSUPPORTED
     assert lib.halo_cuda_gemv_plan_i8(synth.Q4_K, 0, 1024, 148, C.byref(p)) == capi.E_KERNEL
+
+
+# ---- how the int8 family cuts a call into launches (halo_cuda_gemv_tiles_i8) ------------------------------------------------------
+MAX_TILE = {synth.Q4_K: 16, synth.Q4_0: 16, synth.Q8_0: 8, synth.Q6_K: 8}  # x rows of one launch, by format
+
+
+def tiles_i8(wtype: int, rows: int, cols: int, n_vec: int, sms: int = 148):
+    lib = capi.load()
+    t = capi.GemvTiles()
+    rc = lib.halo_cuda_gemv_tiles_i8(wtype, rows, cols, n_vec, sms, C.byref(t))
+    assert rc == 0, capi.last_error()
+    return t
+
+
+def longest_range(wtype: int, rows: int, cols: int, sms: int = 148) -> int:
+    _, _, _, start = plan_i8(wtype, rows, cols, sms)
+    return max(b - a for a, b in zip(start, start[1:]))
+
+
+def test_i8_tiles_of_the_benchmark_shapes():
+    t = tiles_i8(synth.Q4_K, 17408, 5120, 1)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (1, 1, 0, 0)      # a single row is converted in the matmul kernel
+    t = tiles_i8(synth.Q8_0, 5120, 17408, 8)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (8, 1, 0, 0)      # ten columns per CTA: 80 records, made in the kernel
+    t = tiles_i8(synth.Q4_0, 17408, 5120, 16)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (16, 1, 1, 1)     # gate / up: twenty records of sixteen rows do not fit
+    assert 2 <= t.stretch_cols <= 8
+    t = tiles_i8(synth.Q4_0, 5120, 5120, 16)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (8, 2, 1, 0)      # q / o: a short walk, two resident tiles, ONE conversion
+    t = tiles_i8(synth.Q4_0, 5120, 17408, 16)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (16, 1, 1, 0)     # down: a CTA keeps only its ten columns' records
+    t = tiles_i8(synth.Q4_K, 17408, 5120, 17)
+    assert (t.tile_rows, t.launches, t.conversions, t.streamed) == (12, 2, 1, 1)     # equal tiles of whole column groups: 12 + 5 rows
+
+
+@pytest.mark.parametrize("wtype", sorted(MAX_TILE))
+def test_i8_batches_are_one_pass_over_the_weights(wtype):
+    """The cliff this guards against: a CTA that keeps many x records (a tall matrix under the even split, a long K) leaves the
+    resident form room for one or two rows, and a batch of eight used to run as four to eight launches, each reading all weights.
+    Such a batch streams x instead.  Over a grid of shapes: up to eight rows are ONE launch whatever the format; sixteen rows are
+    one launch for the 16-row formats under one or two slices (streamed, or resident where a CTA keeps few records) and two
+    otherwise; never more than one conversion launch."""
+    for cols in (2048, 4096, 5120, 8192, 14336, 17408, 28672):
+        for rows in (1024, 4096, 8192, 20480, 32768, 128256):
+            if rows * cols > 1.3e9:
+                continue
+            slices = plan_i8(wtype, rows, cols)[0]
+            for n_vec in (2, 4, 8, 16):
+                t = tiles_i8(wtype, rows, cols, n_vec)
+                where = f"{rows} x {cols} at {n_vec} rows: {t.launches} launches of {t.tile_rows} rows"
+                assert t.conversions <= 1, where
+                assert t.launches * t.tile_rows >= n_vec and (t.launches - 1) * t.tile_rows < n_vec, where
+                if n_vec <= 8:
+                    assert t.launches == 1, where
+                elif MAX_TILE[wtype] == 8:
+                    assert t.launches == 2 and t.tile_rows == 8, where
+                else:
+                    assert t.launches <= 2 and (t.launches == 1 or slices >= 4), where
