@@ -154,6 +154,7 @@ struct Q4Ki {
     static constexpr bool kPermX = false;
     static constexpr int kMaxTok = 16;  // x rows per launch (four MMA column groups); larger batches, or records that do not fit, run in tiles
     static constexpr uint32_t kStretchMax = 8;  // columns per stretch of streamed x
+    static constexpr bool kPipedConversion = false;
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return g; }
 
     /// Lane constants of the single-row form.
@@ -447,6 +448,9 @@ struct Q80i : Blocks32<Q80i> {
     static constexpr int kShift = 0, kMaxTok = 8;  // the int8 quants are the operand
     static constexpr uint32_t kStretchMax = 3;
     static constexpr bool kPackedEpilogue = false;  // (measured 1.7 % slower at 8 rows: this format waits on its weights, not on issue slots)
+    // A batch that converts its x rows in the kernel does the later rounds behind its first tiles (5120 x 17408 at 8 rows 24.9 -> 22.6 us).
+    // The other formats' batch kernels are bound by issue slots and lose 3 - 6 % to the hooks in the tile loop.
+    static constexpr bool kPipedConversion = true;
     struct Frag {
         uint4 q[4];  // chunk c: (block 2c, k-step 0), (block 2c, k-step 1), (block 2c + 1, k-step 0), (block 2c + 1, k-step 1)
     };
@@ -465,6 +469,7 @@ struct Q40i : Blocks32<Q40i> {
     static constexpr int kShift = 4, kMaxTok = 16;  // the operand is 16 (q - 8)
     static constexpr uint32_t kStretchMax = 8;
     static constexpr bool kPackedEpilogue = true;  // two-wide fp32 operations in the batch epilogue: 1.5 - 2.4 % fewer microseconds at 16 rows
+    static constexpr bool kPipedConversion = false;
     struct Frag {
         uint4 q[2];  // chunk c: the words of blocks 4c .. 4c + 3 (low nibbles: elements 4t .., high nibbles: elements 16 + 4t ..)
     };
@@ -498,6 +503,7 @@ struct Q6Ki {
     static constexpr bool kPermX = true;
     static constexpr int kMaxTok = 8;
     static constexpr uint32_t kStretchMax = 8;
+    static constexpr bool kPipedConversion = false;
     /// 224-byte slot rows put rows g and g + 1 on overlapping banks: fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7
     __device__ static __forceinline__ uint32_t slot_row(uint32_t g) { return ((2u * g) & 7u) | (g >> 2); }
 
@@ -695,7 +701,8 @@ __device__ __forceinline__ void finish_slices(float (&yacc)[G][2], uint32_t unit
 // PRE (every launch of two x rows and up): the x records come from `xstage`, where a conversion launch wrote them, or --
 // xstage == nullptr -- the kernel converts the rows itself (the host chooses: gemv_i8_launch.cuh).  A single row is always
 // converted in the kernel.
-// XC > 0 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of n_rec columns (as many
+// XC == 2: a resident batch launch that converts its x rows itself does so in rounds, the later ones behind its first tiles.
+// XC == 1 (batches whose x records do not all fit): x is STREAMED.  The CTA's columns are walked in stretches of n_rec columns (as many
 // as fit: fewer block barriers, more room for the warps to run ahead of one another); the records of
 // a stretch (KS super-blocks per column, all NTOK rows) sit in one half of a double buffer, the next stretch's are copied into
 // the other half meanwhile, and a block barrier ends every stretch.  Same tiles, same order, same arithmetic as the resident
@@ -763,10 +770,32 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     bool lost = false;
+    // In-kernel conversion of a batch (PRE launches without a conversion launch): pairs to convert, rounds of sixteen, this warp's next round
+    [[maybe_unused]] uint32_t cv_first = 0, cv_items = 0, cv_rounds = 0, cv_next = 0, cv_seen = 1;
+    [[maybe_unused]] auto cv_src = [&](uint32_t i) {  // this lane's eight floats of pair i
+        const uint32_t j = i / NTOK, tok = i - j * NTOK;
+        const uint32_t sb = cv_first + j >= nb ? cv_first + j - nb : cv_first + j;  // (a one-slice partition has cpu == nb)
+        return reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tok} * x_stride) + sb * 64u + 2u * lane;
+    };
+    [[maybe_unused]] auto cv_prefetch = [&]() {  // the row of this warp's next pair -> L1, ahead of the tile it is converted behind
+        const uint32_t i = warp + cv_next * kSkWarps;
+        if (cv_next < cv_rounds && i < cv_items) asm volatile("prefetch.global.L1 [%0];" ::"l"(cv_src(i)));
+    };
+    [[maybe_unused]] auto cv_step = [&]() {  // converts this warp's pair of round cv_next (if it has one) and arrives on the round's barrier
+        const uint32_t i = warp + cv_next * kSkWarps;
+        if (i < cv_items) {
+            const float4* src = cv_src(i);
+            const float4 a = src[0], b = src[1];
+            stage_superblock(smem + off_digits, smem + off_digits + n_rec * (kDigitBytes * NTOK), a, b, i / NTOK, NTOK, i % NTOK, lane, F::kPermX);
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_base + kOffRounds + (cv_next - 2u) * 8u) : "memory");
+        ++cv_next;
+    };
     if constexpr (NTOK == 1)
         for (uint32_t i = tid; i < 512u / 4u; i += kThreads) reinterpret_cast<uint32_t*>(smem + off_zero)[i] = 0u;
     constexpr uint32_t kXFull = kOffRed + 160u;  // two mbarriers of the streamed form (the warp-sum floats before them end at kOffRed + 128)
-    if constexpr (XC > 0) {
+    if constexpr (XC == 1) {
         static_assert(PRE && NTOK >= 2 && kXFull + 16u <= kOffBars, "streamed x: batches, records from the conversion launch");
         if (tid == 0) {
             mbar_init(smem_base + kXFull, 1);
@@ -806,32 +835,64 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 lost = true;
             }
         } else {
-            // No conversion launch (the host leaves it out where a CTA has few records to make): the rows are converted here, a
-            // (record, row) pair per warp at a time, record-major, the loads of kAhead pairs in flight together.  Under a partial
-            // residency these are the super-blocks of the CTA's own columns only; under in-CTA slices every CTA converts all of x.
-            const uint32_t x_c0 = tb.start[cta], x_cols = tb.start[cta + 1] - x_c0;
-            const bool part = KS == 1 && n_rec < nb;
-            const uint32_t x_first = part ? x_c0 % cpu : 0u, n_items = (part ? x_cols : nb) * NTOK;
-            constexpr uint32_t kAhead = 4;  // (eight measured the same or slower)
-            for (uint32_t i0 = warp; i0 < n_items; i0 += kAhead * kSkWarps) {
-                float4 v[kAhead][2];
+            if constexpr (XC == 2) {
+                // No conversion launch (the host leaves it out where a CTA has few records to make): the rows are converted here, a
+                // (record, row) pair per warp at a time, record-major: pair i = warp + 16 u belongs to ROUND u.  Under a partial
+                // residency the records are the super-blocks of the CTA's own columns only; under in-CTA slices every CTA converts all
+                // of x.  Rounds 0 and 1 are converted before the first tile (their loads in flight together, a block barrier behind
+                // them); a later round is converted by every warp after one of its tiles (the row was prefetched before that tile) and
+                // completes behind an mbarrier that only the tiles of its records wait for.
+                const uint32_t x_c0 = tb.start[cta], x_cols = tb.start[cta + 1] - x_c0;
+                const bool part = KS == 1 && n_rec < nb;
+                cv_first = part ? x_c0 % cpu : 0u, cv_items = (part ? x_cols : nb) * NTOK, cv_rounds = (cv_items + kSkWarps - 1u) / kSkWarps;
+                if (tid == 0 && cv_rounds > 2u) {
+                    for (uint32_t u = 2; u < cv_rounds; ++u) mbar_init(smem_base + kOffRounds + (u - 2u) * 8u, kSkWarps);
+                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                }
+                float4 v[2][2];
 #pragma unroll
-                for (uint32_t u = 0; u < kAhead; ++u) {
-                    const uint32_t i = i0 + u * kSkWarps;
-                    if (i < n_items) {
-                        const uint32_t j = i / NTOK, tok = i - j * NTOK;
-                        const uint32_t sb = x_first + j >= nb ? x_first + j - nb : x_first + j;  // (a one-slice partition has cpu == nb)
-                        const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tok} * x_stride);
-                        v[u][0] = xr[sb * 64u + 2u * lane], v[u][1] = xr[sb * 64u + 2u * lane + 1u];
+                for (uint32_t u = 0; u < 2; ++u) {
+                    const uint32_t i = warp + u * kSkWarps;
+                    if (i < cv_items) {
+                        const float4* src = cv_src(i);
+                        v[u][0] = src[0], v[u][1] = src[1];
                     }
                 }
 #pragma unroll
-                for (uint32_t u = 0; u < kAhead; ++u) {
-                    const uint32_t i = i0 + u * kSkWarps;
-                    if (i < n_items) stage_superblock(digits, meta, v[u][0], v[u][1], i / NTOK, NTOK, i % NTOK, lane, F::kPermX);
+                for (uint32_t u = 0; u < 2; ++u) {
+                    const uint32_t i = warp + u * kSkWarps;
+                    if (i < cv_items) stage_superblock(digits, meta, v[u][0], v[u][1], i / NTOK, NTOK, i % NTOK, lane, F::kPermX);
                 }
+                cv_next = 2;
+                __syncthreads();
+            } else {
+                // No conversion launch (the host leaves it out where a CTA has few records to make): the rows are converted here, a
+                // (record, row) pair per warp at a time, record-major, the loads of kAhead pairs in flight together.  Under a partial
+                // residency these are the super-blocks of the CTA's own columns only; under in-CTA slices every CTA converts all of x.
+                const uint32_t x_c0 = tb.start[cta], x_cols = tb.start[cta + 1] - x_c0;
+                const bool part = KS == 1 && n_rec < nb;
+                const uint32_t x_first = part ? x_c0 % cpu : 0u, n_items = (part ? x_cols : nb) * NTOK;
+                constexpr uint32_t kAhead = 4;  // (eight measured the same or slower)
+                for (uint32_t i0 = warp; i0 < n_items; i0 += kAhead * kSkWarps) {
+                    float4 v[kAhead][2];
+#pragma unroll
+                    for (uint32_t u = 0; u < kAhead; ++u) {
+                        const uint32_t i = i0 + u * kSkWarps;
+                        if (i < n_items) {
+                            const uint32_t j = i / NTOK, tok = i - j * NTOK;
+                            const uint32_t sb = x_first + j >= nb ? x_first + j - nb : x_first + j;  // (a one-slice partition has cpu == nb)
+                            const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const uint8_t*>(x) + uint64_t{tok} * x_stride);
+                            v[u][0] = xr[sb * 64u + 2u * lane], v[u][1] = xr[sb * 64u + 2u * lane + 1u];
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t u = 0; u < kAhead; ++u) {
+                        const uint32_t i = i0 + u * kSkWarps;
+                        if (i < n_items) stage_superblock(digits, meta, v[u][0], v[u][1], i / NTOK, NTOK, i % NTOK, lane, F::kPermX);
+                    }
+                }
+                __syncthreads();
             }
-            __syncthreads();
         }
     } else {
         static_assert(NTOK == 1, "batches arrive through the branch above");
@@ -932,7 +993,7 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             }
         finish_slices<G, NTOK>(yacc, unit, r, ks, KS, R, red, tb, cta, partials, counters, y, y_stride, rows, lane, F::slot_row(g), peer);
     };
-    if constexpr (XC > 0) {
+    if constexpr (XC == 1) {
         constexpr uint32_t kD = kDigitBytes * NTOK, kM = kMetaBytes * NTOK;
         const uint32_t xc = n_rec;  // (streamed form: the parameter carries the columns per stretch)
         const uint32_t col_bytes = KS * (kD + kM), half_bytes = xc * col_bytes;  // a column: KS super-blocks of digits, then KS of meta
@@ -1002,6 +1063,21 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     late_ready = true;
                 }
             }
+            if constexpr (XC == 2) {
+                if (cv_rounds > 2u) {
+                    // the round that completes this record; a warp converts its own pairs up to that round before it waits for the others'
+                    const uint32_t need = (rec * NTOK + NTOK - 1u) / kSkWarps;
+                    if (need > cv_seen) {
+                        while (cv_next <= need) cv_step();
+                        if (!mbar_wait(smem_base + kOffRounds + (need - 2u) * 8u, 0)) {
+                            if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
+                            lost = true;
+                        }
+                        cv_seen = need;
+                    }
+                    cv_prefetch();
+                }
+            }
             if (!lost && !mbar_wait(bars + slot * 8u, parity)) {
                 if (lane == 0 && error_word != nullptr) atomicOr(error_word, 1u);
                 lost = true;  // warp-uniform: every lane polled the same barrier
@@ -1012,9 +1088,18 @@ gemv_i8_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 F::item_one(slot0 + slot * kSlot, t, one, rec, meta, P1, release);
             } else {
                 F::template item_many<G, NTOK>(slot0 + slot * kSlot, t, g, digits + rec * (kDigitBytes * NTOK), meta + rec * (kMetaBytes * NTOK), P, release);
+                if constexpr (XC == 2) {
+                    if (cv_next < cv_rounds) cv_step();
+                }
             }
         }
+        if constexpr (XC == 2) {  // before it meets its siblings at the unit's end a warp has converted all its pairs: the warps that
+            while (cv_next < cv_rounds) cv_step();  // still wait for a round wait for nobody who waits for them
+        }
         finish_unit(unit);
+    }
+    if constexpr (XC == 2) {  // a warp without tiles still owes the other warps its pairs
+        while (cv_next < cv_rounds) cv_step();
     }
     if (lost) sk::linger_after_loss();
 }

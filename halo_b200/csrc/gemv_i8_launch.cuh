@@ -90,8 +90,8 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     constexpr bool PRE = NTOK >= 2;
     using L = Layout<F, NTOK, kRing>;
     // n_rec: the resident records, or (streamed form) the columns per stretch
-    const uint32_t ks_shift = log2_of(g.ks), n_rec = XC > 0 ? stretch_columns<F>(NTOK, ks_shift) : sk::resident_records(g);
-    const uint32_t smem_bytes = XC > 0 ? smem_bytes_streamed<F>(NTOK, ks_shift, n_rec) : L::bytes(n_rec, ks_shift);
+    const uint32_t ks_shift = log2_of(g.ks), n_rec = XC == 1 ? stretch_columns<F>(NTOK, ks_shift) : sk::resident_records(g);
+    const uint32_t smem_bytes = XC == 1 ? smem_bytes_streamed<F>(NTOK, ks_shift, n_rec) : L::bytes(n_rec, ks_shift);
     if (smem_bytes > kSmemBudget) return fail(HALO_CUDA_E_KERNEL, "MATMUL: %u x records of %d rows do not fit in shared memory", n_rec, NTOK);
     const float* x = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(c.x) + uint64_t{tok0} * c.x_stride);
     float* y = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c.y) + uint64_t{tok0} * c.y_stride);
@@ -100,7 +100,7 @@ int launch_tile(HaloCudaCtx* ctx, const GemvCall& c, const sk::Geometry& g, uint
     const uint8_t* xstage = nullptr;
     if (PRE && g.staged != nullptr) {  // the call's one conversion launch has written this tile's records
         xstage = g.staged + uint64_t{tok0 / g.staged_tile} * g.nb * rec_bytes(g.staged_tile);
-    } else if (PRE && tile_needs_stage(g, NTOK, XC > 0)) {
+    } else if (PRE && tile_needs_stage(g, NTOK, XC == 1)) {
         void* ws = nullptr;
         if (int rc = workspace(ctx, 0, stage_scratch_bytes(g.nb, NTOK), s, &ws)) return rc;
         if (int rc = launch_stage(x, c.x_stride, static_cast<uint8_t*>(ws), g.nb, NTOK, NTOK, F::kPermX, s)) return rc;
@@ -144,6 +144,14 @@ int launch_tokens(HaloCudaCtx* ctx, const GemvCall& c, sk::Geometry& g, uint32_t
                 if (c.norm_w != nullptr) return fail(HALO_CUDA_E_UNSUPPORTED, "MATMUL: the fused input norm takes one x row");
                 if (g.ks == 2) return launch_tile<F, NTOK, 2, 1>(ctx, c, g, tok0, s);
                 return launch_tile<F, NTOK, 0, 1>(ctx, c, g, tok0, s);
+            }
+        }
+        if constexpr (F::kPipedConversion && NTOK >= 2) {
+            // a launch that converts more than three rounds of (record, row) pairs itself does the later rounds behind its first tiles
+            // (three rounds -- 5120 x 17408 at 4 rows -- measured 1 % slower that way)
+            if (g.staged == nullptr && !tile_needs_stage(g, NTOK, false) && sk::resident_records(g) * NTOK > 3 * kSkWarps) {
+                if (g.ks == 2) return launch_tile<F, NTOK, 2, 2>(ctx, c, g, tok0, s);
+                return launch_tile<F, NTOK, 0, 2>(ctx, c, g, tok0, s);
             }
         }
         if (g.ks == 2) return launch_tile<F, NTOK, 2>(ctx, c, g, tok0, s);  // the partition of the large shapes: slice count folded into the code

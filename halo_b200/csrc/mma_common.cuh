@@ -161,6 +161,7 @@ __device__ __forceinline__ void tma_tile_g2s(uint32_t dst, const CUtensorMap* ma
 //   [0, 16) unused | scales | partial maxima | mbarriers | weight ring |
 //   xs:  [sub-block][column][64 B] fp16 x in slot order    sx: [super-block][column][16 B] sub-block sums / 32
 constexpr uint32_t kOffXBar = 0, kOffScale = 16, kOffInv = 16 + 64, kOffRed = 16 + 128, kOffBars = 512, kOffRing = 2048;
+constexpr uint32_t kOffRounds = 1280;  // int8 family (16 warps, <= 6 stages: barriers end at 1280): up to eight mbarriers of the in-kernel x conversion
 constexpr int kMaxWarps = 32;  // kOffRed holds one float per warp, kOffBars eight bytes per warp and stage (<= 6 stages)
 
 // ---- balanced work partition -----------------------------------------------------------------------------------------
