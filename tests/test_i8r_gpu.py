@@ -153,6 +153,26 @@ def test_i8r_small_batches_stream_x_where_a_cta_keeps_many_records(be):
     assert np.array_equal(bits(y5), bits(y[:5]))
 
 
+@pytest.mark.parametrize("n,m", [(4000, 7), (5120, 5), (3500, 8)])
+def test_i8r_q8_0_batches_that_convert_x_behind_their_first_tiles(be, n, m):
+    """Q8_0 x 17408 under the even split at 5 - 8 rows: a CTA has more than three rounds of sixteen (record, row) pairs to convert, does
+    two in front of its first tile and the rest behind tiles, each round behind its own barrier.  Ragged on purpose: row counts whose
+    last unit leaves warps without tiles (they still owe their pairs), odd batch sizes.  Every row must equal its single-row call
+    (which converts everything up front) bit for bit, and the exact kernel within the family's tolerance."""
+    t, k = synth.Q8_0, 17408
+    w = synth.quant_weights(t, n, k, 21, 1)
+    x = synth.activations(m, k, 21, 2)
+    y = run(be, t, w, x, n, k)
+    raw = be.import_host_readonly(np.ascontiguousarray(w).view(np.uint8).reshape(-1))
+    ref = run_exact(be, t, raw, x, n, k)
+    raw.free()
+    assert np.max(np.abs(y - ref)) <= FAMILY_REL * np.max(np.abs(ref))
+    for r in range(m):
+        y1 = run(be, t, w, x[r:r + 1], n, k)
+        assert np.array_equal(bits(y1[0]), bits(y[r])), f"row {r}"
+    assert np.array_equal(bits(run(be, t, w, x, n, k)), bits(y)), "a second call gives the same bits"
+
+
 @pytest.mark.parametrize("t", TYPES)
 def test_i8r_strided_operands(be, t):
     n, k, m = 77, 1024, 3
