@@ -445,7 +445,7 @@ struct Blocks32 {
 
 struct Q80i : Blocks32<Q80i> {
     static constexpr uint32_t kType = HALO_CUDA_T_Q8_0, kPitch = 272, kItemCoord = 272 / 4, kBoxInner = 272 / 4, kMapElemBytes = 4;
-    static constexpr int kShift = 0, kMaxTok = 8;  // the int8 quants are the operand
+    static constexpr int kShift = 0, kMaxTok = 16;  // the int8 quants are the operand
     static constexpr uint32_t kStretchMax = 3;
     static constexpr bool kPackedEpilogue = false;  // (measured 1.7 % slower at 8 rows: this format waits on its weights, not on issue slots)
     // A batch that converts its x rows in the kernel does the later rounds behind its first tiles (5120 x 17408 at 8 rows 24.9 -> 22.6 us).
@@ -501,7 +501,7 @@ __device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, 
 struct Q6Ki {
     static constexpr uint32_t kType = HALO_CUDA_T_Q6_K, kPitch = 224, kItemCoord = 224 / 4, kBoxInner = 224 / 4, kMapElemBytes = 4;
     static constexpr bool kPermX = true;
-    static constexpr int kMaxTok = 8;
+    static constexpr int kMaxTok = 16;
     static constexpr uint32_t kStretchMax = 8;
     static constexpr bool kPipedConversion = false;
     /// 224-byte slot rows put rows g and g + 1 on overlapping banks: fragment rows 0..7 take slot rows 0,2,4,6,1,3,5,7

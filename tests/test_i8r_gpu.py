@@ -3,7 +3,7 @@
 Same family as gemv_mma_i8x2 (tests/test_i8_gpu.py): x is rounded to 16-bit fixed point per 256-element super-block, the
 products are exact integers up to the per-group scale, so the bound is sum |w_i| * (half a step of x_i) plus the
 reordered-summation bound (tests/unit/hip/test_hip_gemv.cpp:9-15), and rows are bitwise independent of the batch size
-(include/halo/backend/backend.h:300-304) whatever token tile (up to 16 rows for Q4_0, 8 for the others) a call is cut into."""
+(include/halo/backend/backend.h:300-304) whatever token tile (up to 16 rows) a call is cut into."""
 from __future__ import annotations
 
 import numpy as np

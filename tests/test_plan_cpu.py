@@ -148,7 +148,7 @@ def test_i8_plan_rejects_what_the_kernels_do_not_take():
 
 
 # ---- how the int8 family cuts a call into launches (halo_cuda_gemv_tiles_i8) ------------------------------------------------------
-MAX_TILE = {synth.Q4_K: 16, synth.Q4_0: 16, synth.Q8_0: 8, synth.Q6_K: 8}  # x rows of one launch, by format
+MAX_TILE = {synth.Q4_K: 16, synth.Q4_0: 16, synth.Q8_0: 16, synth.Q6_K: 16}  # x rows of one launch, by format
 
 
 def tiles_i8(wtype: int, rows: int, cols: int, n_vec: int, sms: int = 148):
@@ -185,8 +185,8 @@ def test_i8_batches_are_one_pass_over_the_weights(wtype):
     """The cliff this guards against: a CTA that keeps many x records (a tall matrix under the even split, a long K) leaves the
     resident form room for one or two rows, and a batch of eight used to run as four to eight launches, each reading all weights.
     Such a batch streams x instead.  Over a grid of shapes: up to eight rows are ONE launch whatever the format; sixteen rows are
-    one launch for the 16-row formats under one or two slices (streamed, or resident where a CTA keeps few records) and two
-    otherwise; never more than one conversion launch."""
+    one launch under one or two slices (streamed, or resident where a CTA keeps few records) and at most two otherwise; never
+    more than one conversion launch."""
     for cols in (2048, 4096, 5120, 8192, 14336, 17408, 28672):
         for rows in (1024, 4096, 8192, 20480, 32768, 128256):
             if rows * cols > 1.3e9:
@@ -199,7 +199,5 @@ def test_i8_batches_are_one_pass_over_the_weights(wtype):
                 assert t.launches * t.tile_rows >= n_vec and (t.launches - 1) * t.tile_rows < n_vec, where
                 if n_vec <= 8:
                     assert t.launches == 1, where
-                elif MAX_TILE[wtype] == 8:
-                    assert t.launches == 2 and t.tile_rows == 8, where
                 else:
                     assert t.launches <= 2 and (t.launches == 1 or slices >= 4), where
